@@ -1,0 +1,208 @@
+// extern "C" entry points of libfsa_sm100.so (declared in include/fsa_sm100.h): argument
+// checks, workspace carving, TMA tensor-map encoding and kernel dispatch.  No torch types,
+// no allocation, no synchronisation on the compute paths.
+#include "../../include/fsa_sm100.h"
+#include "sel_common.cuh"
+#include "sel_launch.cuh"
+
+#include <cstring>
+#include <mutex>
+
+namespace fsa {
+
+static thread_local int g_last_cuda_error = 0;
+
+static int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return FSA_ERR_CUDA;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 2-D map over a [rows, cols] 16-bit matrix with row stride `row_stride` elements; box = 64 x box_rows,
+// 128-byte swizzle.  Rows past the end read as zero.
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t cols, int64_t row_stride,
+                  int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return cuda_fail(cudaErrorNotSupported);
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)(rows > 0 ? rows : 1)};
+    cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = fn(map, dtype == FSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)cudaErrorInvalidValue;
+        return FSA_ERR_CUDA;
+    }
+    return FSA_OK;
+}
+
+int device_sm_count(int* out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    static int cache[64];
+    if (dev >= 0 && dev < 64 && cache[dev] > 0) { *out = cache[dev]; return FSA_OK; }
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev >= 0 && dev < 64) cache[dev] = n;
+    *out = n;
+    return FSA_OK;
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, SelShape* s) {
+    if (N < 0 || B < 0 || Hq <= 0 || Hk <= 0 || T <= 0 || BK <= 0) return FSA_ERR_BAD_ARG;
+    if (Hq % Hk != 0) return FSA_ERR_BAD_ARG;
+    int G = Hq / Hk;
+    if (G > kTileRows) return FSA_ERR_UNSUPPORTED;
+    if (T > kMaxTopk || N >= kMaxTokens) return FSA_ERR_UNSUPPORTED;
+    if (!(BK == 32 || BK == 64 || BK == 128 || BK == 256)) return FSA_ERR_UNSUPPORTED;
+    if (D != 0 && !(D == 64 || D == 128 || D == 256)) return FSA_ERR_UNSUPPORTED;
+    s->N = N; s->B = B; s->Hq = Hq; s->Hk = Hk; s->G = G; s->D = D; s->T = T; s->BK = BK;
+    s->NBmax = (int)(N / BK) + B + 1;
+    s->TPT = kTileRows / G;
+    if ((int64_t)s->Hk * s->NBmax >= ((int64_t)1 << 30)) return FSA_ERR_UNSUPPORTED;
+    if ((int64_t)s->Hk * N * T >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
+    return FSA_OK;
+}
+
+static int64_t fwd_scratch_bytes(int64_t N, int Hq, int D, int T) {
+    return align_up(N * Hq * T * (int64_t)D * 4, 256) + align_up(N * Hq * T * 8, 256);
+}
+
+}  // namespace fsa
+
+using namespace fsa;
+
+extern "C" {
+
+int fsa_version(void) { return 100; }
+
+const char* fsa_error_string(int code) {
+    switch (code) {
+        case FSA_OK: return "ok";
+        case FSA_ERR_BAD_ARG: return "bad argument (null/misaligned pointer, bad size or stride)";
+        case FSA_ERR_UNSUPPORTED: return "shape not supported by the compiled sm_100a kernels";
+        case FSA_ERR_WORKSPACE: return "workspace too small";
+        case FSA_ERR_CUDA: return "CUDA call failed";
+        case FSA_ERR_DEVICE_STATUS: return "a kernel recorded a device-side failure";
+        default: return "unknown error";
+    }
+}
+
+int fsa_last_cuda_error(void) { return g_last_cuda_error; }
+
+int fsa_sel_index_bytes(int64_t N, int B, int Hq, int Hk, int T, int BK, int64_t* bytes_out) {
+    if (!bytes_out) return FSA_ERR_BAD_ARG;
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, 0, T, BK, &s);
+    if (rc) return rc;
+    *bytes_out = sel_index_bytes(s);
+    return FSA_OK;
+}
+
+int fsa_sel_fwd_scratch_bytes(int64_t N, int Hq, int D, int T, int64_t* bytes_out) {
+    if (!bytes_out || N < 0 || Hq <= 0 || D <= 0 || T <= 0) return FSA_ERR_BAD_ARG;
+    *bytes_out = fwd_scratch_bytes(N, Hq, D, T);
+    return FSA_OK;
+}
+
+int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk_idx, const int32_t* cu_seqlens,
+                int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int dtype, int64_t q_sn, int64_t q_sh,
+                int64_t k_sn, int64_t v_sn, float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse,
+                void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    if (rc) return rc;
+    if (D == 0) return FSA_ERR_BAD_ARG;
+    if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
+    if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;
+    if (N == 0) return FSA_OK;
+    if (!q || !k || !v || !topk_idx || !cu_seqlens || !o || !lse || !index_ws || !scratch) return FSA_ERR_BAD_ARG;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(scratch) || !aligned16(index_ws))
+        return FSA_ERR_BAD_ARG;
+    if ((q_sn % 8) || (q_sh % 8) || (k_sn % 8) || (v_sn % 8) || (o_sn % 8) || (o_sh % 8)) return FSA_ERR_BAD_ARG;
+    if (k_sn < (int64_t)Hk * D || v_sn < (int64_t)Hk * D) return FSA_ERR_BAD_ARG;
+    if (BK == 256 && D == 256) return FSA_ERR_UNSUPPORTED;
+    if (index_ws_bytes < sel_index_bytes(s)) return FSA_ERR_WORKSPACE;
+    if (scratch_bytes < fwd_scratch_bytes(N, Hq, D, T)) return FSA_ERR_WORKSPACE;
+
+    SelIndex ix = sel_index_carve(index_ws, s);
+    cudaError_t e = sel_build_index(topk_idx, cu_seqlens, s, ix, index_ws, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+
+    CUtensorMap kmap, vmap;
+    rc = make_tile_map(&kmap, k, dtype, N, (int64_t)Hk * D, k_sn, BK);
+    if (rc) return rc;
+    rc = make_tile_map(&vmap, v, dtype, N, (int64_t)Hk * D, v_sn, BK);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_sm_count(&sms);
+    if (rc) return rc;
+
+    float* opart = (float*)scratch;
+    float2* ml = (float2*)((char*)scratch + align_up(N * Hq * T * (int64_t)D * 4, 256));
+    e = dispatch_sel_fwd(dtype, q, q_sn, q_sh, s, ix, sm_scale, opart, ml, kmap, vmap, topk_idx, cu_seqlens, o, o_sn,
+                         o_sh, lse, sms, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return FSA_OK;
+}
+
+int fsa_read_status(const void* index_ws, void* stream_, int* status_out) {
+    if (!index_ws || !status_out) return FSA_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int st = 0;
+    cudaError_t e = cudaMemcpyAsync(&st, index_ws, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    *status_out = st;
+    return st == 0 ? FSA_OK : FSA_ERR_DEVICE_STATUS;
+}
+
+int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, int T, int BK, void* stream_,
+                       int32_t* counts_host, int32_t* row0_host, int32_t* blk_off_host, uint32_t* entries_host,
+                       int32_t* header_host) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, 0, T, BK, &s);
+    if (rc) return rc;
+    if (!index_ws) return FSA_ERR_BAD_ARG;
+    SelIndex ix = sel_index_carve(const_cast<void*>(index_ws), s);
+    int64_t HG = (int64_t)s.Hk * s.NBmax;
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (counts_host && (e = cudaMemcpy(counts_host, ix.counts, HG * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (row0_host && (e = cudaMemcpy(row0_host, ix.row0, (int64_t)s.NBmax * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (blk_off_host && (e = cudaMemcpy(blk_off_host, ix.blk_off, (HG + 1) * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (entries_host && (e = cudaMemcpy(entries_host, ix.entries, (int64_t)s.Hk * N * T * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (header_host && (e = cudaMemcpy(header_host, ix.header, 64 * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    return FSA_OK;
+}
+
+}  // extern "C"
+
+// TEMP stubs until sel_bwd.cu lands
+extern "C" int fsa_sel_bwd_scratch_bytes(int64_t, int, int, int, int, int64_t* b) { if (b) *b = 0; return FSA_ERR_UNSUPPORTED; }
+extern "C" int fsa_sel_bwd(const void*, const void*, const void*, const void*, const float*, const void*, const int32_t*,
+                const int32_t*, int64_t, int, int, int, int, int, int, int, int64_t, int64_t, int64_t, int64_t, int64_t,
+                int64_t, int64_t, int64_t, float, void*, void*, void*, void*, int64_t, void*, int64_t, void*) { return FSA_ERR_UNSUPPORTED; }

@@ -1,0 +1,16 @@
+// Host-side launch interfaces of the selected-attention kernels (defined in sel_index.cu,
+// sel_fwd.cu, sel_bwd.cu; called from fsa_api.cu).
+#pragma once
+#include "sel_common.cuh"
+
+namespace fsa {
+
+cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
+                            cudaStream_t stream);
+
+cudaError_t dispatch_sel_fwd(int dtype, const void* q, int64_t q_sn, int64_t q_sh, const SelShape& s,
+                             const SelIndex& ix, float sm_scale, float* opart, float2* ml, const CUtensorMap& kmap,
+                             const CUtensorMap& vmap, const int* topk_idx, const int* cu, void* o, int64_t o_sn,
+                             int64_t o_sh, float* lse, int num_sms, cudaStream_t stream);
+
+}  // namespace fsa

@@ -1,0 +1,100 @@
+/* C ABI of libfsa_sm100.so: hand-written sm_100a (B200) kernels for Native-Sparse-Attention's
+ * selected (top-k block-sparse) attention and the pieces next to it.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host or _out;
+ *   - tensors are described by raw pointers, sizes and element strides; the innermost
+ *     (head_dim) stride is always 1;
+ *   - `dtype`: 0 = bfloat16, 1 = float16 (the type of q/k/v/o/do/dq/dk/dv);
+ *   - every entry point enqueues its work on `stream` (a cudaStream_t) and returns without
+ *     synchronising; it never allocates device memory: workspaces are caller-owned and their
+ *     sizes come from the *_bytes queries;
+ *   - return value: 0 on success, negative FSA_ERR_* otherwise; nothing throws, nothing traps.
+ *     Device-side problems (a bounded wait that ran out) are recorded in a status word inside
+ *     the index workspace and read back with fsa_read_status().
+ *
+ * Each entry point names the reference interface it replaces (path:line inside the
+ * Relaxed-System-Lab/Flash-Sparse-Attention tree).
+ */
+#ifndef FSA_SM100_H_
+#define FSA_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FSA_OK 0
+#define FSA_ERR_BAD_ARG (-1)        /* null pointer, negative size, misaligned pointer/stride */
+#define FSA_ERR_UNSUPPORTED (-2)    /* shape outside the compiled kernels (head_dim, block size, top-k, group) */
+#define FSA_ERR_WORKSPACE (-3)      /* workspace smaller than the matching *_bytes query */
+#define FSA_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed; see fsa_last_cuda_error() */
+#define FSA_ERR_DEVICE_STATUS (-5)  /* fsa_read_status(): a kernel recorded a failure */
+
+#define FSA_DTYPE_BF16 0
+#define FSA_DTYPE_FP16 1
+
+/* Library version and a human-readable string for an error code. */
+int fsa_version(void);
+const char* fsa_error_string(int code);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+int fsa_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Selected attention (fsa/ops/FSA_topk_sparse_attention.py)
+ * ------------------------------------------------------------------------------------------- */
+
+/* Size of the index workspace: the inversion "KV block -> (token, slot) entries" that the
+ * reference rebuilds with block_to_token / index_mapping / bincount in the forward
+ * (FSA_topk_sparse_attention.py:60-135, 622-668, 951-1020) and again with reorder_topk_idx in the
+ * backward (nsa_ref/ops/topk_sparse_attention.py:412-476).  The forward fills it; the backward
+ * reuses it, so the caller keeps it alive between the two. */
+int fsa_sel_index_bytes(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int topk,
+                        int block_size, int64_t* bytes_out);
+
+/* Size of the transient forward scratch (per-(token, head, slot) partial outputs and softmax
+ * statistics; the reference's o_tiles / l_ij / acc_o_scales buffers, :959-988). */
+int fsa_sel_fwd_scratch_bytes(int64_t total_tokens, int num_q_heads, int head_dim, int topk, int64_t* bytes_out);
+
+/* Forward.  Replaces _topk_sparse_attention_fwd_opt (FSA_topk_sparse_attention.py:569-618) as called
+ * by FSATopkSparseAttention.forward (:1889-1932).
+ *   q [N, Hq, D], k/v [N, Hk, D], o [N, Hq, D] in `dtype`; head stride of k and v must be D;
+ *   topk_idx [Hk, N, T] int32 contiguous: block ids local to each sequence, usable ids first,
+ *   -1 padding; cu_seqlens [B+1] int32; lse_out [Hq, N] fp32, log2 units (:178 of nsa_ref's kernel). */
+int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk_idx, const int32_t* cu_seqlens,
+                int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int head_dim, int topk,
+                int block_size, int dtype, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                int64_t v_stride_n, float sm_scale, void* o, int64_t o_stride_n, int64_t o_stride_h, float* lse,
+                void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Size of the transient backward scratch (dQ partials, fp32 dK/dV accumulators, delta). */
+int fsa_sel_bwd_scratch_bytes(int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim, int topk,
+                              int64_t* bytes_out);
+
+/* Backward.  Replaces _topk_sparse_attention_bwd_opt (FSA_topk_sparse_attention.py:1715-1884):
+ * backward_sum_o_do, backward_dkdv, dq_compute_kernel, dq_reduce_kernel.  `index_ws` is the
+ * workspace the forward filled for the same topk_idx / cu_seqlens.
+ *   o, d_o, dq [N, Hq, D]; dk, dv [N, Hk, D] contiguous; lse [Hq, N] from the forward. */
+int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                const int32_t* topk_idx, const int32_t* cu_seqlens, int64_t total_tokens, int batch, int num_q_heads,
+                int num_kv_heads, int head_dim, int topk, int block_size, int dtype, int64_t q_stride_n,
+                int64_t q_stride_h, int64_t k_stride_n, int64_t v_stride_n, int64_t o_stride_n, int64_t o_stride_h,
+                int64_t do_stride_n, int64_t do_stride_h, float sm_scale, void* dq, void* dk, void* dv,
+                void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Copy the device status word of an index workspace to the host (synchronises `stream`).
+ * *status_out: 0 ok, 1 a bounded wait ran out, 2 an out-of-table index was skipped.
+ * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
+int fsa_read_status(const void* index_ws, void* stream, int* status_out);
+
+/* Debug/inspection: copy the block->entries CSR built by the forward to host arrays.
+ * counts_host [Hk * nbmax], row0_host [nbmax]; *nbmax_out = total_tokens / block_size + batch + 1. */
+int fsa_sel_index_dump(const void* index_ws, int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads,
+                       int topk, int block_size, void* stream, int32_t* counts_host, int32_t* row0_host,
+                       int32_t* blk_off_host, uint32_t* entries_host, int32_t* header_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSA_SM100_H_ */
