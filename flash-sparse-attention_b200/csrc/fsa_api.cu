@@ -84,6 +84,12 @@ static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, Se
     return FSA_OK;
 }
 
+static int bwd_nsub(int BK) { return BK > 64 ? BK / 64 : 1; }
+static int64_t bwd_scratch_bytes(int64_t N, int Hq, int Hk, int D, int T, int BK) {
+    return align_up(N * Hq * 4, 256) + align_up(N * Hq * T * bwd_nsub(BK) * (int64_t)D * 4, 256) +
+           align_up(2 * N * Hk * (int64_t)D * 4, 256);
+}
+
 static int64_t fwd_scratch_bytes(int64_t N, int Hq, int D, int T) {
     return align_up(N * Hq * T * (int64_t)D * 4, 256) + align_up(N * Hq * T * 8, 256);
 }
@@ -167,6 +173,61 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
     return FSA_OK;
 }
 
+int fsa_sel_bwd_scratch_bytes(int64_t N, int Hq, int Hk, int D, int T, int BK, int64_t* bytes_out) {
+    if (!bytes_out || N < 0 || Hq <= 0 || Hk <= 0 || D <= 0 || T <= 0 || BK <= 0) return FSA_ERR_BAD_ARG;
+    *bytes_out = bwd_scratch_bytes(N, Hq, Hk, D, T, BK);
+    return FSA_OK;
+}
+
+int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                const int32_t* topk_idx, const int32_t* cu_seqlens, int64_t N, int B, int Hq, int Hk, int D, int T,
+                int BK, int dtype, int64_t q_sn, int64_t q_sh, int64_t k_sn, int64_t v_sn, int64_t o_sn, int64_t o_sh,
+                int64_t do_sn, int64_t do_sh, float sm_scale, void* dq, void* dk, void* dv, void* index_ws,
+                int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    if (rc) return rc;
+    if (D == 0) return FSA_ERR_BAD_ARG;
+    if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
+    if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;
+    if (N == 0) return FSA_OK;
+    if (!q || !k || !v || !o || !lse || !d_o || !topk_idx || !cu_seqlens || !dq || !dk || !dv || !index_ws || !scratch)
+        return FSA_ERR_BAD_ARG;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv) || !aligned16(scratch) || !aligned16(index_ws))
+        return FSA_ERR_BAD_ARG;
+    if ((q_sn % 8) || (q_sh % 8) || (k_sn % 8) || (v_sn % 8) || (o_sn % 8) || (o_sh % 8) || (do_sn % 8) || (do_sh % 8))
+        return FSA_ERR_BAD_ARG;
+    if (k_sn < (int64_t)Hk * D || v_sn < (int64_t)Hk * D) return FSA_ERR_BAD_ARG;
+    if (index_ws_bytes < sel_index_bytes(s)) return FSA_ERR_WORKSPACE;
+    if (scratch_bytes < bwd_scratch_bytes(N, Hq, Hk, D, T, BK)) return FSA_ERR_WORKSPACE;
+
+    SelIndex ix = sel_index_carve(index_ws, s);
+    CUtensorMap kmap, vmap;
+    rc = make_tile_map(&kmap, k, dtype, N, (int64_t)Hk * D, k_sn, 64);
+    if (rc) return rc;
+    rc = make_tile_map(&vmap, v, dtype, N, (int64_t)Hk * D, v_sn, 64);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_sm_count(&sms);
+    if (rc) return rc;
+
+    SelBwdArgs a;
+    a.q = q; a.d_o = d_o; a.o = o;
+    a.q_sn = q_sn; a.q_sh = q_sh; a.do_sn = do_sn; a.do_sh = do_sh; a.o_sn = o_sn; a.o_sh = o_sh;
+    a.lse = lse; a.topk_idx = topk_idx; a.cu = cu_seqlens; a.sm_scale = sm_scale;
+    char* sp = (char*)scratch;
+    a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 256);
+    a.dq_part = (float*)sp; sp += align_up(N * Hq * T * bwd_nsub(BK) * (int64_t)D * 4, 256);
+    a.dk_acc = (float*)sp;
+    a.dv_acc = a.dk_acc + N * Hk * (int64_t)D;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    cudaError_t e = dispatch_sel_bwd(dtype, a, s, ix, kmap, vmap, sms, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return FSA_OK;
+}
+
 int fsa_read_status(const void* index_ws, void* stream_, int* status_out) {
     if (!index_ws || !status_out) return FSA_ERR_BAD_ARG;
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -200,9 +261,3 @@ int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, i
 }
 
 }  // extern "C"
-
-// TEMP stubs until sel_bwd.cu lands
-extern "C" int fsa_sel_bwd_scratch_bytes(int64_t, int, int, int, int, int64_t* b) { if (b) *b = 0; return FSA_ERR_UNSUPPORTED; }
-extern "C" int fsa_sel_bwd(const void*, const void*, const void*, const void*, const float*, const void*, const int32_t*,
-                const int32_t*, int64_t, int, int, int, int, int, int, int, int64_t, int64_t, int64_t, int64_t, int64_t,
-                int64_t, int64_t, int64_t, float, void*, void*, void*, void*, int64_t, void*, int64_t, void*) { return FSA_ERR_UNSUPPORTED; }

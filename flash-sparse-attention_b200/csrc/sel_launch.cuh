@@ -13,4 +13,23 @@ cudaError_t dispatch_sel_fwd(int dtype, const void* q, int64_t q_sn, int64_t q_s
                              const CUtensorMap& vmap, const int* topk_idx, const int* cu, void* o, int64_t o_sn,
                              int64_t o_sh, float* lse, int num_sms, cudaStream_t stream);
 
+struct SelBwdArgs {
+    const void *q, *d_o, *o;
+    int64_t q_sn, q_sh, do_sn, do_sh, o_sn, o_sh;
+    const float* lse;
+    const int* topk_idx;
+    const int* cu;
+    float sm_scale;
+    // scratch
+    float* delta;      // [Hq, N]
+    float* dq_part;    // [N, Hq, T * nsub, D]
+    float* dk_acc;     // [N, Hk, D]; dv_acc follows immediately
+    float* dv_acc;
+    // outputs (contiguous)
+    void *dq, *dk, *dv;
+};
+
+cudaError_t dispatch_sel_bwd(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
+                             const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream);
+
 }  // namespace fsa
