@@ -11,11 +11,14 @@
 namespace fsa {
 
 static thread_local int g_last_cuda_error = 0;
+static thread_local int g_last_cuda_line = 0;
 
-static int cuda_fail(cudaError_t e) {
+static int cuda_fail_at(cudaError_t e, int line) {
     g_last_cuda_error = (int)e;
+    g_last_cuda_line = line;
     return FSA_ERR_CUDA;
 }
+#define cuda_fail(e) cuda_fail_at((e), __LINE__)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -45,10 +48,7 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, i
     CUresult r = fn(map, dtype == FSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                     const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        g_last_cuda_error = (int)cudaErrorInvalidValue;
-        return FSA_ERR_CUDA;
-    }
+    if (r != CUDA_SUCCESS) return cuda_fail_at(cudaErrorInvalidValue, -(int)r - 100000);   // driver error code, negated
     return FSA_OK;
 }
 
@@ -63,6 +63,41 @@ int device_sm_count(int* out) {
     if (e != cudaSuccess) return cuda_fail(e);
     if (dev >= 0 && dev < 64) cache[dev] = n;
     *out = n;
+    return FSA_OK;
+}
+
+// ---- optional kernel timing: a ring of event pairs per kernel id
+constexpr int kProfKernels = 16;
+constexpr int kProfRing = 64;
+static bool g_prof_on = false;
+static cudaEvent_t g_prof_ev[kProfKernels][kProfRing][2];
+static bool g_prof_made[kProfKernels];
+static int g_prof_count[kProfKernels];
+
+void prof_begin(int id, cudaStream_t stream) {
+    if (!g_prof_on || id < 0 || id >= kProfKernels) return;
+    if (!g_prof_made[id]) {
+        for (int i = 0; i < kProfRing; ++i)
+            if (cudaEventCreate(&g_prof_ev[id][i][0]) != cudaSuccess || cudaEventCreate(&g_prof_ev[id][i][1]) != cudaSuccess) return;
+        g_prof_made[id] = true;
+    }
+    cudaEventRecord(g_prof_ev[id][g_prof_count[id] % kProfRing][0], stream);
+}
+void prof_end(int id, cudaStream_t stream) {
+    if (!g_prof_on || id < 0 || id >= kProfKernels || !g_prof_made[id]) return;
+    cudaEventRecord(g_prof_ev[id][g_prof_count[id] % kProfRing][1], stream);
+    ++g_prof_count[id];
+}
+
+// Tensor-map encoding is a driver call and needs the primary context bound to the calling
+// thread; a thread that has only ever been handed device pointers (an autograd worker) may not
+// have one yet.  cudaSetDevice on the current device binds it.
+static int ensure_context() {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaSetDevice(dev);
+    if (e != cudaSuccess) return cuda_fail(e);
     return FSA_OK;
 }
 
@@ -115,6 +150,31 @@ const char* fsa_error_string(int code) {
 }
 
 int fsa_last_cuda_error(void) { return g_last_cuda_error; }
+int fsa_last_cuda_error_line(void) { return g_last_cuda_line; }
+
+int fsa_profile_enable(int on) {
+    g_prof_on = on != 0;
+    for (int i = 0; i < kProfKernels; ++i) g_prof_count[i] = 0;
+    return FSA_OK;
+}
+
+int fsa_profile_read(int kernel_id, float* ms_sum_out, int* launches_out) {
+    if (!ms_sum_out || !launches_out || kernel_id < 0 || kernel_id >= kProfKernels) return FSA_ERR_BAD_ARG;
+    *ms_sum_out = 0.f;
+    *launches_out = 0;
+    if (!g_prof_made[kernel_id]) return FSA_OK;
+    int n = g_prof_count[kernel_id] < kProfRing ? g_prof_count[kernel_id] : kProfRing;
+    for (int i = 0; i < n; ++i) {
+        cudaError_t e = cudaEventSynchronize(g_prof_ev[kernel_id][i][1]);
+        if (e != cudaSuccess) return cuda_fail(e);
+        float ms = 0.f;
+        e = cudaEventElapsedTime(&ms, g_prof_ev[kernel_id][i][0], g_prof_ev[kernel_id][i][1]);
+        if (e != cudaSuccess) return cuda_fail(e);
+        *ms_sum_out += ms;
+    }
+    *launches_out = n;
+    return FSA_OK;
+}
 
 int fsa_sel_index_bytes(int64_t N, int B, int Hq, int Hk, int T, int BK, int64_t* bytes_out) {
     if (!bytes_out) return FSA_ERR_BAD_ARG;
@@ -136,9 +196,11 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
                 int64_t k_sn, int64_t v_sn, float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse,
                 void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
+    (void)cudaGetLastError();   // drop any stale error another library left on this thread
     SelShape s;
     int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
     if (rc) return rc;
+    if ((rc = ensure_context()) != FSA_OK) return rc;
     if (D == 0) return FSA_ERR_BAD_ARG;
     if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
     if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;
@@ -185,9 +247,11 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
                 int64_t do_sn, int64_t do_sh, float sm_scale, void* dq, void* dk, void* dv, void* index_ws,
                 int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
+    (void)cudaGetLastError();   // drop any stale error another library left on this thread
     SelShape s;
     int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
     if (rc) return rc;
+    if ((rc = ensure_context()) != FSA_OK) return rc;
     if (D == 0) return FSA_ERR_BAD_ARG;
     if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
     if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;

@@ -455,12 +455,16 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     int by_smem = (227 * 1024) / (smem + 2048);
     if (by_smem < per_sm) per_sm = by_smem;
     if (per_sm < 1) per_sm = 1;
+    prof_begin(2, stream);
     kern<<<num_sms * per_sm, 128, smem, stream>>>(p, kmap, vmap);
+    prof_end(2, stream);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
+        prof_begin(3, stream);
         sel_bwd_dq_reduce<D, ET><<<grid, 256, 0, stream>>>(a.dq_part, a.topk_idx, a.cu, s, nsub, (ET*)a.dq);
+        prof_end(3, stream);
     }
     if (kv_elems > 0) {
         int64_t n4 = kv_elems / 4;

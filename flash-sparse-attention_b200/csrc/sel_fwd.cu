@@ -320,13 +320,17 @@ cudaError_t launch_sel_fwd(const SelFwdParams<ET>& p, const CUtensorMap& kmap, c
     int per_sm = by_tmem < by_smem ? by_tmem : by_smem;
     if (per_sm < 1) per_sm = 1;
     if (per_sm > 4) per_sm = 4;
+    prof_begin(0, stream);
     kern<<<num_sms * per_sm, 128, smem, stream>>>(p, kmap, vmap);
+    prof_end(0, stream);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     int64_t rows = p.s.N * p.s.Hq;
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
+        prof_begin(1, stream);
         sel_fwd_reduce<D, ET><<<grid, 256, 0, stream>>>(p.opart, p.ml, topk_idx, cu, p.s, o, o_sn, o_sh, lse);
+        prof_end(1, stream);
     }
     return cudaGetLastError();
 }

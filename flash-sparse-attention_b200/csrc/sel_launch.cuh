@@ -5,6 +5,11 @@
 
 namespace fsa {
 
+// Optional per-kernel timing (off by default): library-owned CUDA events bracket a kernel on
+// the stream it is launched on.  Ids are the FSA_KERNEL_* constants of the public header.
+void prof_begin(int kernel_id, cudaStream_t stream);
+void prof_end(int kernel_id, cudaStream_t stream);
+
 cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
                             cudaStream_t stream);
 

@@ -29,6 +29,9 @@ SIGNATURES = {
     "fsa_version": (c_int, []),
     "fsa_error_string": (c_char_p, [c_int]),
     "fsa_last_cuda_error": (c_int, []),
+    "fsa_last_cuda_error_line": (c_int, []),
+    "fsa_profile_enable": (c_int, [c_int]),
+    "fsa_profile_read": (c_int, [c_int, POINTER(c_float), POINTER(c_int)]),
     "fsa_sel_index_bytes": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64)]),
     "fsa_sel_fwd_scratch_bytes": (c_int, [c_int64, c_int, c_int, c_int, POINTER(c_int64)]),
     "fsa_sel_fwd": (
@@ -81,7 +84,7 @@ def check(rc: int, what: str) -> None:
     L = lib()
     msg = L.fsa_error_string(rc).decode()
     if rc == FSA_ERR_CUDA:
-        msg += f" (cudaError {L.fsa_last_cuda_error()})"
+        msg += f" (cudaError {L.fsa_last_cuda_error()} at fsa_api.cu:{L.fsa_last_cuda_error_line()})"
     if rc in (FSA_ERR_BAD_ARG, FSA_ERR_UNSUPPORTED):
         raise ValueError(f"{what}: {msg}")
     raise FsaError(f"{what}: {msg}")

@@ -40,6 +40,20 @@ int fsa_version(void);
 const char* fsa_error_string(int code);
 /* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
 int fsa_last_cuda_error(void);
+/* Source line inside the library's API file of that failing call (diagnostics). */
+int fsa_last_cuda_error_line(void);
+
+/* Optional kernel timing for benchmarks (off by default; no counterpart in the reference, which
+ * times whole operators with CUDA events, utils.py:6-27).  When enabled, the library brackets each
+ * named kernel with its own CUDA events on the launching stream (a ring of 64 launches per kernel,
+ * restarted by every fsa_profile_enable call); fsa_profile_read() waits for those launches and
+ * returns the sum of their durations in milliseconds and how many there were. */
+#define FSA_KERNEL_SEL_FWD_MAIN 0
+#define FSA_KERNEL_SEL_FWD_REDUCE 1
+#define FSA_KERNEL_SEL_BWD_MAIN 2
+#define FSA_KERNEL_SEL_BWD_DQ_REDUCE 3
+int fsa_profile_enable(int on);
+int fsa_profile_read(int kernel_id, float* ms_sum_out, int* launches_out);
 
 /* ---------------------------------------------------------------------------------------------
  * Selected attention (fsa/ops/FSA_topk_sparse_attention.py)
