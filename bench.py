@@ -167,6 +167,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default="cfg1", choices=["cfg1", "small"],
+                    help="small = one 16384-token sequence of cfg1 (a quarter of it), for profiler captures")
+    ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -194,6 +197,8 @@ def main():
 
     L = _lib.lib()
     seqlens, Hk, G, d, bs, T = (CFG[k] for k in ("seqlens", "Hk", "G", "d", "bs", "T"))
+    if args.case == "small":
+        seqlens = seqlens[:1]
     N = sum(seqlens)
     scale = d ** -0.5
     # each rank owns one 4-KV-head shard with its own seed
@@ -257,13 +262,17 @@ def main():
         res = torch.stack([qh.grad.float().norm(), kh.grad.float().norm(), vh.grad.float().norm()])
         return res.cpu()
 
-    e2e_step()
+    if args.no_e2e:
+        e2e_steps = 0
+    else:
+        e2e_step()
     barrier()
     ev0.record()
     for _ in range(e2e_steps):
         res = e2e_step()
     ev1.record()
     barrier()
+    e2e_steps = max(e2e_steps, 1)
     t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -296,7 +305,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded N(0,1) q/k/v/dO, seeded causal block ids)",
-            "config": {"workload": workload_name(), "parallelism": f"kv-head shards x{world}, no collective",
+            "config": {"workload": workload_name() if args.case == "cfg1" else "small: 1x16384 tokens of cfg1", "parallelism": f"kv-head shards x{world}, no collective",
                        "l2": "inputs and partial buffers exceed L2 (q 134 MB, partials > 4 GB per step)",
                        "useful_flops_per_step": flops_step, "tokens_per_s": world * N / (ms_step * 1e-3)},
             "kernels": kern,

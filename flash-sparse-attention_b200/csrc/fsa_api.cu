@@ -5,6 +5,7 @@
 #include "sel_common.cuh"
 #include "sel_launch.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -101,21 +102,27 @@ static int ensure_context() {
     return FSA_OK;
 }
 
+// Tuning knobs read from the environment (0 / unset = built-in default).
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, SelShape* s) {
     if (N < 0 || B < 0 || Hq <= 0 || Hk <= 0 || T <= 0 || BK <= 0) return FSA_ERR_BAD_ARG;
     if (Hq % Hk != 0) return FSA_ERR_BAD_ARG;
     int G = Hq / Hk;
-    if (G > kTileRows) return FSA_ERR_UNSUPPORTED;
+    if (G > 32) return FSA_ERR_UNSUPPORTED;   // a tile needs >= 4 tokens per head row group
     if (T > kMaxTopk || N >= kMaxTokens) return FSA_ERR_UNSUPPORTED;
     if (!(BK == 32 || BK == 64 || BK == 128 || BK == 256)) return FSA_ERR_UNSUPPORTED;
     if (D != 0 && !(D == 64 || D == 128 || D == 256)) return FSA_ERR_UNSUPPORTED;
     s->N = N; s->B = B; s->Hq = Hq; s->Hk = Hk; s->G = G; s->D = D; s->T = T; s->BK = BK;
     s->NBmax = (int)(N / BK) + B + 1;
-    s->TPT = kTileRows / G;
+    s->TPT = (kTileRows / G) & ~3;
     if ((int64_t)s->Hk * s->NBmax >= ((int64_t)1 << 30)) return FSA_ERR_UNSUPPORTED;
-    if ((int64_t)s->Hk * N * T >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
+    if ((int64_t)s->Hk * N * T + (int64_t)s->Hk * s->NBmax * kTileRows >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
     return FSA_OK;
 }
 
@@ -125,8 +132,9 @@ static int64_t bwd_scratch_bytes(int64_t N, int Hq, int Hk, int D, int T, int BK
            align_up(2 * N * Hk * (int64_t)D * 4, 256);
 }
 
-static int64_t fwd_scratch_bytes(int64_t N, int Hq, int D, int T) {
-    return align_up(N * Hq * T * (int64_t)D * 4, 256) + align_up(N * Hq * T * 8, 256);
+static int64_t fwd_scratch_bytes(const SelShape& s) {
+    int64_t rows = sel_max_tiles(s) * kTileRows;
+    return align_up(rows * s.D * 2, 1024) + align_up(rows * 8, 256);
 }
 
 }  // namespace fsa
@@ -185,9 +193,12 @@ int fsa_sel_index_bytes(int64_t N, int B, int Hq, int Hk, int T, int BK, int64_t
     return FSA_OK;
 }
 
-int fsa_sel_fwd_scratch_bytes(int64_t N, int Hq, int D, int T, int64_t* bytes_out) {
-    if (!bytes_out || N < 0 || Hq <= 0 || D <= 0 || T <= 0) return FSA_ERR_BAD_ARG;
-    *bytes_out = fwd_scratch_bytes(N, Hq, D, T);
+int fsa_sel_fwd_scratch_bytes(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int64_t* bytes_out) {
+    if (!bytes_out) return FSA_ERR_BAD_ARG;
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    if (rc) return rc;
+    *bytes_out = fwd_scratch_bytes(s);
     return FSA_OK;
 }
 
@@ -212,25 +223,34 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
     if (k_sn < (int64_t)Hk * D || v_sn < (int64_t)Hk * D) return FSA_ERR_BAD_ARG;
     if (BK == 256 && D == 256) return FSA_ERR_UNSUPPORTED;
     if (index_ws_bytes < sel_index_bytes(s)) return FSA_ERR_WORKSPACE;
-    if (scratch_bytes < fwd_scratch_bytes(N, Hq, D, T)) return FSA_ERR_WORKSPACE;
+    if (scratch_bytes < fwd_scratch_bytes(s)) return FSA_ERR_WORKSPACE;
 
     SelIndex ix = sel_index_carve(index_ws, s);
     cudaError_t e = sel_build_index(topk_idx, cu_seqlens, s, ix, index_ws, stream);
     if (e != cudaSuccess) return cuda_fail(e);
 
-    CUtensorMap kmap, vmap;
+    CUtensorMap kmap, vmap, omap;
     rc = make_tile_map(&kmap, k, dtype, N, (int64_t)Hk * D, k_sn, BK);
     if (rc) return rc;
     rc = make_tile_map(&vmap, v, dtype, N, (int64_t)Hk * D, v_sn, BK);
     if (rc) return rc;
+    const int64_t prow = sel_max_tiles(s) * kTileRows;
+    SelFwdArgs a;
+    a.q = q; a.q_sn = q_sn; a.q_sh = q_sh; a.sm_scale = sm_scale;
+    a.run = env_int("FSA_SEL_RUN", 0);
+    a.opart = scratch;
+    a.ml = (float2*)((char*)scratch + align_up(prow * D * 2, 1024));
+    a.o = o; a.o_sn = o_sn; a.o_sh = o_sh; a.lse = lse;
+    a.kmap = &kmap; a.vmap = &vmap; a.qmap = nullptr; a.omap = nullptr;
+    if (D <= 128 && BK <= 128) {
+        rc = make_tile_map(&omap, scratch, dtype, prow, D, D, 32);
+        if (rc) return rc;
+        a.omap = &omap;
+    }
     int sms = 0;
     rc = device_sm_count(&sms);
     if (rc) return rc;
-
-    float* opart = (float*)scratch;
-    float2* ml = (float2*)((char*)scratch + align_up(N * Hq * T * (int64_t)D * 4, 256));
-    e = dispatch_sel_fwd(dtype, q, q_sn, q_sh, s, ix, sm_scale, opart, ml, kmap, vmap, topk_idx, cu_seqlens, o, o_sn,
-                         o_sh, lse, sms, stream);
+    e = dispatch_sel_fwd(dtype, a, s, ix, sms, stream);
     if (e != cudaSuccess) return cuda_fail(e);
     return FSA_OK;
 }
@@ -305,7 +325,7 @@ int fsa_read_status(const void* index_ws, void* stream_, int* status_out) {
 }
 
 int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, int T, int BK, void* stream_,
-                       int32_t* counts_host, int32_t* row0_host, int32_t* blk_off_host, uint32_t* entries_host,
+                       int32_t* counts_host, int32_t* row0_host, int32_t* tile_off_host, uint32_t* entries_host,
                        int32_t* header_host) {
     cudaStream_t stream = (cudaStream_t)stream_;
     SelShape s;
@@ -318,8 +338,8 @@ int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, i
     if (e != cudaSuccess) return cuda_fail(e);
     if (counts_host && (e = cudaMemcpy(counts_host, ix.counts, HG * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     if (row0_host && (e = cudaMemcpy(row0_host, ix.row0, (int64_t)s.NBmax * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
-    if (blk_off_host && (e = cudaMemcpy(blk_off_host, ix.blk_off, (HG + 1) * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
-    if (entries_host && (e = cudaMemcpy(entries_host, ix.entries, (int64_t)s.Hk * N * T * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (tile_off_host && (e = cudaMemcpy(tile_off_host, ix.tile_off, (HG + 1) * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (entries_host && (e = cudaMemcpy(entries_host, ix.entries, sel_max_tiles(s) * s.TPT * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     if (header_host && (e = cudaMemcpy(header_host, ix.header, 64 * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     return FSA_OK;
 }

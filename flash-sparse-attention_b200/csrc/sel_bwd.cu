@@ -94,7 +94,6 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
     const uint32_t tbase = tmem_slot;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
 
-    const int HG = s.Hk * s.NBmax;
     const int total = p.ix.header[1] * p.nsub;
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int begin = blockIdx.x * per;
@@ -145,7 +144,7 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
         {
             int tl = item / p.nsub;
             if (hg < 0 || tl < hg_first || tl >= hg_first + hg_tiles) {
-                hg = upper_seg(p.ix.tile_off, HG, tl);
+                hg = load_tile(p.ix, tl).hg;     // items of one hg span [tile_off[hg], tile_off[hg+1]) * nsub
                 hg_first = p.ix.tile_off[hg];
                 hg_tiles = p.ix.tile_off[hg + 1] - hg_first;
                 sub = -1;
@@ -161,7 +160,7 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
         const int cnt = p.ix.counts[hg];
         const int e0 = tile * s.TPT;
         const int ne = min(s.TPT, cnt - e0);
-        const int64_t ebase = (int64_t)p.ix.blk_off[hg] + e0;
+        const int64_t ebase = (int64_t)(hg_first + tile) * s.TPT;
 
         // ---- stage 1
         if (new_kv && have_acc) {
@@ -171,6 +170,7 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
             have_acc = false;
         }
         if (tid < s.TPT) s_ent[tid] = tid < ne ? p.ix.entries[ebase + tid] : 0xFFFFFFFFu;
+        (void)e0;
         if (new_kv && tid == 0) {
             mbar_expect_tx(&bar_kv, (uint32_t)(2 * kKT * D * 2));
 #pragma unroll

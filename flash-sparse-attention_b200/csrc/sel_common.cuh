@@ -7,8 +7,13 @@
 //   gb         global KV-block id.  For sequence b starting at row c_b, local block j:
 //                  gb = c_b / BK + b + j      (unique, ascending, < N/BK + B + 1)
 //   hg         kv_head * NBmax + gb, the key of the block->entries CSR
-//   tile       up to TPT = 128 / G consecutive entries of one hg; each entry contributes its G
-//              query heads, so a tile is <= 128 rows of the MMA
+//   tile       up to TPT = (128 / G) & ~3 consecutive entries of one hg; each entry contributes its G
+//              query heads, so a tile is <= 128 rows of the MMA.  Rows are head-major inside a tile:
+//              row r = g * TPT + e (head g of the group, e-th entry of the tile), so that four
+//              consecutive rows are four tokens of one head -- one TMA gather4.
+//   pos        for every (kv head, token, slot): tile_off[hg] * TPT + rank of the entry inside its
+//              block, or -1 for an unusable slot.  Partial results live in tile order
+//              (row = (pos / TPT) * 128 + g * TPT + pos % TPT), which the merge kernels look up here.
 #pragma once
 #include <stdint.h>
 #include "sm100_prims.cuh"
@@ -30,7 +35,7 @@ struct SelShape {
     int T;           // top-k slots
     int BK;          // KV block size
     int NBmax;       // bound on gb: N / BK + B + 1
-    int TPT;         // entries per tile = 128 / G
+    int TPT;         // entries per tile = (128 / G) & ~3
 };
 
 // Index workspace (kept by the caller between forward and backward).  All int32.
@@ -39,12 +44,19 @@ struct SelIndex {
     int* counts;     // [Hk * NBmax]   entries per hg
     int* cursor;     // [Hk * NBmax]   fill cursors (scratch)
     int* row0;       // [NBmax]        first global K/V row of block gb
-    int* blk_off;    // [Hk * NBmax + 1] exclusive scan of counts
-    int* tile_off;   // [Hk * NBmax + 1] exclusive scan of ceil(counts / TPT)
-    uint32_t* entries;  // [Hk * N * T]  packed entries grouped by hg
+    int* tile_off;   // [Hk * NBmax + 1] exclusive scan of ceil(counts / TPT): first tile of every hg
+    int4* tile_rec;  // [max_tiles]   per tile {kv head, first K/V row of the block, entries in the tile, hg}
+    uint32_t* entries;  // [max_tiles * TPT]  packed entries in TILE ORDER: entry e of tile j at j * TPT + e,
+                        //                    0xFFFFFFFF where a tile is not full
+    int* pos;        // [Hk * N * T]  tile-order position of every (head, token, slot), -1 if unusable
 };
 
 __host__ __device__ inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+// upper bound on the number of tiles (known on the host without a sync)
+inline int64_t sel_max_tiles(const SelShape& s) {
+    return ((int64_t)s.Hk * s.N * s.T + s.TPT - 1) / s.TPT + (int64_t)s.Hk * s.NBmax;
+}
 
 inline int64_t sel_index_bytes(const SelShape& s) {
     int64_t HG = (int64_t)s.Hk * s.NBmax;
@@ -52,7 +64,9 @@ inline int64_t sel_index_bytes(const SelShape& s) {
     b += align_up(64 * 4, 256);
     b += align_up(HG * 4, 256) * 2;
     b += align_up((int64_t)s.NBmax * 4, 256);
-    b += align_up((HG + 1) * 4, 256) * 2;
+    b += align_up((HG + 1) * 4, 256);
+    b += align_up(sel_max_tiles(s) * 16, 256);
+    b += align_up(sel_max_tiles(s) * s.TPT * 4, 256);
     b += align_up((int64_t)s.Hk * s.N * s.T * 4, 256);
     return b;
 }
@@ -65,9 +79,10 @@ inline SelIndex sel_index_carve(void* ws, const SelShape& s) {
     ix.counts = (int*)p;   p += align_up(HG * 4, 256);
     ix.cursor = (int*)p;   p += align_up(HG * 4, 256);
     ix.row0 = (int*)p;     p += align_up((int64_t)s.NBmax * 4, 256);
-    ix.blk_off = (int*)p;  p += align_up((HG + 1) * 4, 256);
     ix.tile_off = (int*)p; p += align_up((HG + 1) * 4, 256);
-    ix.entries = (uint32_t*)p;
+    ix.tile_rec = (int4*)p; p += align_up(sel_max_tiles(s) * 16, 256);
+    ix.entries = (uint32_t*)p; p += align_up(sel_max_tiles(s) * s.TPT * 4, 256);
+    ix.pos = (int*)p;
     return ix;
 }
 // bytes from the start of the workspace that must be zero before the index build
@@ -105,5 +120,48 @@ __device__ __forceinline__ int upper_seg(const int* __restrict__ off, int n, int
     }
     return lo;
 }
+
+// Static tile schedule of a persistent grid: runs of `run` consecutive tiles are dealt to the
+// CTAs round-robin, so the whole grid advances through the tile list together (neighbouring
+// blocks of one kv head: their query rows stay in L2) while a CTA still reuses a resident K/V
+// block across the tiles of a run.
+struct TileSchedule {
+    int total, grid, cta, run, nloc;
+    __device__ TileSchedule(int total_, int run_) : total(total_), grid((int)gridDim.x), cta((int)blockIdx.x), run(run_) {
+        const int NR = (total + run - 1) / run;                    // runs in the list
+        const int mine = cta < NR ? (NR - cta + grid - 1) / grid : 0;
+        nloc = mine * run;
+        if (mine > 0 && (NR - 1) % grid == cta) nloc -= NR * run - total;   // the last run may be short
+    }
+    __device__ __forceinline__ int tile(int k) const { return ((k / run) * grid + cta) * run + (k % run); }
+};
+
+// One tile of the list, read from its record: no searching, and the address depends only on the
+// tile index, so records and entries can be prefetched any number of tiles ahead.
+struct TileInfo {
+    int h, row0, ne, hg;
+};
+__device__ __forceinline__ TileInfo load_tile(const SelIndex& ix, int tile) {
+    int4 r = __ldg(ix.tile_rec + tile);
+    return TileInfo{r.x, r.y, r.z, r.w};
+}
+
+// Sequential walker used by the unpipelined kernels.
+struct TileWalker {
+    const SelIndex& ix;
+    const SelShape& s;
+    int hg = -1;
+    int h = 0, row0 = 0, ne = 0;
+    int64_t ebase = 0;
+    __device__ TileWalker(const SelIndex& ix_, const SelShape& s_) : ix(ix_), s(s_) {}
+    // returns true when the tile belongs to a different block than the previous one
+    __device__ __forceinline__ bool seek(int item) {
+        TileInfo t = load_tile(ix, item);
+        bool nb = t.hg != hg;
+        hg = t.hg; h = t.h; row0 = t.row0; ne = t.ne;
+        ebase = (int64_t)item * s.TPT;
+        return nb;
+    }
+};
 
 }  // namespace fsa

@@ -1,51 +1,543 @@
 // Selected-attention forward for sm_100a.
 //
 // Main kernel (replaces forward_kernel_opt and the qk_kernel pre-pass of the reference,
-// fsa/ops/FSA_topk_sparse_attention.py:285-566): KV blocks are the outer loop.  A CTA owns a
-// contiguous range of tiles; a tile is <= 128 rows = (selecting token, query head of the
-// group).  K and V of the block arrive by TMA (128-byte swizzle) and stay resident while the
-// CTA walks the block's tiles; the query rows are gathered by token id with 16-byte async
-// copies into the same swizzled layout.  S = Q K^T and O = P V run on tcgen05 with TMEM
-// accumulators; each thread owns one row of S, so row max / row sum need no shuffles.  The
-// kernel writes, per (token, head, slot), an unnormalised partial O (fp32) and the pair
-// (m, l) = (row max in log2 units, sum of exp2(s - m)).  No atomics, no cross-block state.
+// fsa/ops/FSA_topk_sparse_attention.py:285-566): KV blocks are the outer loop.  A persistent
+// CTA owns a contiguous range of tiles; a tile is <= 128 rows = (query head of the group,
+// selecting token).  Warp-specialised:
+//   warps 0..3  load: K/V block by tiled TMA (128-byte swizzle, double-buffered); query rows
+//               gathered by token id with 16-byte async copies into a ring of swizzled Q stages
+//               (TMA gather4 was measured at ~70 cycles per 512-byte instruction: too slow);
+//   warp 4      one elected thread issues tcgen05.mma S = Q K^T into one of two TMEM S buffers;
+//   warp 5      one elected thread issues O = P V (P read from TMEM, V MN-major from smem) into one
+//               of two TMEM O buffers; two issuing warps keep the two streams from blocking each other;
+//   warps 6..13 two softmax groups, each owning every other tile: one thread per row, row
+//               max / exp2 / row sum from TMEM, P written back to TMEM over S (16-bit), then the
+//               epilogue: O / l rounded to the input dtype, staged in swizzled smem and written
+//               with TMA tile stores (one per warp and 64-column slab).
+// Partials are stored in TILE ORDER (contiguous 128-row slabs) with their (m, l) statistics;
+// no atomics, no cross-block state.
 //
-// Reduce kernel (replaces reduce_kernel, :139-281): one warp per (token, head) merges the
-// <= T partials with 128-bit loads:  M = max m_s, w_s = exp2(m_s - M),
-// o = sum w_s O_s / sum w_s l_s,  lse = M + log2 sum w_s l_s   (log2 units, as the reference).
+// Reduce kernel (replaces reduce_kernel, :139-281): one warp per (token, head) looks up the
+// <= T partial rows through the `pos` map and merges them:  M = max m_s,
+// w_s = exp2(m_s - M),  o = sum w_s O_s / sum w_s l_s,  lse = M + log2 sum w_s l_s  (log2 units;
+// O_s is the unnormalised partial, l_s its row sum).
 #include "sel_launch.cuh"
+#include <cstdlib>
 
 namespace fsa {
 
 template <typename ET>
 struct SelFwdParams {
-    const ET* q;
-    int64_t q_sn, q_sh;      // element strides of q[N, Hq, D]
     SelShape s;
     SelIndex ix;
     float scale_log2;        // softmax scale * log2(e)
-    float* opart;            // [N, Hq, T, D] fp32
-    float2* ml;              // [N, Hq, T]
-};
-
-template <int D, int BK>
-struct SelFwdSmem {
-    static constexpr int kK = BK * D * 2;
-    static constexpr int kV = BK * D * 2;
-    static constexpr int kQ = kTileRows * D * 2;
-    static constexpr int kBytes = kK + kV + kQ + 1024;   // + alignment slack
+    int run;                 // tiles per scheduling run (see TileSchedule)
+    int dbg;                 // debug builds only: bit 0 skip Q copies, bit 1 skip partial stores
+    ET* opart;               // [max_tiles * 128, D]  unnormalised partial outputs, tile order
+    float2* ml;              // [max_tiles * 128]     (row max in log2 units, row sum)
 };
 
 __host__ __device__ constexpr uint32_t tmem_cols_pow2(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
 
+template <int D, int BK>
+struct SelFwdCfg {
+    static constexpr int kQ = kTileRows * D * 2;
+    static constexpr int kKV = 2 * BK * D * 2;         // K then V
+    static constexpr int kOS = kTileRows * D * 2;      // output staging per softmax warpgroup (input dtype)
+    static constexpr int kTail = 2560;                 // barriers, TMEM slot, row-offset table
+    static constexpr int kMax = 227 * 1024;
+    static constexpr int NKV = (2 * kQ + 2 * kKV + 2 * kOS + kTail <= kMax) ? 2 : 1;    // K/V stages
+    static constexpr int NQ = (3 * kQ + NKV * kKV + 2 * kOS + kTail <= kMax) ? 3 : 2;   // Q stages
+    static constexpr int kBytes = NQ * kQ + NKV * kKV + 2 * kOS + kTail;
+    static constexpr int NS = (4 * BK + 2 * D <= 512) ? 4 : 2;   // S buffers (BK columns each); two per softmax group when they fit
+    static constexpr int cS = 0;
+    static constexpr int cO = NS * BK;                 // two O buffers of D columns, one per softmax group
+    static constexpr uint32_t kCols = tmem_cols_pow2(NS * BK + 2 * D);
+};
+
+// warps: 0..3 gather loaders | 4 issues S = Q K^T | 5 issues O = P V | 6..9 softmax group 0 | 10..13 softmax group 1
+// (any four consecutive warps cover the four TMEM lane quarters, warp % 4)
+constexpr int kFwdThreads = 448;
+constexpr int kFwdLoaders = 128;
+
+// Optional cycle accounting per role (debug builds only): FSA_TIMING defines a global table
+// [gridDim.x][32] of accumulated clock64() deltas.
+#ifdef FSA_TIMING
+__device__ unsigned long long g_fwd_timing[512 * 32];
+#define T_DECL unsigned long long _t0 = 0, _acc[12] = {0,0,0,0,0,0,0,0,0,0,0,0}
+#define T_TIC _t0 = clock64()
+#define T_TOC(i) do { unsigned long long _t1 = clock64(); _acc[i] += _t1 - _t0; _t0 = _t1; } while (0)
+#define T_DUMP(base, n) do { for (int _i = 0; _i < (n); ++_i) g_fwd_timing[blockIdx.x * 32 + (base) + _i] = _acc[_i]; } while (0)
+#define TR(role, k, ev) do { if (blockIdx.x == 3 && (k) >= 64 && (k) < 96) g_fwd_trace[((role) * 32 + ((k) - 64)) * 4 + (ev)] = clock64(); } while (0)
+__device__ long long g_fwd_trace[6 * 32 * 4];
+#else
+#define TR(role, k, ev)
+#define T_DECL
+#define T_TIC
+#define T_TOC(i)
+#define T_DUMP(base, n)
+#endif
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 template <int D, int BK, typename ET>
-__global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p, const __grid_constant__ CUtensorMap kmap,
-                                                      const __grid_constant__ CUtensorMap vmap) {
+__global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParams<ET> p, const ET* __restrict__ q, int64_t q_sn,
+                                                               int64_t q_sh, const __grid_constant__ CUtensorMap kmap,
+                                                               const __grid_constant__ CUtensorMap vmap,
+                                                               const __grid_constant__ CUtensorMap omap) {
+    using C = SelFwdCfg<D, BK>;
+    static_assert(C::NS * BK + 2 * D <= 512, "TMEM budget");
+    static_assert(C::kBytes <= 227 * 1024, "smem budget");
+    // The kernel uses no static shared memory: the dynamic region starts 1024-byte aligned, which
+    // the swizzled tiles need, and every byte of the 227 KB is budgeted (checked below).
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sKV = sQ + C::NQ * C::kQ;
+    uint8_t* sOS = sKV + C::NKV * C::kKV;
+    uint8_t* tail = sOS + 2 * C::kOS;
+    long long (*s_off)[kTileRows] = reinterpret_cast<long long (*)[kTileRows]>(tail);   // [2][128] element offset of every
+                                                                                        // tile row in q (-1: padding)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * kTileRows * 8);
+    uint64_t* q_full = bars;                 // [NQ]
+    uint64_t* q_empty = q_full + C::NQ;      // [NQ]
+    uint64_t* kv_full = q_empty + C::NQ;     // [NKV]
+    uint64_t* kv_empty = kv_full + C::NKV;   // [NKV]
+    uint64_t* s_full = kv_empty + C::NKV;    // [NS]
+    uint64_t* s_empty = s_full + C::NS;      // [NS]
+    uint64_t* p_full = s_empty + C::NS;      // [NS]
+    uint64_t* o_full = p_full + C::NS;       // [2]
+    uint64_t* o_empty = o_full + 2;          // [2]
+    uint64_t* meta_full = o_empty + 2;       // [NQ] "new block" flag of the tile in Q stage i is valid
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(meta_full + C::NQ);
+    int* s_nb = reinterpret_cast<int*>(meta_full + C::NQ) + 2;   // [NQ]
+    static_assert(2 * kTileRows * 8 + (3 * C::NQ + 2 * C::NKV + 3 * C::NS + 4) * 8 + 8 + 4 * C::NQ <= C::kTail, "tail budget");
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const SelShape& s = p.s;
+    int* status = p.ix.header;
+    if (smem_u32(smem) & 1023u) {   // never expected; the tiles would be mis-swizzled
+        if (tid == 0) atomicMax(status, (int)kStatusBadIndex);
+        return;
+    }
+
+    if (tid == 0) {
+        for (int i = 0; i < C::NQ; ++i) { mbar_init(&q_full[i], kFwdLoaders); mbar_init(&q_empty[i], 1); mbar_init(&meta_full[i], 1); }
+        for (int i = 0; i < C::NKV; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        for (int i = 0; i < C::NS; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 1); mbar_init(&p_full[i], 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 128); }
+        mbar_init_fence();
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        tma_prefetch_desc(&omap);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, C::kCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = tmem_slot;
+
+    const TileSchedule sched(p.ix.header[1], p.run);
+    const int nloc = sched.nloc;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ loaders (128 threads)
+        // Thread t looks up the token of tile row t, and copies 16-byte chunk (t % CPR) of the rows
+        // t / CPR, t / CPR + RSTEP, ... (a half-warp covers one 256-byte row).
+        T_DECL;
+        const int t = tid;
+        bool ok = true;
+        int kvn = -1;
+        // row t of every tile: head of the group and entry slot are thread constants
+        const int g0 = t / s.TPT, e0 = t - g0 * s.TPT;
+        const bool row_exists = g0 < s.G;
+        // Tile records and entries are addressed by the tile index alone, so they are fetched two
+        // tiles ahead of their use.
+        TileInfo m1{0, 0, 0, -1}, m2{0, 0, 0, -1};
+        uint32_t ent1 = 0xFFFFFFFFu, ent2 = 0xFFFFFFFFu;
+        auto fetch = [&](int k, TileInfo& ti, uint32_t& ent) {
+            const int j = sched.tile(k);
+            ti = load_tile(p.ix, j);
+            ent = 0xFFFFFFFFu;
+            if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e0);
+        };
+        if (nloc > 0) fetch(0, m1, ent1);
+        if (nloc > 1) fetch(1, m2, ent2);
+        int prev_hg = -1;
+        // copy schedule of this thread: chunk c of rows rbase, rbase + RSTEP, ...
+        constexpr int CPR = D / 8;                         // 16-byte chunks per row
+        constexpr int RSTEP = kFwdLoaders / CPR;           // rows advanced per iteration
+        const int cchunk = t % CPR, rbase = t / CPR;
+        const uint32_t slab_off = (uint32_t)(cchunk >> 3) * (kTileRows * 128);
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int qs = k % C::NQ;
+            const TileInfo cur = m1;
+            const uint32_t c_ent = ent1;
+            const int c_h = cur.h, c_row0 = cur.row0;
+            const bool c_nb = cur.hg != prev_hg;
+            prev_hg = cur.hg;
+            m1 = m2; ent1 = ent2;
+            T_TIC;
+            if (k + 2 < nloc) fetch(k + 2, m2, ent2);
+            T_TOC(0);
+            // the Q stage (and its flag slot) is free once the S MMA of the tile that used it is done
+            ok = mbar_wait(&q_empty[qs], ((k / C::NQ) & 1) ^ 1, status) && ok;
+            T_TOC(1);
+            if (t == 0) TR(0, k, 0);
+            if (t == 0) {
+                // tell the MMA thread whether this tile starts a new K/V block (it walks no index itself)
+                s_nb[qs] = c_nb ? 1 : 0;
+                mbar_arrive(&meta_full[qs]);
+            }
+            if (c_nb) {
+                ++kvn;
+                if (t == 0) {
+                    const int ks = kvn % C::NKV;
+                    ok = mbar_wait(&kv_empty[ks], ((kvn / C::NKV) & 1) ^ 1, status) && ok;
+                    mbar_expect_tx(&kv_full[ks], (uint32_t)C::kKV);
+                    uint8_t* dK = sKV + ks * C::kKV;
+                    uint8_t* dV = dK + BK * D * 2;
+#pragma unroll
+                    for (int b = 0; b < D / 64; ++b) {
+                        tma_load_2d(smem_u32(dK + b * BK * 128), &kmap, c_h * D + b * 64, c_row0, &kv_full[ks]);
+                        tma_load_2d(smem_u32(dV + b * BK * 128), &vmap, c_h * D + b * 64, c_row0, &kv_full[ks]);
+                    }
+                }
+            }
+            s_off[k & 1][t] = c_ent != 0xFFFFFFFFu ? (long long)(c_ent >> kSlotBits) * q_sn + (long long)(c_h * s.G + g0) * q_sh : -1ll;
+            T_TOC(2);
+            named_bar_sync(1, kFwdLoaders);
+            {
+                const uint32_t dstq = smem_u32(sQ + qs * C::kQ) + slab_off;
+                const long long* offs = s_off[k & 1];
+#ifdef FSA_TIMING
+                if (!(p.dbg & 1))
+#endif
+                {
+                    // all row offsets first (the copies are asm statements the loads cannot move across)
+                    long long off[kTileRows / RSTEP];
+#pragma unroll
+                    for (int it = 0; it < kTileRows / RSTEP; ++it) off[it] = offs[rbase + it * RSTEP];
+#pragma unroll
+                    for (int it = 0; it < kTileRows / RSTEP; ++it) {
+                        const int r = rbase + it * RSTEP;
+                        const bool valid = off[it] >= 0;
+                        cp_async16(dstq + sw128_chunk_off(r, cchunk & 7), q + (valid ? off[it] : 0) + cchunk * 8, valid);
+                    }
+                }
+            }
+            // arrives on q_full when this thread's copies have landed; nobody waits here, so the
+            // loader never holds a finished tile back behind a later wait
+            cp_async_mbar_arrive_noinc(&q_full[qs]);
+            T_TOC(3);
+            if (t == 0) TR(0, k, 1);
+        }
+        if (t == 0) T_DUMP(0, 5);
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
+        // The whole warp walks the loop (uniform control flow); one elected lane issues.  S and P V
+        // are issued by different warps so that neither waits behind the other's barriers.
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
+        // descriptor words: constant high word (SBO 1024, version, swizzle), low words of the bases
+        constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+        const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16);
+        const uint32_t k_lo = umma_desc_lo(smem_u32(sKV), 16);
+        int kvn = -1;
+        bool ok = true;
+        T_DECL;
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int qs = k % C::NQ, sbuf = k % C::NS;
+            T_TIC;
+            // "does this tile start a new K/V block": published by the loader with the Q stage
+            ok = mbar_wait(&meta_full[qs], (k / C::NQ) & 1, status) && ok;
+            if (s_nb[qs] != 0) {
+                ++kvn;
+                ok = mbar_wait(&kv_full[kvn % C::NKV], (kvn / C::NKV) & 1, status) && ok;
+            }
+            T_TOC(1);
+            if (lane == 0) TR(1, k, 0);
+            ok = mbar_wait(&q_full[qs], (k / C::NQ) & 1, status) && ok;
+            fence_async_smem();   // the Q rows were written by cp.async (generic proxy)
+            T_TOC(2);
+            if (lane == 0) TR(1, k, 1);
+            ok = mbar_wait(&s_empty[sbuf], ((k / C::NS) & 1) ^ 1, status) && ok;
+            T_TOC(3);
+            if (lane == 0) TR(1, k, 2);
+            tc_fence_after();
+            const uint32_t a_lo = q_lo + (uint32_t)(qs * (C::kQ >> 4));
+            const uint32_t b_lo = k_lo + (uint32_t)((kvn % C::NKV) * (C::kKV >> 4));
+            const uint32_t d_s = tbase + C::cS + sbuf * BK;
+            if (leader) {
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    // k-step ks: 64-column slab ks / 4, 32-byte step (ks % 4) inside the 128-byte swizzle row
+                    constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (BK * 128) >> 4;
+                    umma_ss(d_s, umma_desc_pack(a_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                            umma_desc_pack(b_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                }
+                umma_commit(&q_empty[qs]);
+                umma_commit(&s_full[sbuf]);
+            }
+            __syncwarp();
+            T_TOC(4);
+            if (lane == 0) TR(1, k, 3);
+        }
+        if (lane == 0) T_DUMP(8, 5);
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer 2: O = P V
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_o = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);
+        constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+        const uint32_t v_lo = umma_desc_lo(smem_u32(sKV + BK * D * 2), BK * 128);   // MN-major: LBO = slab stride
+        int kvn = -1;
+        bool ok = true;
+        T_DECL;
+        // block ids of the CTA's tiles, fetched two tiles ahead (needed to know when a K/V stage is done)
+        int hg0 = -1, hg1 = -1, hg2 = -1;
+        if (nloc > 0) hg1 = load_tile(p.ix, sched.tile(0)).hg;
+        if (nloc > 1) hg2 = load_tile(p.ix, sched.tile(1)).hg;
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int sb = k & 1, sbuf = k % C::NS;
+            const int prev_hg = hg0;
+            hg0 = hg1; hg1 = hg2;
+            if (k + 2 < nloc) hg2 = load_tile(p.ix, sched.tile(k + 2)).hg;
+            if (hg0 != prev_hg) ++kvn;
+            const bool last_of_block = (k + 1 >= nloc) || (hg1 != hg0);
+            const int kv_cur = kvn % C::NKV;
+            T_TIC;
+            ok = mbar_wait(&p_full[sbuf], (k / C::NS) & 1, status) && ok;
+            T_TOC(5);
+            if (lane == 0) TR(2, k, 0);
+            ok = mbar_wait(&o_empty[sb], ((k >> 1) & 1) ^ 1, status) && ok;
+            T_TOC(6);
+            if (lane == 0) TR(2, k, 1);
+            tc_fence_after();
+            const uint32_t b_lo = v_lo + (uint32_t)(kv_cur * (C::kKV >> 4));
+            const uint32_t d_o = tbase + C::cO + sb * D, a_p = tbase + C::cS + sbuf * BK;
+            if (leader) {
+#pragma unroll
+                for (int ks = 0; ks < BK / 16; ++ks)
+                    umma_ts(d_o, a_p + ks * 8, umma_desc_pack(b_lo + ks * (2048 >> 4), hi_1024), idesc_o, ks > 0);
+                umma_commit(&o_full[sb]);
+                umma_commit(&s_empty[sbuf]);
+                if (last_of_block) umma_commit(&kv_empty[kv_cur]);
+            }
+            __syncwarp();
+            T_TOC(7);
+            if (lane == 0) TR(2, k, 2);
+        }
+#ifdef FSA_TIMING
+        if (lane == 0) for (int i = 5; i < 8; ++i) g_fwd_timing[blockIdx.x * 32 + 8 + i] = _acc[i];
+#endif
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue
+        // Group sb (warps 6..9 / 10..13) owns the CTA's tiles with odd / even local index, hence TMEM
+        // buffers S[sb], O[sb] and its own staging area.  One row per thread.
+        const int sb = (warp - 6) >> 2;
+        const int quarter = warp & 3;                 // TMEM lane quarter this warp may access
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const int g = r / s.TPT;
+        const int e = r - g * s.TPT;
+        // this warp's 32 staged rows: D/64 slabs of 32 rows x 128 bytes, 128-byte swizzle
+        uint8_t* my_os = sOS + sb * C::kOS + quarter * (32 * D * 2);
+        const uint32_t tS0 = tbase + lane_off + C::cS;
+        const uint32_t tO = tbase + lane_off + C::cO + sb * D;
+        bool ok = true;
+        T_DECL;
+        // prefetched entry of this thread's row in the group's next tile
+        const bool row_exists = g < s.G;
+        uint32_t n_ent = 0xFFFFFFFFu; int n_row0 = 0;
+        auto prefetch = [&](int j) {
+            n_row0 = load_tile(p.ix, j).row0;
+            n_ent = 0xFFFFFFFFu;
+            if (row_exists) n_ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);   // consumed one iteration later
+        };
+        bool have_prev = false, prev_valid = false;
+        int prev_j = 0, prev_u = 0;
+        float prev_m = 0.f, prev_l = 0.f;
+        // O / l -> staging -> TMA store, for the tile (prev_j) whose softmax ran one iteration ago
+        auto epilogue = [&]() {
+            T_TIC;
+            ok = mbar_wait(&o_full[sb], prev_u & 1, status) && ok;
+            T_TOC(3);
+            if (quarter == 2 && lane == 0) TR(3, prev_u * 2 + sb, 2);
+            tc_fence_after();
+            if (lane == 0) bulk_wait_read0();   // previous store of this warp has read its staging rows
+            __syncwarp();
+            T_TOC(4);
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tO + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    // unnormalised O (its row sum l travels in the statistics): rounding to a floating-point
+                    // format is scale-free, so dividing first would not make the partial more accurate
+                    uint4 x;
+                    x.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                    x.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                    x.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                    x.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                    const int chunk = (c0 >> 3) + q4;     // 16-byte chunk of the row
+                    *reinterpret_cast<uint4*>(my_os + (chunk >> 3) * (32 * 128) + sw128_chunk_off(lane, chunk & 7)) = x;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&o_empty[sb]);
+            if (prev_valid) p.ml[(int64_t)prev_j * kTileRows + r] = make_float2(prev_m, prev_l);
+            fence_async_smem();
+            __syncwarp();
+#ifdef FSA_TIMING
+            if (!(p.dbg & 2))
+#endif
+            if (lane == 0) {
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b)
+                    tma_store_2d(&omap, b * 64, prev_j * kTileRows + quarter * 32, smem_u32(my_os + b * (32 * 128)));
+                bulk_commit();
+            }
+            T_TOC(5);
+            if (quarter == 2 && lane == 0) TR(3, prev_u * 2 + sb, 3);
+        };
+        if (sb < nloc) prefetch(sched.tile(sb));
+        for (int k = sb; k < nloc && ok; k += 2) {
+            const int j = sched.tile(k);
+            const int u = k >> 1;                     // use count of this group's O buffer
+            const int sbuf = k % C::NS;
+            const uint32_t tS = tS0 + sbuf * BK;
+            const bool row_valid = n_ent != 0xFFFFFFFFu;
+            const int tok = (int)(n_ent >> kSlotBits);
+            const int nvis = row_valid ? min(BK, tok - n_row0 + 1) : BK;   // causal: key row0 + c <= tok
+            T_TIC;
+            if (k + 2 < nloc) prefetch(sched.tile(k + 2));
+            T_TOC(0);
+            ok = mbar_wait(&s_full[sbuf], (k / C::NS) & 1, status) && ok;
+            T_TOC(1);
+            if (quarter == 2 && lane == 0) TR(3, k, 0);
+            tc_fence_after();
+            float m, l;
+            if constexpr (BK <= 64) {
+                // whole row in registers: one TMEM read
+                uint32_t v[BK];
+                {
+                    uint32_t (&v0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[0]);
+                    tmem_ld32(tS, v0);
+                    if constexpr (BK == 64) {
+                        uint32_t (&v1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[32]);
+                        tmem_ld32(tS + 32, v1);
+                    }
+                    tmem_ld_wait();
+                }
+                if (nvis < BK) {
+#pragma unroll
+                    for (int i = 0; i < BK; ++i)
+                        if (i >= nvis) v[i] = 0xff800000u;   // -inf: exp2 gives exactly 0
+                }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < BK; i += 4) {
+                    mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
+                    mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
+                    mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
+                    mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
+                }
+                m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+                float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[BK / 2];
+#pragma unroll
+                for (int i = 0; i < BK; i += 4) {
+                    float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m));
+                    float p2 = ex2_approx(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m));
+                    float p3 = ex2_approx(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m));
+                    ls[0] += p0; ls[1] += p1; ls[2] += p2; ls[3] += p3;
+                    pk[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                    pk[(i >> 1) + 1] = ElemTraits<ET>::pack2(p2, p3);
+                }
+                l = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                if constexpr (BK == 64) {
+                    tmem_st32(tS, *reinterpret_cast<uint32_t (*)[32]>(&pk[0]));
+                } else {
+                    tmem_st16(tS, *reinterpret_cast<uint32_t (*)[16]>(&pk[0]));
+                }
+            } else {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c0 = 0; c0 < BK; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tS + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c0 + i < nvis) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+                m = mx * p.scale_log2;
+                l = 0.f;
+#pragma unroll
+                for (int c0 = 0; c0 < BK; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tS + c0, v);
+                    tmem_ld_wait();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float p0 = (c0 + i < nvis) ? ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m)) : 0.f;
+                        float p1 = (c0 + i + 1 < nvis) ? ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m)) : 0.f;
+                        l += p0 + p1;
+                        pk[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                    }
+                    tmem_st16(tS + (c0 >> 1), pk);
+                }
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_full[sbuf]);
+            T_TOC(2);
+            if (quarter == 2 && lane == 0) TR(3, k, 1);
+
+            // the epilogue of this group's previous tile runs now: its P V has had a whole softmax
+            // to finish, so the wait below is normally free
+            if (have_prev) epilogue();
+            have_prev = true;
+            prev_j = j; prev_u = u; prev_m = m; prev_l = l; prev_valid = row_valid;
+        }
+        if (have_prev && ok) epilogue();
+        if (lane == 0) bulk_wait0();
+        if (warp == 6 && lane == 0) T_DUMP(16, 6);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, C::kCols);
+}
+
+// ------------------------------------------------------------------------------------------
+// Unpipelined variant (one tile at a time, 128 threads) for the shapes whose tiles do not fit
+// the staged layout above (head_dim 256, 256-key blocks).  Same partial layout.
+template <int D, int BK>
+struct SelFwdSimpleSmem {
+    static constexpr int kK = BK * D * 2;
+    static constexpr int kQ = kTileRows * D * 2;
+    static constexpr int kBytes = 2 * kK + kQ + 1024;
+};
+
+template <int D, int BK, typename ET>
+__global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> p, const ET* __restrict__ q, int64_t q_sn,
+                                                        int64_t q_sh, const __grid_constant__ CUtensorMap kmap,
+                                                        const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sK = smem;
-    uint8_t* sV = sK + SelFwdSmem<D, BK>::kK;
-    uint8_t* sQ = sV + SelFwdSmem<D, BK>::kV;
+    uint8_t* sV = sK + SelFwdSimpleSmem<D, BK>::kK;
+    uint8_t* sQ = sV + SelFwdSimpleSmem<D, BK>::kK;
     __shared__ uint64_t bar_kv, bar_s, bar_o;
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t s_ent[kTileRows];
@@ -54,76 +546,50 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
     const int tid = threadIdx.x, warp = tid >> 5;
     const SelShape& s = p.s;
     int* status = p.ix.header;
-
     if (tid == 0) {
         mbar_init(&bar_kv, 1);
         mbar_init(&bar_s, 1);
         mbar_init(&bar_o, 1);
         mbar_init_fence();
-        tma_prefetch_desc(&kmap);
-        tma_prefetch_desc(&vmap);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, kCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = tmem_slot;
-    const uint32_t tS = tbase;            // S (fp32, BK cols); P (packed 16-bit, BK/2 cols) aliases it
-    const uint32_t tO = tbase + BK;       // O (fp32, D cols)
+    const uint32_t tS = tbase, tO = tbase + BK;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-
-    const int HG = s.Hk * s.NBmax;
     const int total = p.ix.header[1];
     const int per = (total + gridDim.x - 1) / gridDim.x;
-    const int begin = blockIdx.x * per;
+    const int begin = min(total, (int)blockIdx.x * per);
     const int end = min(total, begin + per);
-
     constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
     constexpr uint32_t idesc_o = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);
-
-    int hg = -1, hg_end = 0, hg_begin = 0;
+    TileWalker w(p.ix, s);
     uint32_t kv_loads = 0;
     bool ok = true;
     int it = 0;
     for (int item = begin; item < end && ok; ++item, ++it) {
-        bool new_kv = false;
-        if (hg < 0 || item >= hg_end) {
-            hg = upper_seg(p.ix.tile_off, HG, item);
-            hg_begin = p.ix.tile_off[hg];
-            hg_end = p.ix.tile_off[hg + 1];
-            new_kv = true;
-        }
-        const int h = hg / s.NBmax;
-        const int gb = hg - h * s.NBmax;
-        const int row0 = p.ix.row0[gb];
-        const int cnt = p.ix.counts[hg];
-        const int e0 = (item - hg_begin) * s.TPT;
-        const int ne = min(s.TPT, cnt - e0);
-        const int64_t ebase = (int64_t)p.ix.blk_off[hg] + e0;
-
-        // ---- stage 1: entries -> smem; K/V tile by TMA when the block changes
-        if (tid < s.TPT) s_ent[tid] = tid < ne ? p.ix.entries[ebase + tid] : 0xFFFFFFFFu;
+        const bool new_kv = w.seek(item);
+        if (tid < s.TPT) s_ent[tid] = tid < w.ne ? p.ix.entries[w.ebase + tid] : 0u;
         if (new_kv && tid == 0) {
             mbar_expect_tx(&bar_kv, (uint32_t)(2 * BK * D * 2));
 #pragma unroll
             for (int b = 0; b < D / 64; ++b) {
-                tma_load_2d(smem_u32(sK + b * BK * 128), &kmap, h * D + b * 64, row0, &bar_kv);
-                tma_load_2d(smem_u32(sV + b * BK * 128), &vmap, h * D + b * 64, row0, &bar_kv);
+                tma_load_2d(smem_u32(sK + b * BK * 128), &kmap, w.h * D + b * 64, w.row0, &bar_kv);
+                tma_load_2d(smem_u32(sV + b * BK * 128), &vmap, w.h * D + b * 64, w.row0, &bar_kv);
             }
         }
         __syncthreads();
-
-        // ---- stage 2: gather Q rows (row r = entry r / G, head r % G)
         {
-            constexpr int CPR = D / 8;   // 16-byte chunks per row
+            constexpr int CPR = D / 8;
 #pragma unroll 4
             for (int i = tid; i < kTileRows * CPR; i += 128) {
                 int r = i / CPR, c = i % CPR;
-                int e = r / s.G, g = r - e * s.G;
-                bool valid = e < ne;
-                uint32_t ent = valid ? s_ent[e] : 0u;
-                int64_t n = ent >> kSlotBits;
-                const ET* src = p.q + n * p.q_sn + (int64_t)(h * s.G + g) * p.q_sh + c * 8;
+                int g = r / s.TPT, e = r - g * s.TPT;
+                bool valid = g < s.G && e < w.ne;
+                int64_t n = valid ? (s_ent[e] >> kSlotBits) : 0;
+                const ET* src = q + n * q_sn + (int64_t)(w.h * s.G + (valid ? g : 0)) * q_sh + c * 8;
                 uint32_t dst = smem_u32(sQ + (c >> 3) * (kTileRows * 128)) + sw128_chunk_off(r, c & 7);
                 cp_async16(dst, src, valid);
             }
@@ -133,12 +599,8 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
         }
         tc_fence_before();
         __syncthreads();
-
-        // ---- stage 3: S = Q K^T
         if (tid == 0) {
-            if (new_kv) {
-                ok = mbar_wait(&bar_kv, kv_loads & 1, status);
-            }
+            if (new_kv) ok = mbar_wait(&bar_kv, kv_loads & 1, status);
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
@@ -151,17 +613,13 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
         if (new_kv) ++kv_loads;
         ok = mbar_wait(&bar_s, it & 1, status) && ok;
         tc_fence_after();
-
-        // ---- stage 4: row softmax statistics, P -> TMEM
         const int r = tid;
-        const int e = r / s.G;
-        const bool row_valid = e < ne;
-        const uint32_t ent = row_valid ? s_ent[e] : 0u;
-        const int tok = (int)(ent >> kSlotBits);
-        const int slot = (int)(ent & (kMaxTopk - 1));
-        const int nvis = row_valid ? min(BK, tok - row0 + 1) : BK;   // causal: key row0 + j <= tok
+        const int g = r / s.TPT, e = r - g * s.TPT;
+        const bool row_valid = g < s.G && e < w.ne;
+        const int tok = row_valid ? (int)(s_ent[e] >> kSlotBits) : 0;
+        const int nvis = row_valid ? min(BK, tok - w.row0 + 1) : BK;
         float mx = -INFINITY;
-#pragma unroll
+#pragma unroll 2
         for (int c0 = 0; c0 < BK; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tS + lane_off + c0, v);
@@ -172,7 +630,7 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
         }
         const float m = mx * p.scale_log2;
         float l = 0.f;
-#pragma unroll
+#pragma unroll 2
         for (int c0 = 0; c0 < BK; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tS + lane_off + c0, v);
@@ -190,8 +648,6 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
         tmem_st_wait();
         tc_fence_before();
         __syncthreads();
-
-        // ---- stage 5: O = P V   (P from TMEM, V MN-major from smem)
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
@@ -203,28 +659,29 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
         }
         ok = mbar_wait(&bar_o, it & 1, status) && ok;
         tc_fence_after();
-
-        // ---- stage 6: partial O and (m, l) -> global, indexed by (token, head, slot)
         {
-            const int hq = h * s.G + (r - e * s.G);
-            const int64_t prow = ((int64_t)tok * s.Hq + hq) * s.T + slot;
-            if (row_valid) p.ml[prow] = make_float2(m, l);
-            float4* dst = reinterpret_cast<float4*>(p.opart + prow * D);
-#pragma unroll
+            const int64_t grow = (int64_t)item * kTileRows + r;
+            if (row_valid) p.ml[grow] = make_float2(m, l);
+            uint4* dst = reinterpret_cast<uint4*>(p.opart + grow * D);
+#pragma unroll 2
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tO + lane_off + c0, v);
                 tmem_ld_wait();
                 if (row_valid) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        dst[(c0 >> 2) + i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                         __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 u;
+                        u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                        u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                        u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                        u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                        dst[(c0 >> 3) + q4] = u;
+                    }
                 }
             }
         }
         tc_fence_before();
-        // make every thread see the same `ok` so the loop exits together
         ok = __syncthreads_and(ok);
     }
     tc_fence_before();
@@ -234,26 +691,33 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_main(const SelFwdParams<ET> p,
 
 // ------------------------------------------------------------------------------------------
 template <int D, typename ET>
-__global__ void __launch_bounds__(256) sel_fwd_reduce(const float* __restrict__ opart, const float2* __restrict__ ml,
-                                                      const int* __restrict__ topk_idx, const int* __restrict__ cu,
-                                                      SelShape s, ET* __restrict__ o, int64_t o_sn, int64_t o_sh,
-                                                      float* __restrict__ lse) {
+__global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opart, const float2* __restrict__ ml,
+                                                      const int* __restrict__ pos, SelShape s, ET* __restrict__ o,
+                                                      int64_t o_sn, int64_t o_sh, float* __restrict__ lse) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // n * Hq + hq
     if (row >= s.N * s.Hq) return;
     const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);
-    const int h = hq / s.G;
-    const int* idrow = topk_idx + ((int64_t)h * s.N + n) * s.T;
-    // lane handles slots lane and lane + 32
+    const int h = hq / s.G, g = hq - h * s.G;
+    const int* prow = pos + ((int64_t)h * s.N + n) * s.T;
+    // lane handles slots lane and lane + 32: partial row index and statistics
+    int64_t pr0 = -1, pr1 = -1;
     float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
-    int r0;
-    if (lane < s.T && entry_block(cu, s.B, s.BK, n, __ldg(idrow + lane), &r0) >= 0) {
-        float2 v = ml[row * s.T + lane];
-        m0 = v.x; l0 = v.y;
+    if (lane < s.T) {
+        int ps = __ldg(prow + lane);
+        if (ps >= 0) {
+            pr0 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
+            float2 v = ml[pr0];
+            m0 = v.x; l0 = v.y;
+        }
     }
-    if (lane + 32 < s.T && entry_block(cu, s.B, s.BK, n, __ldg(idrow + lane + 32), &r0) >= 0) {
-        float2 v = ml[row * s.T + lane + 32];
-        m1 = v.x; l1 = v.y;
+    if (lane + 32 < s.T) {
+        int ps = __ldg(prow + lane + 32);
+        if (ps >= 0) {
+            pr1 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
+            float2 v = ml[pr1];
+            m1 = v.x; l1 = v.y;
+        }
     }
     float M = fmaxf(m0, m1);
 #pragma unroll
@@ -264,28 +728,30 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const float* __restrict__ 
 #pragma unroll
     for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
 
-    constexpr int V = D / 32;   // floats per lane
+    constexpr int V = D / 32;   // elements per lane
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    const float* base = opart + row * s.T * D + lane * V;
     for (int sl = 0; sl < s.T; ++sl) {
-        float w = __shfl_sync(0xffffffffu, sl < 32 ? w0 : w1, sl & 31);
+        const float w = __shfl_sync(0xffffffffu, sl < 32 ? w0 : w1, sl & 31);
+        const long long pr = __shfl_sync(0xffffffffu, (long long)(sl < 32 ? pr0 : pr1), sl & 31);
         if (w == 0.f) continue;
-        const float* src = base + (int64_t)sl * D;
-        if constexpr (V == 4) {
-            float4 x = *reinterpret_cast<const float4*>(src);
+        const ET* src = opart + pr * D + lane * V;
+        if constexpr (V == 2) {
+            float2 x = ElemTraits<ET>::unpack2(*reinterpret_cast<const uint32_t*>(src));
             acc[0] = fmaf(w, x.x, acc[0]); acc[1] = fmaf(w, x.y, acc[1]);
-            acc[2] = fmaf(w, x.z, acc[2]); acc[3] = fmaf(w, x.w, acc[3]);
-        } else if constexpr (V == 2) {
-            float2 x = *reinterpret_cast<const float2*>(src);
+        } else if constexpr (V == 4) {
+            uint2 u = *reinterpret_cast<const uint2*>(src);
+            float2 x = ElemTraits<ET>::unpack2(u.x), y = ElemTraits<ET>::unpack2(u.y);
             acc[0] = fmaf(w, x.x, acc[0]); acc[1] = fmaf(w, x.y, acc[1]);
+            acc[2] = fmaf(w, y.x, acc[2]); acc[3] = fmaf(w, y.y, acc[3]);
         } else {
+            uint4 u = *reinterpret_cast<const uint4*>(src);
+            const uint32_t* uu = &u.x;
 #pragma unroll
-            for (int i = 0; i < V; i += 4) {
-                float4 x = *reinterpret_cast<const float4*>(src + i);
-                acc[i] = fmaf(w, x.x, acc[i]); acc[i + 1] = fmaf(w, x.y, acc[i + 1]);
-                acc[i + 2] = fmaf(w, x.z, acc[i + 2]); acc[i + 3] = fmaf(w, x.w, acc[i + 3]);
+            for (int i = 0; i < 4; ++i) {
+                float2 x = ElemTraits<ET>::unpack2(uu[i]);
+                acc[2 * i] = fmaf(w, x.x, acc[2 * i]); acc[2 * i + 1] = fmaf(w, x.y, acc[2 * i + 1]);
             }
         }
     }
@@ -293,61 +759,77 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const float* __restrict__ 
     ET* dst = o + (int64_t)n * o_sn + (int64_t)hq * o_sh + lane * V;
     if constexpr (V == 2) {
         *reinterpret_cast<uint32_t*>(dst) = ElemTraits<ET>::pack2(acc[0] * inv, acc[1] * inv);
+    } else if constexpr (V == 4) {
+        uint2 u;
+        u.x = ElemTraits<ET>::pack2(acc[0] * inv, acc[1] * inv);
+        u.y = ElemTraits<ET>::pack2(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2*>(dst) = u;
     } else {
-#pragma unroll
-        for (int i = 0; i < V; i += 4) {
-            uint2 u;
-            u.x = ElemTraits<ET>::pack2(acc[i] * inv, acc[i + 1] * inv);
-            u.y = ElemTraits<ET>::pack2(acc[i + 2] * inv, acc[i + 3] * inv);
-            *reinterpret_cast<uint2*>(dst + i) = u;
-        }
+        uint4 u;
+        u.x = ElemTraits<ET>::pack2(acc[0] * inv, acc[1] * inv);
+        u.y = ElemTraits<ET>::pack2(acc[2] * inv, acc[3] * inv);
+        u.z = ElemTraits<ET>::pack2(acc[4] * inv, acc[5] * inv);
+        u.w = ElemTraits<ET>::pack2(acc[6] * inv, acc[7] * inv);
+        *reinterpret_cast<uint4*>(dst) = u;
     }
     if (lane == 0) lse[(int64_t)hq * s.N + n] = L > 0.f ? M + log2f(L) : -INFINITY;
 }
 
 // ------------------------------------------------------------------------------------------
 template <int D, int BK, typename ET>
-cudaError_t launch_sel_fwd(const SelFwdParams<ET>& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
-                           const int* topk_idx, const int* cu, ET* o, int64_t o_sn, int64_t o_sh, float* lse,
-                           int num_sms, cudaStream_t stream) {
-    auto kern = sel_fwd_main<D, BK, ET>;
-    constexpr int smem = SelFwdSmem<D, BK>::kBytes;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    constexpr int tmem_per_cta = (int)tmem_cols_pow2(BK + D);
-    int by_tmem = 512 / tmem_per_cta;
-    int by_smem = (227 * 1024) / (smem + 2048);
-    int per_sm = by_tmem < by_smem ? by_tmem : by_smem;
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 4) per_sm = 4;
-    prof_begin(0, stream);
-    kern<<<num_sms * per_sm, 128, smem, stream>>>(p, kmap, vmap);
-    prof_end(0, stream);
+static cudaError_t launch_sel_fwd(const SelFwdArgs& a, const SelShape& s, const SelIndex& ix, int num_sms,
+                                  cudaStream_t stream) {
+    SelFwdParams<ET> p;
+    p.s = s; p.ix = ix;
+    p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+    p.opart = (ET*)a.opart; p.ml = a.ml;
+    p.run = a.run > 0 ? a.run : 8;
+    p.dbg = 0;
+#ifdef FSA_TIMING
+    { const char* v = getenv("FSA_DBG"); p.dbg = v ? atoi(v) : 0; }
+#endif
+    cudaError_t e;
+    constexpr bool kPipelined = (D <= 128 && BK <= 128);
+    if (kPipelined && a.omap) {
+        if constexpr (kPipelined) {
+            auto kern = sel_fwd_main<D, BK, ET>;
+            constexpr int smem = SelFwdCfg<D, BK>::kBytes;
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return e;
+            prof_begin(0, stream);
+            kern<<<num_sms, kFwdThreads, smem, stream>>>(p, (const ET*)a.q, a.q_sn, a.q_sh, *a.kmap, *a.vmap, *a.omap);
+            prof_end(0, stream);
+        }
+    } else {
+        auto kern = sel_fwd_simple<D, BK, ET>;
+        constexpr int smem = SelFwdSimpleSmem<D, BK>::kBytes;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        constexpr int tmem_per_cta = (int)tmem_cols_pow2(BK + D);
+        int per_sm = 512 / tmem_per_cta;
+        int by_smem = (227 * 1024) / (smem + 2048);
+        if (by_smem < per_sm) per_sm = by_smem;
+        if (per_sm < 1) per_sm = 1;
+        prof_begin(0, stream);
+        kern<<<num_sms * per_sm, 128, smem, stream>>>(p, (const ET*)a.q, a.q_sn, a.q_sh, *a.kmap, *a.vmap);
+        prof_end(0, stream);
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    int64_t rows = p.s.N * p.s.Hq;
+    int64_t rows = s.N * s.Hq;
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(1, stream);
-        sel_fwd_reduce<D, ET><<<grid, 256, 0, stream>>>(p.opart, p.ml, topk_idx, cu, p.s, o, o_sn, o_sh, lse);
+        sel_fwd_reduce<D, ET><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
         prof_end(1, stream);
     }
     return cudaGetLastError();
 }
 
 template <typename ET>
-static cudaError_t dispatch_typed(const void* q, int64_t q_sn, int64_t q_sh, const SelShape& s, const SelIndex& ix,
-                                  float sm_scale, float* opart, float2* ml, const CUtensorMap& kmap,
-                                  const CUtensorMap& vmap, const int* topk_idx, const int* cu, void* o, int64_t o_sn,
-                                  int64_t o_sh, float* lse, int num_sms, cudaStream_t stream) {
-    SelFwdParams<ET> p;
-    p.q = (const ET*)q; p.q_sn = q_sn; p.q_sh = q_sh;
-    p.s = s; p.ix = ix;
-    p.scale_log2 = sm_scale * 1.4426950408889634f;
-    p.opart = opart; p.ml = ml;
-#define FSA_CASE(DD, BB)                                                                                         \
-    if (s.D == DD && s.BK == BB)                                                                                 \
-        return launch_sel_fwd<DD, BB, ET>(p, kmap, vmap, topk_idx, cu, (ET*)o, o_sn, o_sh, lse, num_sms, stream);
+static cudaError_t dispatch_typed(const SelFwdArgs& a, const SelShape& s, const SelIndex& ix, int num_sms, cudaStream_t stream) {
+#define FSA_CASE(DD, BB) \
+    if (s.D == DD && s.BK == BB) return launch_sel_fwd<DD, BB, ET>(a, s, ix, num_sms, stream);
     FSA_CASE(64, 32) FSA_CASE(64, 64) FSA_CASE(64, 128) FSA_CASE(64, 256)
     FSA_CASE(128, 32) FSA_CASE(128, 64) FSA_CASE(128, 128) FSA_CASE(128, 256)
     FSA_CASE(256, 32) FSA_CASE(256, 64) FSA_CASE(256, 128)
@@ -355,15 +837,19 @@ static cudaError_t dispatch_typed(const void* q, int64_t q_sn, int64_t q_sh, con
     return cudaErrorInvalidValue;
 }
 
-cudaError_t dispatch_sel_fwd(int dtype, const void* q, int64_t q_sn, int64_t q_sh, const SelShape& s,
-                             const SelIndex& ix, float sm_scale, float* opart, float2* ml, const CUtensorMap& kmap,
-                             const CUtensorMap& vmap, const int* topk_idx, const int* cu, void* o, int64_t o_sn,
-                             int64_t o_sh, float* lse, int num_sms, cudaStream_t stream) {
-    if (dtype == kBF16)
-        return dispatch_typed<__nv_bfloat16>(q, q_sn, q_sh, s, ix, sm_scale, opart, ml, kmap, vmap, topk_idx, cu, o, o_sn,
-                                             o_sh, lse, num_sms, stream);
-    return dispatch_typed<__half>(q, q_sn, q_sh, s, ix, sm_scale, opart, ml, kmap, vmap, topk_idx, cu, o, o_sn, o_sh, lse,
-                                  num_sms, stream);
+cudaError_t dispatch_sel_fwd(int dtype, const SelFwdArgs& a, const SelShape& s, const SelIndex& ix, int num_sms,
+                             cudaStream_t stream) {
+    if (dtype == kBF16) return dispatch_typed<__nv_bfloat16>(a, s, ix, num_sms, stream);
+    return dispatch_typed<__half>(a, s, ix, num_sms, stream);
 }
 
 }  // namespace fsa
+
+#ifdef FSA_TIMING
+extern "C" int fsa_debug_read_fwd_trace(long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, fsa::g_fwd_trace, (size_t)n * sizeof(long long));
+}
+extern "C" int fsa_debug_read_fwd_timing(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, fsa::g_fwd_timing, (size_t)n * sizeof(unsigned long long));
+}
+#endif

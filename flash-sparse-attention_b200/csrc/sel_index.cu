@@ -38,8 +38,12 @@ __global__ void __launch_bounds__(256) sel_index_pass(const int* __restrict__ to
                 if ((int)lane == leader) base = atomicAdd(ix.cursor + key, cnt);
                 base = __shfl_sync(m, base, leader);
                 int rank = __popc(m & lt);
-                ix.entries[(int64_t)ix.blk_off[key] + base + rank] = ((uint32_t)n << kSlotBits) | (uint32_t)sl;
+                const int ps = ix.tile_off[key] * s.TPT + base + rank;
+                ix.entries[ps] = ((uint32_t)n << kSlotBits) | (uint32_t)sl;
+                ix.pos[((int64_t)h * s.N + n) * s.T + sl] = ps;
             }
+        } else if (FILL && active) {
+            ix.pos[((int64_t)h * s.N + n) * s.T + sl] = -1;
         }
     }
 }
@@ -76,20 +80,32 @@ __global__ void __launch_bounds__(1024) sel_index_scan(SelShape s, SelIndex ix) 
         __syncthreads();
         int pa = carry_a + (warp ? wsum_a[warp - 1] : 0);
         int pb = carry_b + (warp ? wsum_b[warp - 1] : 0);
-        if (i < HG) {
-            ix.blk_off[i] = pa + sa - a;
-            ix.tile_off[i] = pb + sb - b;
-        }
+        if (i < HG) ix.tile_off[i] = pb + sb - b;
         __syncthreads();
         if (tid == 1023) { carry_a = pa + sa; carry_b = pb + sb; }
         __syncthreads();
     }
     if (tid == 0) {
-        ix.blk_off[HG] = carry_a;
         ix.tile_off[HG] = carry_b;
         ix.header[1] = carry_b;
         ix.header[2] = carry_a;
     }
+}
+
+// Tile records and the padding of the tile-ordered entry list: one warp per hg.
+__global__ void __launch_bounds__(256) sel_index_tiles(SelShape s, SelIndex ix) {
+    const int lane = threadIdx.x & 31;
+    const int hg = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (hg >= s.Hk * s.NBmax) return;
+    const int cnt = ix.counts[hg];
+    if (cnt == 0) return;
+    const int t0 = ix.tile_off[hg], nt = ix.tile_off[hg + 1] - t0;
+    const int h = hg / s.NBmax;
+    const int row0 = ix.row0[hg - h * s.NBmax];
+    for (int t = lane; t < nt; t += 32) ix.tile_rec[t0 + t] = make_int4(h, row0, min(s.TPT, cnt - t * s.TPT), hg);
+    // unused slots of the last tile
+    const int used = cnt - (nt - 1) * s.TPT;
+    for (int e = used + lane; e < s.TPT; e += 32) ix.entries[(int64_t)(t0 + nt - 1) * s.TPT + e] = 0xFFFFFFFFu;
 }
 
 cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
@@ -101,6 +117,7 @@ cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& 
     unsigned grid = (unsigned)((total + 255) / 256);
     sel_index_pass<false><<<grid, 256, 0, stream>>>(topk_idx, cu, s, ix);
     sel_index_scan<<<1, 1024, 0, stream>>>(s, ix);
+    sel_index_tiles<<<(unsigned)((s.Hk * s.NBmax + 7) / 8), 256, 0, stream>>>(s, ix);
     sel_index_pass<true><<<grid, 256, 0, stream>>>(topk_idx, cu, s, ix);
     return cudaGetLastError();
 }

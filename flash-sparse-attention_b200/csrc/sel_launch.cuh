@@ -13,10 +13,24 @@ void prof_end(int kernel_id, cudaStream_t stream);
 cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
                             cudaStream_t stream);
 
-cudaError_t dispatch_sel_fwd(int dtype, const void* q, int64_t q_sn, int64_t q_sh, const SelShape& s,
-                             const SelIndex& ix, float sm_scale, float* opart, float2* ml, const CUtensorMap& kmap,
-                             const CUtensorMap& vmap, const int* topk_idx, const int* cu, void* o, int64_t o_sn,
-                             int64_t o_sh, float* lse, int num_sms, cudaStream_t stream);
+struct SelFwdArgs {
+    const void* q;            // used by the unpipelined kernel (arbitrary strides)
+    int64_t q_sn, q_sh;
+    float sm_scale;
+    int run;                  // tiles per scheduling run; 0 = default
+    void* opart;              // [max_tiles * 128, D] input dtype
+    float2* ml;               // [max_tiles * 128]
+    void* o;
+    int64_t o_sn, o_sh;
+    float* lse;
+    const CUtensorMap* qmap;  // [N, Hq*D] box {64,1} for gather4; null when q's head stride != D
+    const CUtensorMap* kmap;  // [N, Hk*D] box {64, BK}
+    const CUtensorMap* vmap;
+    const CUtensorMap* omap;  // [max_tiles * 128, D] box {64, 32} for the partial stores
+};
+
+cudaError_t dispatch_sel_fwd(int dtype, const SelFwdArgs& a, const SelShape& s, const SelIndex& ix, int num_sms,
+                             cudaStream_t stream);
 
 struct SelBwdArgs {
     const void *q, *d_o, *o;

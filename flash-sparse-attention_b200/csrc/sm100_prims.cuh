@@ -26,12 +26,21 @@ enum : int {
     kStatusBadIndex = 2,       // an index outside its table was seen and skipped
 };
 
-#ifndef FSA_WAIT_LIMIT
-#define FSA_WAIT_LIMIT (1u << 22)
-#endif
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// One lane of a fully converged warp (predicate true in exactly one lane).  Code that must be
+// issued by a single thread (tcgen05.mma, TMA) is wrapped in `if (elect_one())` inside
+// warp-uniform control flow, so that addresses and descriptors stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 // ---------------------------------------------------------------- mbarrier
@@ -59,11 +68,31 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
         : "memory");
     return ok;
 }
-// Bounded wait.  Returns false (and records the failure) when the limit is reached; the
-// caller keeps going so that TMEM is freed and the kernel returns.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: polls until the phase completes, FSA_WAIT_NS nanoseconds have passed, or
+// another thread of the grid has already recorded a failure in the status word.  Returns false
+// (and records the failure) in the last two cases; the caller keeps going so that TMEM is
+// freed and the kernel returns.
+#ifndef FSA_WAIT_NS
+#define FSA_WAIT_NS 200000000ull   // 0.2 s
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
-    for (uint32_t it = 0; it < FSA_WAIT_LIMIT; ++it) {
+    // fast path: no timer, no status read (each try_wait already sleeps for a while in hardware)
+#pragma unroll 1
+    for (int it = 0; it < 256; ++it)
         if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
+            if (global_timer_ns() - t0 > FSA_WAIT_NS) break;
+        }
     }
     if (status) atomicMax(status, (int)kStatusWaitTimeout);
     return false;
@@ -81,6 +110,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, b
     int sz = valid ? 16 : 0;   // src-size 0 zero-fills the 16 bytes
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(sz) : "memory");
 }
+// The mbarrier receives one arrival (counted in its expected count) when all cp.async issued so
+// far by this thread have completed; the thread itself does not wait.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -94,6 +128,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// TMA gather4: four rows (y0..y3) of a 2-D tensor, box {cols, 1}, land in four consecutive
+// 128-byte rows of the destination (swizzled like a tiled load).
+__device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const CUtensorMap* map, int x, int y0, int y1, int y2, int y3,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, "
+        "%6}], [%7];" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(smem_u32(bar))
+        : "memory");
+}
+// 2-D tiled store smem -> global (bulk async-group completion).  x and y must be non-negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src_smem) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(x), "r"(y), "r"(src_smem)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest 0 groups have finished READING their smem source
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -173,6 +228,18 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
+}
+
+// The same descriptor split for cheap per-k-step updates: the high word is constant for a tile
+// layout, the low word is (address >> 4) | (lbo >> 4) << 16 and advances by (bytes >> 4).
+__device__ __forceinline__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t umma_desc_pack(uint32_t lo, uint32_t hi) {
+    return ((uint64_t)hi << 32) | lo;
 }
 
 // Instruction descriptor for kind::f16 (fp16/bf16 inputs, fp32 accumulate).

@@ -33,7 +33,7 @@ SIGNATURES = {
     "fsa_profile_enable": (c_int, [c_int]),
     "fsa_profile_read": (c_int, [c_int, POINTER(c_float), POINTER(c_int)]),
     "fsa_sel_index_bytes": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64)]),
-    "fsa_sel_fwd_scratch_bytes": (c_int, [c_int64, c_int, c_int, c_int, POINTER(c_int64)]),
+    "fsa_sel_fwd_scratch_bytes": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64)]),
     "fsa_sel_fwd": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

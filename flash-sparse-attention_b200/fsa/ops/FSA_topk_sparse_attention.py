@@ -56,7 +56,7 @@ def sel_attn_fwd(q, k, v, topk_idx, block_size, cu_seqlens, sm_scale, check_stat
     nb = c_int64(0)
     _lib.check(L.fsa_sel_index_bytes(N, B, Hq, Hk, T, block_size, byref(nb)), "fsa_sel_index_bytes")
     index_ws = _alloc_bytes(nb.value, dev)
-    _lib.check(L.fsa_sel_fwd_scratch_bytes(N, Hq, D, T, byref(nb)), "fsa_sel_fwd_scratch_bytes")
+    _lib.check(L.fsa_sel_fwd_scratch_bytes(N, B, Hq, Hk, D, T, block_size, byref(nb)), "fsa_sel_fwd_scratch_bytes")
     scratch = _alloc_bytes(nb.value, dev)
     o = torch.empty((N, Hq, D), dtype=q.dtype, device=dev)
     lse = torch.empty((Hq, N), dtype=torch.float32, device=dev)

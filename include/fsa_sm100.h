@@ -67,9 +67,10 @@ int fsa_profile_read(int kernel_id, float* ms_sum_out, int* launches_out);
 int fsa_sel_index_bytes(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int topk,
                         int block_size, int64_t* bytes_out);
 
-/* Size of the transient forward scratch (per-(token, head, slot) partial outputs and softmax
- * statistics; the reference's o_tiles / l_ij / acc_o_scales buffers, :959-988). */
-int fsa_sel_fwd_scratch_bytes(int64_t total_tokens, int num_q_heads, int head_dim, int topk, int64_t* bytes_out);
+/* Size of the transient forward scratch (per-tile partial outputs in the input dtype and fp32
+ * softmax statistics; the reference's o_tiles / l_ij / acc_o_scales buffers, :959-988). */
+int fsa_sel_fwd_scratch_bytes(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int head_dim, int topk,
+                              int block_size, int64_t* bytes_out);
 
 /* Forward.  Replaces _topk_sparse_attention_fwd_opt (FSA_topk_sparse_attention.py:569-618) as called
  * by FSATopkSparseAttention.forward (:1889-1932).
@@ -102,11 +103,16 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
 int fsa_read_status(const void* index_ws, void* stream, int* status_out);
 
-/* Debug/inspection: copy the block->entries CSR built by the forward to host arrays.
- * counts_host [Hk * nbmax], row0_host [nbmax]; *nbmax_out = total_tokens / block_size + batch + 1. */
+/* Debug/inspection: copy the block->entries structure built by the forward to host arrays.
+ * With nbmax = total_tokens / block_size + batch + 1 and tpt = (128 / group) & ~3:
+ *   counts_host [Hk * nbmax] entries per (kv head, block); row0_host [nbmax] first K/V row of a block;
+ *   tile_off_host [Hk * nbmax + 1] first tile of every (kv head, block);
+ *   entries_host [(ceil(Hk * total_tokens * topk / tpt) + Hk * nbmax) * tpt] entries in tile order:
+ *   the entries of (kv head, block) hg start at tile_off[hg] * tpt; an entry is (token << 6) | slot;
+ *   header_host [64]: [0] status, [1] tiles, [2] entries. */
 int fsa_sel_index_dump(const void* index_ws, int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads,
                        int topk, int block_size, void* stream, int32_t* counts_host, int32_t* row0_host,
-                       int32_t* blk_off_host, uint32_t* entries_host, int32_t* header_host);
+                       int32_t* tile_off_host, uint32_t* entries_host, int32_t* header_host);
 
 #ifdef __cplusplus
 }

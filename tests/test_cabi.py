@@ -44,7 +44,7 @@ def test_workspace_queries():
     assert L.fsa_sel_index_bytes(65536, 4, 8, 4, 16, 64, byref(n)) == 0
     entries = 4 * 65536 * 16 * 4
     assert entries <= n.value < entries + (1 << 20)
-    assert L.fsa_sel_fwd_scratch_bytes(65536, 8, 128, 16, byref(n)) == 0
+    assert L.fsa_sel_fwd_scratch_bytes(65536, 4, 8, 4, 128, 16, 64, byref(n)) == 0
     assert n.value >= 65536 * 8 * 16 * 64 * 2  # at least bf16 partials
     assert L.fsa_sel_bwd_scratch_bytes(65536, 8, 4, 128, 16, 64, byref(n)) == 0
     assert n.value > 0
