@@ -127,9 +127,11 @@ static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, Se
 }
 
 static int bwd_nsub(int BK) { return BK > 64 ? BK / 64 : 1; }
-static int64_t bwd_scratch_bytes(int64_t N, int Hq, int Hk, int D, int T, int BK) {
-    return align_up(N * Hq * 4, 256) + align_up(N * Hq * T * bwd_nsub(BK) * (int64_t)D * 4, 256) +
-           align_up(2 * N * Hk * (int64_t)D * 4, 256);
+static int64_t bwd_dq_part_bytes(const SelShape& s) {
+    return align_up(sel_max_tiles(s) * bwd_nsub(s.BK) * kTileRows * (int64_t)s.D * 2, 1024);
+}
+static int64_t bwd_scratch_bytes(const SelShape& s) {
+    return align_up(s.N * s.Hq * 4, 1024) + bwd_dq_part_bytes(s) + align_up(2 * s.N * s.Hk * (int64_t)s.D * 4, 256);
 }
 
 static int64_t fwd_scratch_bytes(const SelShape& s) {
@@ -255,9 +257,12 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
     return FSA_OK;
 }
 
-int fsa_sel_bwd_scratch_bytes(int64_t N, int Hq, int Hk, int D, int T, int BK, int64_t* bytes_out) {
-    if (!bytes_out || N < 0 || Hq <= 0 || Hk <= 0 || D <= 0 || T <= 0 || BK <= 0) return FSA_ERR_BAD_ARG;
-    *bytes_out = bwd_scratch_bytes(N, Hq, Hk, D, T, BK);
+int fsa_sel_bwd_scratch_bytes(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int64_t* bytes_out) {
+    if (!bytes_out) return FSA_ERR_BAD_ARG;
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    if (rc) return rc;
+    *bytes_out = bwd_scratch_bytes(s);
     return FSA_OK;
 }
 
@@ -285,7 +290,7 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
         return FSA_ERR_BAD_ARG;
     if (k_sn < (int64_t)Hk * D || v_sn < (int64_t)Hk * D) return FSA_ERR_BAD_ARG;
     if (index_ws_bytes < sel_index_bytes(s)) return FSA_ERR_WORKSPACE;
-    if (scratch_bytes < bwd_scratch_bytes(N, Hq, Hk, D, T, BK)) return FSA_ERR_WORKSPACE;
+    if (scratch_bytes < bwd_scratch_bytes(s)) return FSA_ERR_WORKSPACE;
 
     SelIndex ix = sel_index_carve(index_ws, s);
     CUtensorMap kmap, vmap;
@@ -302,8 +307,8 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
     a.q_sn = q_sn; a.q_sh = q_sh; a.do_sn = do_sn; a.do_sh = do_sh; a.o_sn = o_sn; a.o_sh = o_sh;
     a.lse = lse; a.topk_idx = topk_idx; a.cu = cu_seqlens; a.sm_scale = sm_scale;
     char* sp = (char*)scratch;
-    a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 256);
-    a.dq_part = (float*)sp; sp += align_up(N * Hq * T * bwd_nsub(BK) * (int64_t)D * 4, 256);
+    a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 1024);
+    a.dq_part = (void*)sp;  sp += bwd_dq_part_bytes(s);
     a.dk_acc = (float*)sp;
     a.dv_acc = a.dk_acc + N * Hk * (int64_t)D;
     a.dq = dq; a.dk = dk; a.dv = dv;

@@ -31,7 +31,7 @@ struct SelBwdParams {
     SelIndex ix;
     int nsub;              // 64-key sub-tiles per block
     float scale, scale_log2;
-    float* dq_part;        // [N, Hq, T * nsub, D]
+    ET* dq_part;           // [max_tiles * nsub * 128, D] partial dQ rows in tile order (input dtype)
     float* dk_acc;         // [N, Hk, D] fp32, zero-initialised
     float* dv_acc;
 };
@@ -187,11 +187,11 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
 #pragma unroll 4
             for (int i = tid; i < kTileRows * CPR; i += 128) {
                 int r = i / CPR, c = i % CPR;
-                int e = r / s.G, g = r - e * s.G;
-                bool valid = e < ne;
+                int g = r / s.TPT, e = r - g * s.TPT;      // head-major rows, as in the forward
+                bool valid = g < s.G && e < ne;
                 uint32_t ent = valid ? s_ent[e] : 0u;
                 int64_t n = ent >> kSlotBits;
-                int hq = h * s.G + g;
+                int hq = h * s.G + (valid ? g : 0);
                 uint32_t off = (uint32_t)((c >> 3) * (kTileRows * 128)) + sw128_chunk_off(r, c & 7);
                 cp_async16(smem_u32(sQ) + off, p.q + n * p.q_sn + (int64_t)hq * p.q_sh + c * 8, valid);
                 cp_async16(smem_u32(sDO) + off, p.d_o + n * p.do_sn + (int64_t)hq * p.do_sh + c * 8, valid);
@@ -199,12 +199,12 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
             cp_async_commit();
         }
         const int r = tid;
-        const int e = r / s.G;
-        const bool row_valid = e < ne;
+        const int g_row = r / s.TPT;
+        const int e = r - g_row * s.TPT;
+        const bool row_valid = g_row < s.G && e < ne;
         const uint32_t ent = row_valid ? s_ent[e] : 0u;
         const int tok = (int)(ent >> kSlotBits);
-        const int slot = (int)(ent & (kMaxTopk - 1));
-        const int hq_row = h * s.G + (r - e * s.G);
+        const int hq_row = h * s.G + (row_valid ? g_row : 0);
         float lse_r = 0.f, delta_r = 0.f;
         if (row_valid) {
             lse_r = __ldg(p.lse + (int64_t)hq_row * s.N + tok);
@@ -303,8 +303,8 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
 
         // ---- stage 6: dQ partial -> global
         {
-            const int64_t prow = ((int64_t)tok * s.Hq + hq_row) * (s.T * p.nsub) + slot * p.nsub + sub;
-            float4* dst = reinterpret_cast<float4*>(p.dq_part + prow * D);
+            const int64_t prow = ((int64_t)(hg_first + tile) * p.nsub + sub) * kTileRows + r;
+            uint4* dst = reinterpret_cast<uint4*>(p.dq_part + prow * D);
 #pragma unroll
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t v[32];
@@ -312,9 +312,14 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
                 tmem_ld_wait();
                 if (row_valid) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        dst[(c0 >> 2) + i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                         __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 u;
+                        u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                        u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                        u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                        u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                        dst[(c0 >> 3) + q4] = u;
+                    }
                 }
             }
         }
@@ -361,39 +366,49 @@ __global__ void __launch_bounds__(256) sel_bwd_delta(const ET* __restrict__ o, i
     if (lane == 0) delta[(int64_t)hq * N + n] = acc;
 }
 
-// dq[n, hq, :] = sum over usable slots (and sub-tiles) of the partials; one warp per (n, hq)
+// dq[n, hq, :] = sum over usable slots (and sub-tiles) of the partial rows, looked up through
+// the `pos` map; one warp per (n, hq)
 template <int D, typename ET>
-__global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const float* __restrict__ dq_part, const int* __restrict__ topk_idx,
-                                                         const int* __restrict__ cu, SelShape s, int nsub,
-                                                         ET* __restrict__ dq) {
+__global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const ET* __restrict__ dq_part, const int* __restrict__ pos, SelShape s,
+                                                         int nsub, ET* __restrict__ dq) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= s.N * s.Hq) return;
     const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);
-    const int h = hq / s.G;
-    const int* idrow = topk_idx + ((int64_t)h * s.N + n) * s.T;
-    int r0;
-    bool v0 = lane < s.T && entry_block(cu, s.B, s.BK, n, __ldg(idrow + lane), &r0) >= 0;
-    bool v1 = lane + 32 < s.T && entry_block(cu, s.B, s.BK, n, __ldg(idrow + lane + 32), &r0) >= 0;
-    unsigned m0 = __ballot_sync(0xffffffffu, v0), m1 = __ballot_sync(0xffffffffu, v1);
+    const int h = hq / s.G, g = hq - h * s.G;
+    const int* prow = pos + ((int64_t)h * s.N + n) * s.T;
+    long long pr0 = -1, pr1 = -1;    // partial row of slot lane / lane + 32 (sub-tile 0)
+    if (lane < s.T) {
+        int ps = __ldg(prow + lane);
+        if (ps >= 0) pr0 = ((long long)(ps / s.TPT) * nsub) * kTileRows + g * s.TPT + ps % s.TPT;
+    }
+    if (lane + 32 < s.T) {
+        int ps = __ldg(prow + lane + 32);
+        if (ps >= 0) pr1 = ((long long)(ps / s.TPT) * nsub) * kTileRows + g * s.TPT + ps % s.TPT;
+    }
     constexpr int V = D / 32;
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    const float* base = dq_part + row * (int64_t)(s.T * nsub) * D + lane * V;
     for (int sl = 0; sl < s.T; ++sl) {
-        bool valid = sl < 32 ? ((m0 >> sl) & 1) : ((m1 >> (sl - 32)) & 1);
-        if (!valid) continue;
+        const long long pr = __shfl_sync(0xffffffffu, sl < 32 ? pr0 : pr1, sl & 31);
+        if (pr < 0) continue;
         for (int u = 0; u < nsub; ++u) {
-            const float* src = base + (int64_t)(sl * nsub + u) * D;
+            const ET* src = dq_part + (pr + (long long)u * kTileRows) * D + lane * V;
             if constexpr (V == 2) {
-                float2 x = *reinterpret_cast<const float2*>(src);
+                float2 x = ElemTraits<ET>::unpack2(*reinterpret_cast<const uint32_t*>(src));
                 acc[0] += x.x; acc[1] += x.y;
+            } else if constexpr (V == 4) {
+                uint2 w = *reinterpret_cast<const uint2*>(src);
+                float2 x = ElemTraits<ET>::unpack2(w.x), y = ElemTraits<ET>::unpack2(w.y);
+                acc[0] += x.x; acc[1] += x.y; acc[2] += y.x; acc[3] += y.y;
             } else {
+                uint4 w = *reinterpret_cast<const uint4*>(src);
+                const uint32_t* ww = &w.x;
 #pragma unroll
-                for (int i = 0; i < V; i += 4) {
-                    float4 x = *reinterpret_cast<const float4*>(src + i);
-                    acc[i] += x.x; acc[i + 1] += x.y; acc[i + 2] += x.z; acc[i + 3] += x.w;
+                for (int i = 0; i < 4; ++i) {
+                    float2 x = ElemTraits<ET>::unpack2(ww[i]);
+                    acc[2 * i] += x.x; acc[2 * i + 1] += x.y;
                 }
             }
         }
@@ -401,14 +416,18 @@ __global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const float* __restrict
     ET* dst = dq + row * D + lane * V;
     if constexpr (V == 2) {
         *reinterpret_cast<uint32_t*>(dst) = ElemTraits<ET>::pack2(acc[0], acc[1]);
+    } else if constexpr (V == 4) {
+        uint2 w;
+        w.x = ElemTraits<ET>::pack2(acc[0], acc[1]);
+        w.y = ElemTraits<ET>::pack2(acc[2], acc[3]);
+        *reinterpret_cast<uint2*>(dst) = w;
     } else {
-#pragma unroll
-        for (int i = 0; i < V; i += 4) {
-            uint2 u;
-            u.x = ElemTraits<ET>::pack2(acc[i], acc[i + 1]);
-            u.y = ElemTraits<ET>::pack2(acc[i + 2], acc[i + 3]);
-            *reinterpret_cast<uint2*>(dst + i) = u;
-        }
+        uint4 w;
+        w.x = ElemTraits<ET>::pack2(acc[0], acc[1]);
+        w.y = ElemTraits<ET>::pack2(acc[2], acc[3]);
+        w.z = ElemTraits<ET>::pack2(acc[4], acc[5]);
+        w.w = ElemTraits<ET>::pack2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(dst) = w;
     }
 }
 
@@ -446,7 +465,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.lse = a.lse; p.delta = a.delta;
     p.s = s; p.ix = ix; p.nsub = nsub;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
-    p.dq_part = a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
+    p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     auto kern = sel_bwd_main<D, ET>;
     constexpr int smem = SelBwdCfg<D>::kBytes;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -463,7 +482,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(3, stream);
-        sel_bwd_dq_reduce<D, ET><<<grid, 256, 0, stream>>>(a.dq_part, a.topk_idx, a.cu, s, nsub, (ET*)a.dq);
+        sel_bwd_dq_reduce<D, ET><<<grid, 256, 0, stream>>>((const ET*)a.dq_part, ix.pos, s, nsub, (ET*)a.dq);
         prof_end(3, stream);
     }
     if (kv_elems > 0) {

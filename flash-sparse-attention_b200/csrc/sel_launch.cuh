@@ -41,7 +41,7 @@ struct SelBwdArgs {
     float sm_scale;
     // scratch
     float* delta;      // [Hq, N]
-    float* dq_part;    // [N, Hq, T * nsub, D]
+    void* dq_part;     // [max_tiles * nsub * 128, D] input dtype
     float* dk_acc;     // [N, Hk, D]; dv_acc follows immediately
     float* dv_acc;
     // outputs (contiguous)

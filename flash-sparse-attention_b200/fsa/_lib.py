@@ -40,7 +40,7 @@ SIGNATURES = {
          c_int64, c_int64, c_int64, c_int64, c_float, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64,
          c_void_p, c_int64, c_void_p],
     ),
-    "fsa_sel_bwd_scratch_bytes": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64)]),
+    "fsa_sel_bwd_scratch_bytes": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64)]),
     "fsa_sel_bwd": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,

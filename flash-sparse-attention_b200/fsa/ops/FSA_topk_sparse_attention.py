@@ -86,7 +86,7 @@ def sel_attn_bwd(q, k, v, o, lse, do, topk_idx, block_size, cu_seqlens, sm_scale
     topk_idx = topk_idx.contiguous()
     dev = q.device
     nb = c_int64(0)
-    _lib.check(L.fsa_sel_bwd_scratch_bytes(N, Hq, Hk, D, T, block_size, byref(nb)), "fsa_sel_bwd_scratch_bytes")
+    _lib.check(L.fsa_sel_bwd_scratch_bytes(N, B, Hq, Hk, D, T, block_size, byref(nb)), "fsa_sel_bwd_scratch_bytes")
     scratch = _alloc_bytes(nb.value, dev)
     dq = torch.empty((N, Hq, D), dtype=q.dtype, device=dev)
     dk = torch.empty((N, Hk, D), dtype=q.dtype, device=dev)

@@ -84,8 +84,8 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
                 void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream);
 
 /* Size of the transient backward scratch (dQ partials, fp32 dK/dV accumulators, delta). */
-int fsa_sel_bwd_scratch_bytes(int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim, int topk,
-                              int block_size, int64_t* bytes_out);
+int fsa_sel_bwd_scratch_bytes(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                              int topk, int block_size, int64_t* bytes_out);
 
 /* Backward.  Replaces _topk_sparse_attention_bwd_opt (FSA_topk_sparse_attention.py:1715-1884):
  * backward_sum_o_do, backward_dkdv, dq_compute_kernel, dq_reduce_kernel.  `index_ws` is the
