@@ -306,6 +306,8 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
     a.q = q; a.d_o = d_o; a.o = o;
     a.q_sn = q_sn; a.q_sh = q_sh; a.do_sn = do_sn; a.do_sh = do_sh; a.o_sn = o_sn; a.o_sh = o_sh;
     a.lse = lse; a.topk_idx = topk_idx; a.cu = cu_seqlens; a.sm_scale = sm_scale;
+    a.run = env_int("FSA_SEL_RUN", 0);
+    a.force_simple = env_int("FSA_SEL_BWD_SIMPLE", 0);
     char* sp = (char*)scratch;
     a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 1024);
     a.dq_part = (void*)sp;  sp += bwd_dq_part_bytes(s);

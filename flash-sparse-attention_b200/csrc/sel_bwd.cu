@@ -466,19 +466,24 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.s = s; p.ix = ix; p.nsub = nsub;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
-    auto kern = sel_bwd_main<D, ET>;
-    constexpr int smem = SelBwdCfg<D>::kBytes;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    int per_sm = (int)(512 / SelBwdCfg<D>::kCols);
-    int by_smem = (227 * 1024) / (smem + 2048);
-    if (by_smem < per_sm) per_sm = by_smem;
-    if (per_sm < 1) per_sm = 1;
-    prof_begin(2, stream);
-    kern<<<num_sms * per_sm, 128, smem, stream>>>(p, kmap, vmap);
-    prof_end(2, stream);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
+    if (D == 128 && s.BK <= kKT && !a.force_simple) {
+        e = launch_sel_bwd_pipe(ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16, a, s, ix, kmap, vmap, num_sms, stream);
+        if (e != cudaSuccess) return e;
+    } else {
+        auto kern = sel_bwd_main<D, ET>;
+        constexpr int smem = SelBwdCfg<D>::kBytes;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        int per_sm = (int)(512 / SelBwdCfg<D>::kCols);
+        int by_smem = (227 * 1024) / (smem + 2048);
+        if (by_smem < per_sm) per_sm = by_smem;
+        if (per_sm < 1) per_sm = 1;
+        prof_begin(2, stream);
+        kern<<<num_sms * per_sm, 128, smem, stream>>>(p, kmap, vmap);
+        prof_end(2, stream);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(3, stream);

@@ -1,0 +1,466 @@
+// Selected-attention backward, pipelined kernel for head_dim 128 and blocks of <= 64 keys
+// (the shapes of the benchmark configurations); other shapes use the unpipelined kernel in
+// sel_bwd.cu.  Same math and same outputs: per tile of <= 128 (head, token) rows of one KV block
+//     S = Q K^T, dP = dO V^T | P = exp2(S c - lse), dS = scale P (dP - delta) | dQ = dS K,
+//     dK^T += Q^T dS, dV^T += dO^T P
+// Warp roles (512 threads, one CTA per SM, persistent over a round-robin run schedule):
+//   warps 0,1    gather Q and dO rows with 16-byte async copies (two stages), load K/V blocks by
+//                TMA (two stages);
+//   warp 2       issues S and dP (tcgen05, fp32 in TMEM, two buffers);
+//   warp 3       issues dQ, dK^T, dV^T;
+//   warps 4..7   move the finished dK^T / dV^T accumulators of a block from TMEM to registers
+//                (freeing them for the next block at once) and add them to the fp32 global
+//                accumulators (red.add) while the next block computes;
+//   warps 8..15  two groups, one row per thread, alternate tiles: P / dS to swizzled smem, then the
+//                dQ partial of the tile from TMEM to global memory (input dtype, tile order).
+#include "sel_launch.cuh"
+
+namespace fsa {
+
+template <typename ET>
+struct SelBwdPipeParams {
+    const ET* q;   int64_t q_sn, q_sh;
+    const ET* d_o; int64_t do_sn, do_sh;
+    const float* lse;
+    const float* delta;
+    SelShape s;
+    SelIndex ix;
+    float scale, scale_log2;
+    int run;
+    ET* dq_part;       // [max_tiles * 128, D]
+    float* dk_acc;     // [N, Hk, D] fp32, zero-initialised
+    float* dv_acc;
+};
+
+namespace bwdpipe {
+constexpr int D = 128, KT = 64;
+constexpr int kThreads = 512, kLoaders = 64;
+constexpr int kKV = 2 * KT * D * 2;              // K then V: 32 KB
+constexpr int kQD = 2 * kTileRows * D * 2;       // Q then dO: 64 KB
+constexpr int kPS = 2 * kTileRows * KT * 2;      // P then dS: 32 KB
+constexpr int kTail = 2560;
+constexpr int kBytes = 2 * kKV + 2 * kQD + kPS + kTail;
+constexpr int cS = 0, cDP = 64;                  // + 128 * buffer
+constexpr int cDQ = 256, cDK = 384, cDV = 448;
+constexpr uint32_t kCols = 512;
+static_assert(kBytes <= 227 * 1024, "smem budget");
+}  // namespace bwdpipe
+
+__device__ __forceinline__ float ex2_approx_b(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename ET>
+__global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBwdPipeParams<ET> p,
+                                                                     const __grid_constant__ CUtensorMap kmap,
+                                                                     const __grid_constant__ CUtensorMap vmap) {
+    using namespace bwdpipe;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sKV = smem;
+    uint8_t* sQD = sKV + 2 * kKV;
+    uint8_t* sP = sQD + 2 * kQD;
+    uint8_t* sDS = sP + kTileRows * KT * 2;
+    uint8_t* tail = sP + kPS;
+    int (*s_offq)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail);               // [2][128] q row offset / 8, -1 padding
+    int (*s_offd)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail + 1024);        // [2][128] dO row offset / 8
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
+    uint64_t* qd_full = bars;            // [2]
+    uint64_t* qd_empty = bars + 2;       // [2]
+    uint64_t* kv_full = bars + 4;        // [2]
+    uint64_t* kv_empty = bars + 6;       // [2]
+    uint64_t* meta_full = bars + 8;      // [2]
+    uint64_t* sdp_full = bars + 10;      // [2]
+    uint64_t* sdp_empty = bars + 12;     // [2]
+    uint64_t* pds_full = bars + 14;
+    uint64_t* pds_empty = bars + 15;
+    uint64_t* dq_full = bars + 16;
+    uint64_t* dq_empty = bars + 17;
+    uint64_t* acc_full = bars + 18;
+    uint64_t* acc_empty = bars + 19;
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 20);
+    int* s_nb = reinterpret_cast<int*>(bars + 21);   // [2]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const SelShape& s = p.s;
+    int* status = p.ix.header;
+    if (smem_u32(smem) & 1023u) {
+        if (tid == 0) atomicMax(status, (int)kStatusBadIndex);
+        return;
+    }
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&qd_full[i], kLoaders); mbar_init(&qd_empty[i], 1);
+            mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&meta_full[i], 1);
+            mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 128);
+        }
+        mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
+        mbar_init(dq_full, 1); mbar_init(dq_empty, 128);
+        mbar_init(acc_full, 1); mbar_init(acc_empty, 128);
+        mbar_init_fence();
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, kCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = tmem_slot;
+    const TileSchedule sched(p.ix.header[1], p.run);
+    const int nloc = sched.nloc;
+    const int key_lim = min(KT, s.BK);
+
+    if (warp < 2) {
+        // ------------------------------------------------------------------ loaders
+        const int t = tid;
+        bool ok = true;
+        int kvn = -1;
+        // rows t and t + 64 of every tile
+        const int g0 = t / s.TPT, e0 = t - g0 * s.TPT;
+        const int g1 = (t + 64) / s.TPT, e1 = (t + 64) - g1 * s.TPT;
+        const bool ex0 = g0 < s.G, ex1 = g1 < s.G;
+        TileInfo m1{0, 0, 0, -1}, m2{0, 0, 0, -1};
+        uint32_t ent1a = 0xFFFFFFFFu, ent1b = 0xFFFFFFFFu, ent2a = 0xFFFFFFFFu, ent2b = 0xFFFFFFFFu;
+        auto fetch = [&](int k, TileInfo& ti, uint32_t& ea, uint32_t& eb) {
+            const int j = sched.tile(k);
+            ti = load_tile(p.ix, j);
+            ea = 0xFFFFFFFFu; eb = 0xFFFFFFFFu;
+            if (ex0) ea = __ldg(p.ix.entries + (int64_t)j * s.TPT + e0);
+            if (ex1) eb = __ldg(p.ix.entries + (int64_t)j * s.TPT + e1);
+        };
+        if (nloc > 0) fetch(0, m1, ent1a, ent1b);
+        if (nloc > 1) fetch(1, m2, ent2a, ent2b);
+        int prev_hg = -1;
+        constexpr int CPR = D / 8, RSTEP = kLoaders / CPR;   // 16 chunks per row, 4 rows per step
+        const int cchunk = t % CPR, rbase = t / CPR;
+        const uint32_t slab_off = (uint32_t)(cchunk >> 3) * (kTileRows * 128);
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int st = k & 1;
+            const TileInfo cur = m1;
+            const uint32_t c_ea = ent1a, c_eb = ent1b;
+            const bool c_nb = cur.hg != prev_hg;
+            prev_hg = cur.hg;
+            m1 = m2; ent1a = ent2a; ent1b = ent2b;
+            if (k + 2 < nloc) fetch(k + 2, m2, ent2a, ent2b);
+            ok = mbar_wait(&qd_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
+            if (t == 0) {
+                s_nb[st] = c_nb ? 1 : 0;
+                mbar_arrive(&meta_full[st]);
+            }
+            if (c_nb) {
+                ++kvn;
+                if (t == 0) {
+                    const int ks = kvn & 1;
+                    ok = mbar_wait(&kv_empty[ks], ((kvn >> 1) & 1) ^ 1, status) && ok;
+                    mbar_expect_tx(&kv_full[ks], (uint32_t)kKV);
+                    uint8_t* dK = sKV + ks * kKV;
+                    uint8_t* dV = dK + KT * D * 2;
+#pragma unroll
+                    for (int b = 0; b < D / 64; ++b) {
+                        tma_load_2d(smem_u32(dK + b * KT * 128), &kmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
+                        tma_load_2d(smem_u32(dV + b * KT * 128), &vmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
+                    }
+                }
+            }
+            {
+                const bool va = c_ea != 0xFFFFFFFFu, vb = c_eb != 0xFFFFFFFFu;
+                const long long ta = c_ea >> kSlotBits, tb = c_eb >> kSlotBits;
+                const int ha = cur.h * s.G + g0, hb = cur.h * s.G + g1;
+                s_offq[st][t] = va ? (int)((ta * p.q_sn + (long long)ha * p.q_sh) >> 3) : -1;
+                s_offd[st][t] = va ? (int)((ta * p.do_sn + (long long)ha * p.do_sh) >> 3) : -1;
+                s_offq[st][t + 64] = vb ? (int)((tb * p.q_sn + (long long)hb * p.q_sh) >> 3) : -1;
+                s_offd[st][t + 64] = vb ? (int)((tb * p.do_sn + (long long)hb * p.do_sh) >> 3) : -1;
+            }
+            named_bar_sync(1, kLoaders);
+            {
+                const uint32_t dq_ = smem_u32(sQD + st * kQD) + slab_off;
+                const uint32_t dd_ = dq_ + kTileRows * D * 2;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    constexpr int NIT = kTileRows / RSTEP / 2;     // 16 rows per half
+                    int oq[NIT], od[NIT];
+#pragma unroll
+                    for (int it = 0; it < NIT; ++it) {
+                        oq[it] = s_offq[st][rbase + (half * NIT + it) * RSTEP];
+                        od[it] = s_offd[st][rbase + (half * NIT + it) * RSTEP];
+                    }
+#pragma unroll
+                    for (int it = 0; it < NIT; ++it) {
+                        const int r = rbase + (half * NIT + it) * RSTEP;
+                        const bool valid = oq[it] >= 0;
+                        const uint32_t so = sw128_chunk_off(r, cchunk & 7);
+                        cp_async16(dq_ + so, p.q + ((long long)(valid ? oq[it] : 0) << 3) + cchunk * 8, valid);
+                        cp_async16(dd_ + so, p.d_o + ((long long)(valid ? od[it] : 0) << 3) + cchunk * 8, valid);
+                    }
+                }
+            }
+            cp_async_mbar_arrive_noinc(&qd_full[st]);
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------------------------------------------ accumulator flush
+        // Walks the CTA's tiles to find the block boundaries; for every finished block: wait for its
+        // last products, pull dK^T / dV^T (lane = head-dim index, columns = keys) into registers,
+        // release the TMEM accumulators, then add to the fp32 global accumulators.
+        const int d_idx = (warp & 3) * 32 + lane;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        bool ok = true;
+        int nflush = 0;
+        int k = 0;
+        while (k < nloc && ok) {
+            const TileInfo ti = load_tile(p.ix, sched.tile(k));
+            int k2 = k + 1;
+            while (k2 < nloc && load_tile(p.ix, sched.tile(k2)).hg == ti.hg) ++k2;   // tiles [k, k2) form the block
+            ok = mbar_wait(acc_full, nflush & 1, status) && ok;
+            tc_fence_after();
+            const int nkeys = (int)min((int64_t)key_lim, s.N - ti.row0);
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                uint32_t v[KT];
+#pragma unroll
+                for (int c0 = 0; c0 < KT; c0 += 32)
+                    tmem_ld32(tbase + lane_off + (which == 0 ? cDK : cDV) + c0, *reinterpret_cast<uint32_t (*)[32]>(&v[c0]));
+                tmem_ld_wait();
+                if (which == 1) {
+                    // both accumulators are in registers now: the next block may overwrite them
+                    tc_fence_before();
+                    mbar_arrive(acc_empty);
+                    ++nflush;
+                }
+                float* dst = (which == 0 ? p.dk_acc : p.dv_acc) + ((int64_t)ti.row0 * s.Hk + ti.h) * D + d_idx;
+#pragma unroll
+                for (int key = 0; key < KT; ++key)
+                    if (key < nkeys) atomicAdd(dst + (int64_t)key * s.Hk * D, __uint_as_float(v[key]));
+            }
+            k = k2;
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ MMA issuer 1: S and dP
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, KT, false, false);
+        constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+        const uint32_t qd_lo = umma_desc_lo(smem_u32(sQD), 16);
+        const uint32_t kv_lo = umma_desc_lo(smem_u32(sKV), 16);
+        int kvn = -1;
+        bool ok = true;
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int st = k & 1;
+            ok = mbar_wait(&meta_full[st], (k >> 1) & 1, status) && ok;
+            if (s_nb[st] != 0) {
+                ++kvn;
+                ok = mbar_wait(&kv_full[kvn & 1], (kvn >> 1) & 1, status) && ok;
+            }
+            ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;
+            fence_async_smem();
+            ok = mbar_wait(&sdp_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
+            tc_fence_after();
+            const uint32_t aq = qd_lo + (uint32_t)(st * (kQD >> 4));
+            const uint32_t ad = aq + (uint32_t)((kTileRows * D * 2) >> 4);
+            const uint32_t bk = kv_lo + (uint32_t)((kvn & 1) * (kKV >> 4));
+            const uint32_t bv = bk + (uint32_t)((KT * D * 2) >> 4);
+            const uint32_t dS_ = tbase + cS + st * 128, dP_ = tbase + cDP + st * 128;
+            if (leader) {
+                constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (KT * 128) >> 4;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(dS_, umma_desc_pack(aq + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                            umma_desc_pack(bk + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(dP_, umma_desc_pack(ad + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                            umma_desc_pack(bv + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                umma_commit(&sdp_full[st]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------------ MMA issuer 2: dQ, dK^T, dV^T
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_dq = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);     // dS (K-major) x K (MN-major)
+        constexpr uint32_t idesc_dk = umma_idesc(ElemTraits<ET>::kIsBF16, 128, KT, true, true);     // Q^T / dO^T x dS / P
+        constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+        const uint32_t ds_k_lo = umma_desc_lo(smem_u32(sDS), 16);                       // dS as K-major A
+        const uint32_t ds_mn_lo = umma_desc_lo(smem_u32(sDS), 8192);                    // dS as MN-major B (one slab)
+        const uint32_t p_mn_lo = umma_desc_lo(smem_u32(sP), 8192);
+        const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sKV), KT * 128);                 // K as MN-major B: slabs KT*128 apart
+        const uint32_t qd_mn_lo = umma_desc_lo(smem_u32(sQD), kTileRows * 128);         // Q / dO as MN-major A
+        int kvn = -1, blk = -1;
+        bool ok = true;
+        int hg0 = -1, hg1 = -1, hg2 = -1;
+        if (nloc > 0) hg1 = load_tile(p.ix, sched.tile(0)).hg;
+        if (nloc > 1) hg2 = load_tile(p.ix, sched.tile(1)).hg;
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int st = k & 1;
+            const int prev_hg = hg0;
+            hg0 = hg1; hg1 = hg2;
+            if (k + 2 < nloc) hg2 = load_tile(p.ix, sched.tile(k + 2)).hg;
+            const bool first_of_block = hg0 != prev_hg;
+            const bool last_of_block = (k + 1 >= nloc) || (hg1 != hg0);
+            if (first_of_block) { ++kvn; ++blk; }
+            ok = mbar_wait(pds_full, k & 1, status) && ok;
+            ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
+            ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;     // already complete: acquire only
+            ok = mbar_wait(&kv_full[kvn & 1], (kvn >> 1) & 1, status) && ok;
+            if (first_of_block && blk > 0) ok = mbar_wait(acc_empty, (blk - 1) & 1, status) && ok;
+            fence_async_smem();
+            tc_fence_after();
+            const uint32_t bk = k_mn_lo + (uint32_t)((kvn & 1) * (kKV >> 4));
+            const uint32_t aq = qd_mn_lo + (uint32_t)(st * (kQD >> 4));
+            const uint32_t ad = aq + (uint32_t)((kTileRows * D * 2) >> 4);
+            if (leader) {
+#pragma unroll
+                for (int ks = 0; ks < KT / 16; ++ks)
+                    umma_ss(tbase + cDQ, umma_desc_pack(ds_k_lo + ks * 2, hi_1024), umma_desc_pack(bk + ks * (2048 >> 4), hi_1024),
+                            idesc_dq, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < kTileRows / 16; ++ks) {
+                    const uint32_t acc = (!first_of_block || ks > 0) ? 1u : 0u;
+                    umma_ss(tbase + cDK, umma_desc_pack(aq + ks * (2048 >> 4), hi_1024),
+                            umma_desc_pack(ds_mn_lo + ks * (2048 >> 4), hi_1024), idesc_dk, acc);
+                    umma_ss(tbase + cDV, umma_desc_pack(ad + ks * (2048 >> 4), hi_1024),
+                            umma_desc_pack(p_mn_lo + ks * (2048 >> 4), hi_1024), idesc_dk, acc);
+                }
+                umma_commit(pds_empty);
+                umma_commit(&qd_empty[st]);
+                umma_commit(dq_full);
+                if (last_of_block) {
+                    umma_commit(&kv_empty[kvn & 1]);
+                    umma_commit(acc_full);
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------------ P / dS and dQ epilogue
+        const int sb = (warp - 8) >> 2;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const int g = r / s.TPT;
+        const int e = r - g * s.TPT;
+        const bool row_exists = g < s.G;
+        bool ok = true;
+        // software pipeline over this group's tiles: entries two tiles ahead, lse / delta one ahead
+        uint32_t entB = 0xFFFFFFFFu;            // entry of tile k + 2
+        uint32_t entA = 0xFFFFFFFFu;            // entry of tile k (after rotation)
+        int row0A = 0, row0B = 0, hA = 0, hB = 0;
+        float lseA = 0.f, deltaA = 0.f;
+        auto fetch_ent = [&](int k, uint32_t& ent, int& row0, int& h) {
+            const int j = sched.tile(k);
+            TileInfo ti = load_tile(p.ix, j);
+            row0 = ti.row0; h = ti.h;
+            ent = 0xFFFFFFFFu;
+            if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);
+        };
+        auto fetch_stats = [&](uint32_t ent, int h, float& lse_, float& delta_) {
+            lse_ = 0.f; delta_ = 0.f;
+            if (ent != 0xFFFFFFFFu) {
+                const int64_t idx = (int64_t)(h * s.G + g) * s.N + (ent >> kSlotBits);
+                lse_ = __ldg(p.lse + idx);
+                delta_ = __ldg(p.delta + idx);
+            }
+        };
+        if (sb < nloc) {
+            fetch_ent(sb, entA, row0A, hA);
+            fetch_stats(entA, hA, lseA, deltaA);
+        }
+        if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B, hB);
+        for (int k = sb; k < nloc && ok; k += 2) {
+            const int j = sched.tile(k);
+            const uint32_t ent = entA;
+            const int row0 = row0A;
+            const float lse_r = lseA, delta_r = deltaA;
+            // rotate the prefetch registers
+            entA = entB; row0A = row0B; hA = hB;
+            if (k + 2 < nloc) fetch_stats(entA, hA, lseA, deltaA);
+            if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B, hB);
+            const bool row_valid = ent != 0xFFFFFFFFu;
+            const int tok = (int)(ent >> kSlotBits);
+            const int nvis = row_valid ? min(key_lim, tok - row0 + 1) : 0;   // may be <= 0
+            ok = mbar_wait(&sdp_full[sb], (k >> 1) & 1, status) && ok;
+            tc_fence_after();
+            uint32_t pp[KT / 2], dd[KT / 2];
+#pragma unroll
+            for (int c0 = 0; c0 < KT; c0 += 32) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tbase + lane_off + cS + sb * 128 + c0, sv);
+                tmem_ld32(tbase + lane_off + cDP + sb * 128 + c0, dv);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = (c0 + i < nvis) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                    float p1 = (c0 + i + 1 < nvis) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                    float d0 = p0 * (__uint_as_float(dv[i]) - delta_r) * p.scale;
+                    float d1 = p1 * (__uint_as_float(dv[i + 1]) - delta_r) * p.scale;
+                    pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                    dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&sdp_empty[sb]);
+            ok = mbar_wait(pds_empty, (k & 1) ^ 1, status) && ok;
+#pragma unroll
+            for (int ch = 0; ch < KT / 8; ++ch) {
+                const uint32_t off = sw128_chunk_off(r, ch);
+                *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+                *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[ch * 4], dd[ch * 4 + 1], dd[ch * 4 + 2], dd[ch * 4 + 3]);
+            }
+            fence_async_smem();
+            mbar_arrive(pds_full);
+            // ---- dQ partial of this tile
+            ok = mbar_wait(dq_full, k & 1, status) && ok;
+            tc_fence_after();
+            uint4* dst = reinterpret_cast<uint4*>(p.dq_part + ((int64_t)j * kTileRows + r) * D);
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tbase + lane_off + cDQ + c0, v);
+                tmem_ld_wait();
+                if (row_valid) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 u;
+                        u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                        u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                        u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                        u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                        dst[(c0 >> 3) + q4] = u;
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(dq_empty);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, bwdpipe::kCols);
+}
+
+template <typename ET>
+static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const SelIndex& ix, const CUtensorMap& kmap,
+                               const CUtensorMap& vmap, int num_sms, cudaStream_t stream) {
+    SelBwdPipeParams<ET> p;
+    p.q = (const ET*)a.q; p.q_sn = a.q_sn; p.q_sh = a.q_sh;
+    p.d_o = (const ET*)a.d_o; p.do_sn = a.do_sn; p.do_sh = a.do_sh;
+    p.lse = a.lse; p.delta = a.delta;
+    p.s = s; p.ix = ix;
+    p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+    p.run = a.run > 0 ? a.run : 8;
+    p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
+    auto kern = sel_bwd_pipe<ET>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwdpipe::kBytes);
+    if (e != cudaSuccess) return e;
+    prof_begin(2, stream);
+    kern<<<num_sms, bwdpipe::kThreads, bwdpipe::kBytes, stream>>>(p, kmap, vmap);
+    prof_end(2, stream);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sel_bwd_pipe(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
+                                const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream) {
+    return dtype == kBF16 ? launch_pipe<__nv_bfloat16>(a, s, ix, kmap, vmap, num_sms, stream)
+                          : launch_pipe<__half>(a, s, ix, kmap, vmap, num_sms, stream);
+}
+
+}  // namespace fsa

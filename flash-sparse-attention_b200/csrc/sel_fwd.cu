@@ -83,9 +83,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
 
 template <int D, int BK, typename ET>
 __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParams<ET> p, const ET* __restrict__ q, int64_t q_sn,

@@ -13,6 +13,10 @@ void prof_end(int kernel_id, cudaStream_t stream);
 cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
                             cudaStream_t stream);
 
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 struct SelFwdArgs {
     const void* q;            // used by the unpipelined kernel (arbitrary strides)
     int64_t q_sn, q_sh;
@@ -39,6 +43,8 @@ struct SelBwdArgs {
     const int* topk_idx;
     const int* cu;
     float sm_scale;
+    int run;           // tiles per scheduling run; 0 = default
+    int force_simple;  // diagnostics: use the unpipelined main kernel even where the pipelined one applies
     // scratch
     float* delta;      // [Hq, N]
     void* dq_part;     // [max_tiles * nsub * 128, D] input dtype
@@ -47,6 +53,10 @@ struct SelBwdArgs {
     // outputs (contiguous)
     void *dq, *dk, *dv;
 };
+
+// pipelined main kernel for head_dim 128, block size <= 64 (sel_bwd_pipe.cu)
+cudaError_t launch_sel_bwd_pipe(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
+                                const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream);
 
 cudaError_t dispatch_sel_bwd(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
                              const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream);
