@@ -155,6 +155,7 @@ const char* fsa_error_string(int code) {
         case FSA_ERR_WORKSPACE: return "workspace too small";
         case FSA_ERR_CUDA: return "CUDA call failed";
         case FSA_ERR_DEVICE_STATUS: return "a kernel recorded a device-side failure";
+        case FSA_ERR_STATIC_LIMIT: return "problem needs more scratch than the library's built-in static buffer holds";
         default: return "unknown error";
     }
 }
@@ -349,6 +350,61 @@ int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, i
     if (entries_host && (e = cudaMemcpy(entries_host, ix.entries, sel_max_tiles(s) * s.TPT * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     if (header_host && (e = cudaMemcpy(header_host, ix.header, 64 * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     return FSA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward without any caller-provided workspace.
+//
+// Some host programs may not allocate device memory once they are running: they handed the whole
+// GPU to their own arena at start-up, or they cannot afford the device-wide synchronisation and
+// the late out-of-memory failure that an allocation can bring in the middle of serving.  For them
+// the index workspace and the partial-result scratch of the forward live in this fixed array,
+// which every GPU that loads the library carries until the process exits.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_sel_static_scratch[FSA_SEL_STATIC_SCRATCH_BYTES];
+
+// Device address of the array on each device (index = CUDA device ordinal).  In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel may use.
+static void* g_sel_static_ptr[64];
+static std::mutex g_sel_static_mutex;
+
+static int sel_static_base(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev < 0 || dev >= 64) return FSA_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_sel_static_mutex);
+    if (!g_sel_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_sel_static_scratch);   // address on the current device
+        if (e != cudaSuccess) return cuda_fail(e);
+        if (!p || ((uintptr_t)p & 255)) return FSA_ERR_BAD_ARG;
+        g_sel_static_ptr[dev] = p;
+    }
+    *out = g_sel_static_ptr[dev];
+    return FSA_OK;
+}
+
+int fsa_sel_fwd_static(const void* q, const void* k, const void* v, const int32_t* topk_idx, const int32_t* cu_seqlens,
+                       int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int dtype, int64_t q_sn, int64_t q_sh,
+                       int64_t k_sn, int64_t v_sn, float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse,
+                       void* stream_) {
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    if (rc) return rc;
+    if (D == 0) return FSA_ERR_BAD_ARG;
+    // layout inside the static array: [index workspace | forward scratch], each 1024-byte aligned
+    const int64_t index_bytes = align_up(sel_index_bytes(s), 1024);
+    const int64_t scratch_bytes = fwd_scratch_bytes(s);
+    if (index_bytes + scratch_bytes > (int64_t)FSA_SEL_STATIC_SCRATCH_BYTES) return FSA_ERR_STATIC_LIMIT;
+    void* base = nullptr;
+    rc = sel_static_base(&base);
+    if (rc) return rc;
+    // The array keeps the previous call's contents.  Everything that must start from zero (status word,
+    // per-block counters and cursors) is cleared by the index build on `stream`; every other word is
+    // written before it is read.
+    return fsa_sel_fwd(q, k, v, topk_idx, cu_seqlens, N, B, Hq, Hk, D, T, BK, dtype, q_sn, q_sh, k_sn, v_sn, sm_scale, o, o_sn,
+                       o_sh, lse, base, index_bytes, (char*)base + index_bytes, scratch_bytes, stream_);
 }
 
 }  // extern "C"

@@ -19,6 +19,7 @@ FSA_ERR_UNSUPPORTED = -2
 FSA_ERR_WORKSPACE = -3
 FSA_ERR_CUDA = -4
 FSA_ERR_DEVICE_STATUS = -5
+FSA_ERR_STATIC_LIMIT = -6
 
 DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}
 
@@ -39,6 +40,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_int64, c_int64, c_int64, c_int64, c_float, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64,
          c_void_p, c_int64, c_void_p],
+    ),
+    "fsa_sel_fwd_static": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_int64, c_int64, c_int64, c_int64, c_float, c_void_p, c_int64, c_int64, c_void_p, c_void_p],
     ),
     "fsa_sel_bwd_scratch_bytes": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64)]),
     "fsa_sel_bwd": (

@@ -31,6 +31,7 @@ extern "C" {
 #define FSA_ERR_WORKSPACE (-3)      /* workspace smaller than the matching *_bytes query */
 #define FSA_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed; see fsa_last_cuda_error() */
 #define FSA_ERR_DEVICE_STATUS (-5)  /* fsa_read_status(): a kernel recorded a failure */
+#define FSA_ERR_STATIC_LIMIT (-6)   /* fsa_sel_fwd_static(): the problem does not fit the built-in scratch array */
 
 #define FSA_DTYPE_BF16 0
 #define FSA_DTYPE_FP16 1
@@ -82,6 +83,34 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
                 int block_size, int dtype, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                 int64_t v_stride_n, float sm_scale, void* o, int64_t o_stride_n, int64_t o_stride_h, float* lse,
                 void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Forward for callers that cannot allocate device memory.  (No counterpart in the reference, whose
+ * forward allocates its scratch tensors with torch on every call.)
+ *
+ * Who needs it: a host program that gave the whole GPU to its own arena at start-up, or one that
+ * must not risk the device-wide synchronisation or a late out-of-memory failure of an allocation
+ * while it is serving.  Such a caller has no workspace to hand to fsa_sel_fwd, so here the index
+ * workspace and the partial-result scratch live in a fixed array of FSA_SEL_STATIC_SCRATCH_BYTES
+ * inside the library; every GPU that loads the library holds that array until the process exits.
+ *
+ * Same inputs, outputs and results as fsa_sel_fwd.  Differences:
+ *   - problems whose index workspace plus forward scratch (the two *_bytes queries above, each rounded
+ *     up to 1 KiB) exceed FSA_SEL_STATIC_SCRATCH_BYTES are refused with FSA_ERR_STATIC_LIMIT;
+ *   - the first call on each device looks up the array's device address (one runtime query, with that
+ *     device current); make that first call before any stream capture begins;
+ *   - no cudaMalloc / cudaFree or any other allocating call is made, on the first call or later;
+ *   - all calls on a device share the one array, and it keeps what the previous call left: the words
+ *     that must start at zero are cleared on `stream` by the call itself, but two calls that may
+ *     overlap on the GPU (different streams, no ordering between them) race on the array and must be
+ *     serialised by the caller;
+ *   - there is no workspace to keep for a backward pass: fsa_sel_bwd needs the caller-owned index
+ *     workspace of fsa_sel_fwd. */
+#define FSA_SEL_STATIC_SCRATCH_BYTES (64u << 20)
+int fsa_sel_fwd_static(const void* q, const void* k, const void* v, const int32_t* topk_idx, const int32_t* cu_seqlens,
+                       int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int head_dim, int topk,
+                       int block_size, int dtype, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t v_stride_n, float sm_scale, void* o, int64_t o_stride_n, int64_t o_stride_h, float* lse,
+                       void* stream);
 
 /* Size of the transient backward scratch (dQ partials, fp32 dK/dV accumulators, delta). */
 int fsa_sel_bwd_scratch_bytes(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int head_dim,
