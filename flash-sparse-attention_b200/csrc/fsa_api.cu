@@ -110,16 +110,17 @@ static int env_int(const char* name, int dflt) {
 
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
-static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, SelShape* s) {
+static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, SelShape* s, int64_t Nk = -1) {
+    if (Nk < 0) Nk = N;
     if (N < 0 || B < 0 || Hq <= 0 || Hk <= 0 || T <= 0 || BK <= 0) return FSA_ERR_BAD_ARG;
     if (Hq % Hk != 0) return FSA_ERR_BAD_ARG;
     int G = Hq / Hk;
     if (G > 32) return FSA_ERR_UNSUPPORTED;   // a tile needs >= 4 tokens per head row group
-    if (T > kMaxTopk || N >= kMaxTokens) return FSA_ERR_UNSUPPORTED;
+    if (T > kMaxTopk || N >= kMaxTokens || Nk >= kMaxTokens) return FSA_ERR_UNSUPPORTED;
     if (!(BK == 32 || BK == 64 || BK == 128 || BK == 256)) return FSA_ERR_UNSUPPORTED;
     if (D != 0 && !(D == 64 || D == 128 || D == 256)) return FSA_ERR_UNSUPPORTED;
-    s->N = N; s->B = B; s->Hq = Hq; s->Hk = Hk; s->G = G; s->D = D; s->T = T; s->BK = BK;
-    s->NBmax = (int)(N / BK) + B + 1;
+    s->N = N; s->Nk = Nk; s->B = B; s->Hq = Hq; s->Hk = Hk; s->G = G; s->D = D; s->T = T; s->BK = BK;
+    s->NBmax = (int)(Nk / BK) + B + 1;
     s->TPT = (kTileRows / G) & ~3;
     if ((int64_t)s->Hk * s->NBmax >= ((int64_t)1 << 30)) return FSA_ERR_UNSUPPORTED;
     if ((int64_t)s->Hk * N * T + (int64_t)s->Hk * s->NBmax * kTileRows >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
@@ -131,7 +132,7 @@ static int64_t bwd_dq_part_bytes(const SelShape& s) {
     return align_up(sel_max_tiles(s) * bwd_nsub(s.BK) * kTileRows * (int64_t)s.D * 2, 1024);
 }
 static int64_t bwd_scratch_bytes(const SelShape& s) {
-    return align_up(s.N * s.Hq * 4, 1024) + bwd_dq_part_bytes(s) + align_up(2 * s.N * s.Hk * (int64_t)s.D * 4, 256);
+    return align_up(s.N * s.Hq * 4, 1024) + bwd_dq_part_bytes(s) + align_up(2 * s.Nk * s.Hk * (int64_t)s.D * 4, 256);
 }
 
 static int64_t fwd_scratch_bytes(const SelShape& s) {
@@ -205,21 +206,23 @@ int fsa_sel_fwd_scratch_bytes(int64_t N, int B, int Hq, int Hk, int D, int T, in
     return FSA_OK;
 }
 
-int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk_idx, const int32_t* cu_seqlens,
-                int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int dtype, int64_t q_sn, int64_t q_sh,
+}  // extern "C"
+
+static int sel_fwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const void* k, const void* v, const int32_t* topk_idx,
+                        const int32_t* cu_seqlens, int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int dtype, int64_t q_sn, int64_t q_sh,
                 int64_t k_sn, int64_t v_sn, float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse,
                 void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     (void)cudaGetLastError();   // drop any stale error another library left on this thread
     SelShape s;
-    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s, Nk);
     if (rc) return rc;
     if ((rc = ensure_context()) != FSA_OK) return rc;
     if (D == 0) return FSA_ERR_BAD_ARG;
     if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
     if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;
     if (N == 0) return FSA_OK;
-    if (!q || !k || !v || !topk_idx || !cu_seqlens || !o || !lse || !index_ws || !scratch) return FSA_ERR_BAD_ARG;
+    if (!q || !k || !v || (!topk_idx && !bd.kv_hi) || !cu_seqlens || !o || !lse || !index_ws || !scratch) return FSA_ERR_BAD_ARG;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(scratch) || !aligned16(index_ws))
         return FSA_ERR_BAD_ARG;
     if ((q_sn % 8) || (q_sh % 8) || (k_sn % 8) || (v_sn % 8) || (o_sn % 8) || (o_sh % 8)) return FSA_ERR_BAD_ARG;
@@ -229,13 +232,13 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
     if (scratch_bytes < fwd_scratch_bytes(s)) return FSA_ERR_WORKSPACE;
 
     SelIndex ix = sel_index_carve(index_ws, s);
-    cudaError_t e = sel_build_index(topk_idx, cu_seqlens, s, ix, index_ws, stream);
+    cudaError_t e = sel_build_index(topk_idx, cu_seqlens, bd, s, ix, index_ws, stream);
     if (e != cudaSuccess) return cuda_fail(e);
 
     CUtensorMap kmap, vmap, omap;
-    rc = make_tile_map(&kmap, k, dtype, N, (int64_t)Hk * D, k_sn, BK);
+    rc = make_tile_map(&kmap, k, dtype, Nk, (int64_t)Hk * D, k_sn, BK);
     if (rc) return rc;
-    rc = make_tile_map(&vmap, v, dtype, N, (int64_t)Hk * D, v_sn, BK);
+    rc = make_tile_map(&vmap, v, dtype, Nk, (int64_t)Hk * D, v_sn, BK);
     if (rc) return rc;
     const int64_t prow = sel_max_tiles(s) * kTileRows;
     SelFwdArgs a;
@@ -245,6 +248,7 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
     a.ml = (float2*)((char*)scratch + align_up(prow * D * 2, 1024));
     a.o = o; a.o_sn = o_sn; a.o_sh = o_sh; a.lse = lse;
     a.kmap = &kmap; a.vmap = &vmap; a.qmap = nullptr; a.omap = nullptr;
+    a.bd = bd;
     if (D <= 128 && BK <= 128) {
         rc = make_tile_map(&omap, scratch, dtype, prow, D, D, 32);
         if (rc) return rc;
@@ -258,6 +262,29 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
     return FSA_OK;
 }
 
+
+extern "C" {
+
+int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk_idx, const int32_t* cu_seqlens,
+                int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int dtype, int64_t q_sn, int64_t q_sh,
+                int64_t k_sn, int64_t v_sn, float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse,
+                void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
+    if (!topk_idx) return FSA_ERR_BAD_ARG;
+    return sel_fwd_impl(SelBounds{nullptr, nullptr, nullptr}, N, q, k, v, topk_idx, cu_seqlens, N, B, Hq, Hk, D, T, BK, dtype, q_sn,
+                        q_sh, k_sn, v_sn, sm_scale, o, o_sn, o_sh, lse, index_ws, index_ws_bytes, scratch, scratch_bytes, stream_);
+}
+
+int fsa_range_attn_fwd(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                       const int32_t* kv_lo, const int32_t* kv_hi, int64_t N, int64_t Nk, int B, int Hq, int Hk, int D,
+                       int max_blocks, int BK, int dtype, int64_t q_sn, int64_t q_sh, int64_t k_sn, int64_t v_sn,
+                       float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse, void* index_ws,
+                       int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
+    if (!kv_hi || !cu_seqlens_k) return FSA_ERR_BAD_ARG;
+    return sel_fwd_impl(SelBounds{cu_seqlens_k, kv_lo, kv_hi}, Nk, q, k, v, nullptr, cu_seqlens_q, N, B, Hq, Hk, D, max_blocks, BK,
+                        dtype, q_sn, q_sh, k_sn, v_sn, sm_scale, o, o_sn, o_sh, lse, index_ws, index_ws_bytes, scratch,
+                        scratch_bytes, stream_);
+}
+
 int fsa_sel_bwd_scratch_bytes(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, int64_t* bytes_out) {
     if (!bytes_out) return FSA_ERR_BAD_ARG;
     SelShape s;
@@ -267,22 +294,24 @@ int fsa_sel_bwd_scratch_bytes(int64_t N, int B, int Hq, int Hk, int D, int T, in
     return FSA_OK;
 }
 
-int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
-                const int32_t* topk_idx, const int32_t* cu_seqlens, int64_t N, int B, int Hq, int Hk, int D, int T,
+}  // extern "C"
+
+static int sel_bwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                        const void* d_o, const int32_t* topk_idx, const int32_t* cu_seqlens, int64_t N, int B, int Hq, int Hk, int D, int T,
                 int BK, int dtype, int64_t q_sn, int64_t q_sh, int64_t k_sn, int64_t v_sn, int64_t o_sn, int64_t o_sh,
                 int64_t do_sn, int64_t do_sh, float sm_scale, void* dq, void* dk, void* dv, void* index_ws,
                 int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     (void)cudaGetLastError();   // drop any stale error another library left on this thread
     SelShape s;
-    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
+    int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s, Nk);
     if (rc) return rc;
     if ((rc = ensure_context()) != FSA_OK) return rc;
     if (D == 0) return FSA_ERR_BAD_ARG;
     if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
     if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;
     if (N == 0) return FSA_OK;
-    if (!q || !k || !v || !o || !lse || !d_o || !topk_idx || !cu_seqlens || !dq || !dk || !dv || !index_ws || !scratch)
+    if (!q || !k || !v || !o || !lse || !d_o || !cu_seqlens || !dq || !dk || !dv || !index_ws || !scratch)
         return FSA_ERR_BAD_ARG;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
         !aligned16(dk) || !aligned16(dv) || !aligned16(scratch) || !aligned16(index_ws))
@@ -295,9 +324,9 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
 
     SelIndex ix = sel_index_carve(index_ws, s);
     CUtensorMap kmap, vmap;
-    rc = make_tile_map(&kmap, k, dtype, N, (int64_t)Hk * D, k_sn, 64);
+    rc = make_tile_map(&kmap, k, dtype, Nk, (int64_t)Hk * D, k_sn, 64);
     if (rc) return rc;
-    rc = make_tile_map(&vmap, v, dtype, N, (int64_t)Hk * D, v_sn, 64);
+    rc = make_tile_map(&vmap, v, dtype, Nk, (int64_t)Hk * D, v_sn, 64);
     if (rc) return rc;
     int sms = 0;
     rc = device_sm_count(&sms);
@@ -313,10 +342,47 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
     a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 1024);
     a.dq_part = (void*)sp;  sp += bwd_dq_part_bytes(s);
     a.dk_acc = (float*)sp;
-    a.dv_acc = a.dk_acc + N * Hk * (int64_t)D;
+    a.dv_acc = a.dk_acc + Nk * Hk * (int64_t)D;
+    a.bd = bd;
     a.dq = dq; a.dk = dk; a.dv = dv;
     cudaError_t e = dispatch_sel_bwd(dtype, a, s, ix, kmap, vmap, sms, stream);
     if (e != cudaSuccess) return cuda_fail(e);
+    return FSA_OK;
+}
+
+
+extern "C" {
+
+int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                const int32_t* topk_idx, const int32_t* cu_seqlens, int64_t N, int B, int Hq, int Hk, int D, int T,
+                int BK, int dtype, int64_t q_sn, int64_t q_sh, int64_t k_sn, int64_t v_sn, int64_t o_sn, int64_t o_sh,
+                int64_t do_sn, int64_t do_sh, float sm_scale, void* dq, void* dk, void* dv, void* index_ws,
+                int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream_) {
+    return sel_bwd_impl(SelBounds{nullptr, nullptr, nullptr}, N, q, k, v, o, lse, d_o, topk_idx, cu_seqlens, N, B, Hq, Hk, D, T, BK,
+                        dtype, q_sn, q_sh, k_sn, v_sn, o_sn, o_sh, do_sn, do_sh, sm_scale, dq, dk, dv, index_ws, index_ws_bytes,
+                        scratch, scratch_bytes, stream_);
+}
+
+int fsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                       const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* kv_lo, const int32_t* kv_hi,
+                       int64_t N, int64_t Nk, int B, int Hq, int Hk, int D, int max_blocks, int BK, int dtype, int64_t q_sn,
+                       int64_t q_sh, int64_t k_sn, int64_t v_sn, int64_t o_sn, int64_t o_sh, int64_t do_sn, int64_t do_sh,
+                       float sm_scale, void* dq, void* dk, void* dv, void* index_ws, int64_t index_ws_bytes, void* scratch,
+                       int64_t scratch_bytes, void* stream_) {
+    if (!kv_hi || !cu_seqlens_k) return FSA_ERR_BAD_ARG;
+    return sel_bwd_impl(SelBounds{cu_seqlens_k, kv_lo, kv_hi}, Nk, q, k, v, o, lse, d_o, nullptr, cu_seqlens_q, N, B, Hq, Hk, D,
+                        max_blocks, BK, dtype, q_sn, q_sh, k_sn, v_sn, o_sn, o_sh, do_sn, do_sh, sm_scale, dq, dk, dv, index_ws,
+                        index_ws_bytes, scratch, scratch_bytes, stream_);
+}
+
+int fsa_range_attn_bytes(int64_t N, int64_t Nk, int B, int Hq, int Hk, int D, int max_blocks, int BK, int64_t* index_bytes_out,
+                         int64_t* fwd_scratch_bytes_out, int64_t* bwd_scratch_bytes_out) {
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, D, max_blocks, BK, &s, Nk);
+    if (rc) return rc;
+    if (index_bytes_out) *index_bytes_out = sel_index_bytes(s);
+    if (fwd_scratch_bytes_out) *fwd_scratch_bytes_out = fwd_scratch_bytes(s);
+    if (bwd_scratch_bytes_out) *bwd_scratch_bytes_out = bwd_scratch_bytes(s);
     return FSA_OK;
 }
 

@@ -30,6 +30,7 @@ struct SelBwdParams {
     SelShape s;
     SelIndex ix;
     int nsub;              // 64-key sub-tiles per block
+    SelBounds bd;          // visible K/V rows per token
     float scale, scale_log2;
     ET* dq_part;           // [max_tiles * nsub * 128, D] partial dQ rows in tile order (input dtype)
     float* dk_acc;         // [N, Hk, D] fp32, zero-initialised
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
                         for (int i = 0; i < 32; ++i) {
                             int key = c0 + i;
                             int64_t row = (int64_t)cur_row0 + key;
-                            if (key < key_lim && row < s.N)
+                            if (key < key_lim && row < s.Nk)
                                 atomicAdd(acc + (row * s.Hk + cur_h) * D + d, __uint_as_float(v[i]));
                         }
                     }
@@ -239,7 +240,8 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
 
         // ---- stage 4: P and dS rows -> smem (K-major rows of 64 keys)
         {
-            int nvis = row_valid ? min(min(kKT, s.BK), tok - row0 + 1) : 0;   // may be <= 0: nothing visible
+            int c_lo = 0, c_hi = 0;   // may be empty: nothing visible
+            if (row_valid) visible_cols(p.bd, tok, row0, min(kKT, s.BK), c_lo, c_hi);
 #pragma unroll
             for (int c0 = 0; c0 < kKT; c0 += 32) {
                 uint32_t sv[32], dv[32];
@@ -252,8 +254,8 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         int i = ch * 8 + j * 2;
-                        float p0 = (c0 + i < nvis) ? exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
-                        float p1 = (c0 + i + 1 < nvis) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                        float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                        float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
                         float d0 = p0 * (__uint_as_float(dv[i]) - delta_r) * p.scale;
                         float d1 = p1 * (__uint_as_float(dv[i + 1]) - delta_r) * p.scale;
                         pp[j] = ElemTraits<ET>::pack2(p0, p1);
@@ -451,7 +453,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
                                   const CUtensorMap& vmap, int num_sms, cudaStream_t stream) {
     const int nsub = s.BK > kKT ? s.BK / kKT : 1;
     const int64_t rows = s.N * s.Hq;
-    const int64_t kv_elems = s.N * s.Hk * (int64_t)D;
+    const int64_t kv_elems = s.Nk * s.Hk * (int64_t)D;
     cudaError_t e = cudaMemsetAsync(a.dk_acc, 0, kv_elems * 4 * 2, stream);   // dk_acc and dv_acc are adjacent
     if (e != cudaSuccess) return e;
     if (rows > 0) {
@@ -463,7 +465,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.q = (const ET*)a.q; p.q_sn = a.q_sn; p.q_sh = a.q_sh;
     p.d_o = (const ET*)a.d_o; p.do_sn = a.do_sn; p.do_sh = a.do_sh;
     p.lse = a.lse; p.delta = a.delta;
-    p.s = s; p.ix = ix; p.nsub = nsub;
+    p.s = s; p.ix = ix; p.nsub = nsub; p.bd = a.bd;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     if (D == 128 && s.BK <= kKT && !a.force_simple) {

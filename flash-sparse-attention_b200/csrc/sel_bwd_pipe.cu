@@ -27,6 +27,7 @@ struct SelBwdPipeParams {
     SelIndex ix;
     float scale, scale_log2;
     int run;
+    SelBounds bd;      // visible K/V rows per token
     ET* dq_part;       // [max_tiles * 128, D]
     float* dk_acc;     // [N, Hk, D] fp32, zero-initialised
     float* dv_acc;
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             while (k2 < nloc && load_tile(p.ix, sched.tile(k2)).hg == ti.hg) ++k2;   // tiles [k, k2) form the block
             ok = mbar_wait(acc_full, nflush & 1, status) && ok;
             tc_fence_after();
-            const int nkeys = (int)min((int64_t)key_lim, s.N - ti.row0);
+            const int nkeys = (int)min((int64_t)key_lim, s.Nk - ti.row0);
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
                 uint32_t v[KT];
@@ -345,6 +346,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         uint32_t entA = 0xFFFFFFFFu;            // entry of tile k (after rotation)
         int row0A = 0, row0B = 0, hA = 0, hB = 0;
         float lseA = 0.f, deltaA = 0.f;
+        int cloA = 0, chiA = 0;
         auto fetch_ent = [&](int k, uint32_t& ent, int& row0, int& h) {
             const int j = sched.tile(k);
             TileInfo ti = load_tile(p.ix, j);
@@ -352,31 +354,31 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             ent = 0xFFFFFFFFu;
             if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);
         };
-        auto fetch_stats = [&](uint32_t ent, int h, float& lse_, float& delta_) {
-            lse_ = 0.f; delta_ = 0.f;
+        auto fetch_stats = [&](uint32_t ent, int h, int row0, float& lse_, float& delta_, int& c_lo, int& c_hi) {
+            lse_ = 0.f; delta_ = 0.f; c_lo = 0; c_hi = 0;    // padding rows: nothing visible
             if (ent != 0xFFFFFFFFu) {
-                const int64_t idx = (int64_t)(h * s.G + g) * s.N + (ent >> kSlotBits);
+                const int tok_ = (int)(ent >> kSlotBits);
+                const int64_t idx = (int64_t)(h * s.G + g) * s.N + tok_;
                 lse_ = __ldg(p.lse + idx);
                 delta_ = __ldg(p.delta + idx);
+                visible_cols(p.bd, tok_, row0, key_lim, c_lo, c_hi);
             }
         };
         if (sb < nloc) {
             fetch_ent(sb, entA, row0A, hA);
-            fetch_stats(entA, hA, lseA, deltaA);
+            fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
         }
         if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B, hB);
         for (int k = sb; k < nloc && ok; k += 2) {
             const int j = sched.tile(k);
             const uint32_t ent = entA;
-            const int row0 = row0A;
             const float lse_r = lseA, delta_r = deltaA;
+            const int c_lo = cloA, c_hi = chiA;
             // rotate the prefetch registers
             entA = entB; row0A = row0B; hA = hB;
-            if (k + 2 < nloc) fetch_stats(entA, hA, lseA, deltaA);
+            if (k + 2 < nloc) fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
             if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B, hB);
             const bool row_valid = ent != 0xFFFFFFFFu;
-            const int tok = (int)(ent >> kSlotBits);
-            const int nvis = row_valid ? min(key_lim, tok - row0 + 1) : 0;   // may be <= 0
             ok = mbar_wait(&sdp_full[sb], (k >> 1) & 1, status) && ok;
             tc_fence_after();
             uint32_t pp[KT / 2], dd[KT / 2];
@@ -388,8 +390,8 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = (c0 + i < nvis) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
-                    float p1 = (c0 + i + 1 < nvis) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                    float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                    float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
                     float d0 = p0 * (__uint_as_float(dv[i]) - delta_r) * p.scale;
                     float d1 = p1 * (__uint_as_float(dv[i + 1]) - delta_r) * p.scale;
                     pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
@@ -447,6 +449,7 @@ static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const Sel
     p.s = s; p.ix = ix;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.run = a.run > 0 ? a.run : 8;
+    p.bd = a.bd;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     auto kern = sel_bwd_pipe<ET>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwdpipe::kBytes);

@@ -28,7 +28,8 @@ constexpr int64_t kMaxTokens = (int64_t)1 << (31 - kSlotBits);
 enum DType : int { kBF16 = 0, kFP16 = 1 };
 
 struct SelShape {
-    int64_t N;       // total packed tokens
+    int64_t N;       // total packed (query) tokens
+    int64_t Nk;      // rows of K / V (= N for selected attention; compressed tokens for the compressed branch)
     int B;           // sequences
     int Hq, Hk, G;   // heads, G = Hq / Hk
     int D;           // head dim
@@ -39,6 +40,16 @@ struct SelShape {
 };
 
 // Index workspace (kept by the caller between forward and backward).  All int32.
+// Which K/V rows a token may attend.  Selected attention: kv_lo = kv_hi = null, the rule is the
+// causal one (rows <= the token's own row) and the blocks come from topk_idx.  Range mode
+// (compressed and sliding-window branches): every token attends the K/V rows [kv_lo[n], kv_hi[n]]
+// (global row ids, empty when hi < lo) and "selects" every block that range touches.
+struct SelBounds {
+    const int* cu_k;     // [B+1] sequence starts in K/V rows (null: same as the query cu_seqlens)
+    const int* kv_lo;    // [N] or null
+    const int* kv_hi;    // [N] or null
+};
+
 struct SelIndex {
     int* header;     // [64]: [0] status, [1] total tiles
     int* counts;     // [Hk * NBmax]   entries per hg
@@ -101,14 +112,38 @@ __device__ __forceinline__ int find_seq(const int* __restrict__ cu, int B, int n
     return lo;
 }
 
-// A slot is usable when 0 <= id <= t_local / BK (nsa_ref/ops/topk_sparse_attention.py:116-119).
-__device__ __forceinline__ int entry_block(const int* __restrict__ cu, int B, int BK, int n, int id, int* row0_out) {
-    int b = find_seq(cu, B, n);
-    int c = __ldg(cu + b);
-    int t_local = n - c;
-    if (id < 0 || id > t_local / BK) return -1;
-    *row0_out = c + id * BK;
-    return c / BK + b + id;
+// Block of slot `sl` of token n, or -1.  List mode: a slot is usable when 0 <= id <= t_local / BK
+// (nsa_ref/ops/topk_sparse_attention.py:116-119).  Range mode: slot sl is the sl-th block touched by
+// [kv_lo[n], kv_hi[n]].
+__device__ __forceinline__ int entry_block(const int* __restrict__ cu, const SelBounds& bd, int B, int BK, int n, int sl,
+                                           const int* __restrict__ idrow, int* row0_out) {
+    const int b = find_seq(cu, B, n);
+    const int c = __ldg(cu + b);
+    const int ck = bd.cu_k ? __ldg(bd.cu_k + b) : c;
+    int id;
+    if (bd.kv_hi) {
+        const int lo = bd.kv_lo ? __ldg(bd.kv_lo + n) : ck, hi = __ldg(bd.kv_hi + n);
+        if (hi < lo) return -1;
+        id = (lo - ck) / BK + sl;
+        if (id > (hi - ck) / BK) return -1;
+    } else {
+        id = __ldg(idrow + sl);
+        if (id < 0 || id > (n - c) / BK) return -1;
+    }
+    *row0_out = ck + id * BK;
+    return ck / BK + b + id;
+}
+
+// Visible key columns [c_lo, c_hi) of a tile row whose block starts at K/V row `row0` and holds
+// `klim` keys: list mode is causal (rows <= tok); range mode uses the per-token bounds.
+__device__ __forceinline__ void visible_cols(const SelBounds& bd, int tok, int row0, int klim, int& c_lo, int& c_hi) {
+    int lo = row0, hi = tok;
+    if (bd.kv_hi) {
+        hi = __ldg(bd.kv_hi + tok);
+        if (bd.kv_lo) lo = __ldg(bd.kv_lo + tok);
+    }
+    c_lo = max(0, lo - row0);
+    c_hi = min(klim, hi - row0 + 1);
 }
 
 // largest i in [0, n) with off[i] <= x  (off ascending, off[0] = 0)

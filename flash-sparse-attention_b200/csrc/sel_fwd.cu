@@ -32,6 +32,7 @@ struct SelFwdParams {
     SelIndex ix;
     float scale_log2;        // softmax scale * log2(e)
     int run;                 // tiles per scheduling run (see TileSchedule)
+    SelBounds bd;            // visible K/V rows per token
     int dbg;                 // debug builds only: bit 0 skip Q copies, bit 1 skip partial stores
     ET* opart;               // [max_tiles * 128, D]  unnormalised partial outputs, tile order
     float2* ml;              // [max_tiles * 128]     (row max in log2 units, row sum)
@@ -349,13 +350,20 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
         const uint32_t tO = tbase + lane_off + C::cO + sb * D;
         bool ok = true;
         T_DECL;
-        // prefetched entry of this thread's row in the group's next tile
+        // software pipeline over this group's tiles: the entry of this thread's row is fetched two
+        // own tiles ahead, the visible-column bounds (which may need the token's row limits) one ahead
         const bool row_exists = g < s.G;
-        uint32_t n_ent = 0xFFFFFFFFu; int n_row0 = 0;
-        auto prefetch = [&](int j) {
-            n_row0 = load_tile(p.ix, j).row0;
-            n_ent = 0xFFFFFFFFu;
-            if (row_exists) n_ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);   // consumed one iteration later
+        uint32_t entA = 0xFFFFFFFFu, entB = 0xFFFFFFFFu;
+        int row0A = 0, row0B = 0, cloA = 0, chiA = BK;
+        auto fetch_ent = [&](int k, uint32_t& ent, int& row0) {
+            const int j = sched.tile(k);
+            row0 = load_tile(p.ix, j).row0;
+            ent = 0xFFFFFFFFu;
+            if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);
+        };
+        auto fetch_bounds = [&](uint32_t ent, int row0, int& c_lo, int& c_hi) {
+            c_lo = 0; c_hi = BK;   // padding rows: anything finite
+            if (ent != 0xFFFFFFFFu) visible_cols(p.bd, (int)(ent >> kSlotBits), row0, BK, c_lo, c_hi);
         };
         bool have_prev = false, prev_valid = false;
         int prev_j = 0, prev_u = 0;
@@ -405,17 +413,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             T_TOC(5);
             if (quarter == 2 && lane == 0) TR(3, prev_u * 2 + sb, 3);
         };
-        if (sb < nloc) prefetch(sched.tile(sb));
+        if (sb < nloc) {
+            fetch_ent(sb, entA, row0A);
+            fetch_bounds(entA, row0A, cloA, chiA);
+        }
+        if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B);
         for (int k = sb; k < nloc && ok; k += 2) {
             const int j = sched.tile(k);
             const int u = k >> 1;                     // use count of this group's O buffer
             const int sbuf = k % C::NS;
             const uint32_t tS = tS0 + sbuf * BK;
-            const bool row_valid = n_ent != 0xFFFFFFFFu;
-            const int tok = (int)(n_ent >> kSlotBits);
-            const int nvis = row_valid ? min(BK, tok - n_row0 + 1) : BK;   // causal: key row0 + c <= tok
+            const bool row_valid = entA != 0xFFFFFFFFu;
+            const int c_lo = cloA, c_hi = chiA;            // visible key columns of this row
+            entA = entB; row0A = row0B;
             T_TIC;
-            if (k + 2 < nloc) prefetch(sched.tile(k + 2));
+            if (k + 2 < nloc) fetch_bounds(entA, row0A, cloA, chiA);
+            if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B);
             T_TOC(0);
             ok = mbar_wait(&s_full[sbuf], (k / C::NS) & 1, status) && ok;
             T_TOC(1);
@@ -434,10 +447,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
                     }
                     tmem_ld_wait();
                 }
-                if (nvis < BK) {
+                if (c_lo > 0 || c_hi < BK) {
 #pragma unroll
                     for (int i = 0; i < BK; ++i)
-                        if (i >= nvis) v[i] = 0xff800000u;   // -inf: exp2 gives exactly 0
+                        if (i < c_lo || i >= c_hi) v[i] = 0xff800000u;   // -inf: exp2 gives exactly 0
                 }
                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -475,7 +488,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (c0 + i < nvis) mx = fmaxf(mx, __uint_as_float(v[i]));
+                        if (c0 + i >= c_lo && c0 + i < c_hi) mx = fmaxf(mx, __uint_as_float(v[i]));
                 }
                 m = mx * p.scale_log2;
                 l = 0.f;
@@ -487,8 +500,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float p0 = (c0 + i < nvis) ? ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m)) : 0.f;
-                        float p1 = (c0 + i + 1 < nvis) ? ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m)) : 0.f;
+                        float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m)) : 0.f;
+                        float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m)) : 0.f;
                         l += p0 + p1;
                         pk[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
                     }
@@ -614,7 +627,8 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> 
         const int g = r / s.TPT, e = r - g * s.TPT;
         const bool row_valid = g < s.G && e < w.ne;
         const int tok = row_valid ? (int)(s_ent[e] >> kSlotBits) : 0;
-        const int nvis = row_valid ? min(BK, tok - w.row0 + 1) : BK;
+        int c_lo = 0, c_hi = BK;
+        if (row_valid) visible_cols(p.bd, tok, w.row0, BK, c_lo, c_hi);
         float mx = -INFINITY;
 #pragma unroll 2
         for (int c0 = 0; c0 < BK; c0 += 32) {
@@ -623,7 +637,7 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> 
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                if (c0 + i < nvis) mx = fmaxf(mx, __uint_as_float(v[i]));
+                if (c0 + i >= c_lo && c0 + i < c_hi) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
         const float m = mx * p.scale_log2;
         float l = 0.f;
@@ -635,8 +649,8 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> 
             uint32_t pk[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float p0 = (c0 + i < nvis) ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m)) : 0.f;
-                float p1 = (c0 + i + 1 < nvis) ? exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m)) : 0.f;
+                float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m)) : 0.f;
+                float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m)) : 0.f;
                 l += p0 + p1;
                 pk[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
             }
@@ -781,6 +795,7 @@ static cudaError_t launch_sel_fwd(const SelFwdArgs& a, const SelShape& s, const 
     p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.opart = (ET*)a.opart; p.ml = a.ml;
     p.run = a.run > 0 ? a.run : 8;
+    p.bd = a.bd;
     p.dbg = 0;
 #ifdef FSA_TIMING
     { const char* v = getenv("FSA_DBG"); p.dbg = v ? atoi(v) : 0; }

@@ -10,7 +10,7 @@ namespace fsa {
 
 template <bool FILL>
 __global__ void __launch_bounds__(256) sel_index_pass(const int* __restrict__ topk_idx, const int* __restrict__ cu,
-                                                      SelShape s, SelIndex ix) {
+                                                      SelBounds bd, SelShape s, SelIndex ix) {
     int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = (int64_t)s.Hk * s.N;
     bool active = gid < total;
@@ -20,9 +20,8 @@ __global__ void __launch_bounds__(256) sel_index_pass(const int* __restrict__ to
     unsigned lane = threadIdx.x & 31;
     unsigned lt = (1u << lane) - 1;
     for (int sl = 0; sl < s.T; ++sl) {
-        int id = active ? __ldg(row + sl) : -1;
         int r0 = 0;
-        int gb = active ? entry_block(cu, s.B, s.BK, n, id, &r0) : -1;
+        int gb = active ? entry_block(cu, bd, s.B, s.BK, n, sl, row, &r0) : -1;
         int key = gb < 0 ? -1 : h * s.NBmax + gb;
         unsigned m = __match_any_sync(0xffffffffu, key);
         if (key >= 0) {
@@ -108,17 +107,17 @@ __global__ void __launch_bounds__(256) sel_index_tiles(SelShape s, SelIndex ix) 
     for (int e = used + lane; e < s.TPT; e += 32) ix.entries[(int64_t)(t0 + nt - 1) * s.TPT + e] = 0xFFFFFFFFu;
 }
 
-cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
-                            cudaStream_t stream) {
+cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelBounds& bd, const SelShape& s, const SelIndex& ix,
+                            void* ws, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(ws, 0, sel_index_zero_bytes(s), stream);
     if (e != cudaSuccess) return e;
     int64_t total = (int64_t)s.Hk * s.N;
     if (total == 0) return cudaSuccess;
     unsigned grid = (unsigned)((total + 255) / 256);
-    sel_index_pass<false><<<grid, 256, 0, stream>>>(topk_idx, cu, s, ix);
+    sel_index_pass<false><<<grid, 256, 0, stream>>>(topk_idx, cu, bd, s, ix);
     sel_index_scan<<<1, 1024, 0, stream>>>(s, ix);
     sel_index_tiles<<<(unsigned)((s.Hk * s.NBmax + 7) / 8), 256, 0, stream>>>(s, ix);
-    sel_index_pass<true><<<grid, 256, 0, stream>>>(topk_idx, cu, s, ix);
+    sel_index_pass<true><<<grid, 256, 0, stream>>>(topk_idx, cu, bd, s, ix);
     return cudaGetLastError();
 }
 

@@ -10,8 +10,8 @@ namespace fsa {
 void prof_begin(int kernel_id, cudaStream_t stream);
 void prof_end(int kernel_id, cudaStream_t stream);
 
-cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelShape& s, const SelIndex& ix, void* ws,
-                            cudaStream_t stream);
+cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelBounds& bd, const SelShape& s, const SelIndex& ix,
+                            void* ws, cudaStream_t stream);
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -31,6 +31,7 @@ struct SelFwdArgs {
     const CUtensorMap* kmap;  // [N, Hk*D] box {64, BK}
     const CUtensorMap* vmap;
     const CUtensorMap* omap;  // [max_tiles * 128, D] box {64, 32} for the partial stores
+    SelBounds bd;             // visible K/V rows per token (all null: causal rule of selected attention)
 };
 
 cudaError_t dispatch_sel_fwd(int dtype, const SelFwdArgs& a, const SelShape& s, const SelIndex& ix, int num_sms,
@@ -52,6 +53,7 @@ struct SelBwdArgs {
     float* dv_acc;
     // outputs (contiguous)
     void *dq, *dk, *dv;
+    SelBounds bd;      // visible K/V rows per token (all null: causal rule of selected attention)
 };
 
 // pipelined main kernel for head_dim 128, block size <= 64 (sel_bwd_pipe.cu)

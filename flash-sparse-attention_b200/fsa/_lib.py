@@ -53,6 +53,30 @@ SIGNATURES = {
          c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
          c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p],
     ),
+    "fsa_range_attn_bytes": (c_int, [c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64),
+                                     POINTER(c_int64), POINTER(c_int64)]),
+    "fsa_range_attn_fwd": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p, c_int64, c_int64, c_void_p,
+         c_void_p, c_int64, c_void_p, c_int64, c_void_p],
+    ),
+    "fsa_range_attn_bwd": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+         c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+         c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p],
+    ),
+    "fsa_select_topk_seq": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
+         c_int, c_int, c_void_p, c_void_p],
+    ),
+    "fsa_rope": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
+                         c_void_p, c_void_p]),
+    "fsa_gate_mix_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "fsa_gate_mix_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p]),
     "fsa_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
     "fsa_sel_index_dump": (
         c_int,

@@ -1,0 +1,91 @@
+"""Compressed-branch attention + top-k block selection with the reference's interface
+(``compressed_attention``, nsa_ref/ops/compressed_attention.py:1161-1317).
+
+The attention itself runs on the sm_100a range-attention kernels; the selection scores are the
+raw products of the first query head of each GQA group with the compressed keys (one batched
+library GEMM per sequence, fp32 out) fed to the fused exp / block-score / top-k kernel.
+"""
+from __future__ import annotations
+
+import math
+import warnings
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from fsa import _lib
+from fsa.ops.range_attention import compressed_attention_core
+
+
+def select_topk_blocks(q, ck, lse, kernel_size, kernel_stride, block_size, topk, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+                       sm_scale, init_blocks=1, local_blocks=2, seqlens_q: Optional[Sequence[int]] = None,
+                       seqlens_k: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """``topk_idx [Hk, N, min(topk, max_blocks)]`` int32: ascending sequence-local block ids, -1 padded."""
+    L = _lib.lib()
+    N, Hq, d = q.shape
+    Hk = ck.shape[1]
+    G = Hq // Hk
+    max_blocks = math.ceil(max_seqlen_q / block_size)
+    t_out = min(topk, max_blocks)
+    if seqlens_q is None:
+        seqlens_q = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).tolist()
+    if seqlens_k is None:
+        seqlens_k = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).tolist()
+    out = torch.empty((Hk, N, t_out), dtype=torch.int32, device=q.device)
+    lse = lse.contiguous()
+    qs = ks = 0
+    with torch.cuda.device(q.device):
+        for Lq, Lk in zip(seqlens_q, seqlens_k):
+            if Lq > 0:
+                q0 = q[qs : qs + Lq, ::G].transpose(0, 1)                 # [Hk, Lq, d] first head of each group
+                kk = ck[ks : ks + Lk].permute(1, 2, 0)                    # [Hk, d, Lk]
+                ld = max((Lk + 3) // 4 * 4, 4)
+                qk = torch.empty((Hk, Lq, ld), dtype=torch.float32, device=q.device)
+                if Lk > 0:
+                    qk[:, :, :Lk] = torch.bmm(q0.float(), kk.float())
+                rc = L.fsa_select_topk_seq(_lib.ptr(qk), ld, _lib.ptr(lse), N, qs, Lq, Lk, Hk, G, float(sm_scale), kernel_size,
+                                           kernel_stride, block_size, init_blocks, local_blocks, max_blocks, t_out, _lib.ptr(out),
+                                           _lib.current_stream(q.device))
+                _lib.check(rc, "fsa_select_topk_seq")
+            qs += Lq
+            ks += Lk
+    return out
+
+
+def compressed_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    kernel_size: int,
+    kernel_stride: int,
+    block_size: int,
+    topk: int,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    sm_scale: float = None,
+    init_blocks: int = 1,
+    local_blocks: int = 2,
+    parallel_topk_compute="auto",
+    seqlens_q: Optional[Sequence[int]] = None,
+    seqlens_k: Optional[Sequence[int]] = None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Attention between queries and compressed keys/values, and the top-k block ids for the
+    selected branch.  Same arguments and return contract as the reference; ``parallel_topk_compute``
+    is accepted and ignored (there is one selection kernel)."""
+    if max_seqlen_q is None:
+        max_seqlen_q = int((cu_seqlens_q[1:] - cu_seqlens_q[:-1]).max().item())
+    if max_seqlen_k is None:
+        max_seqlen_k = int((cu_seqlens_k[1:] - cu_seqlens_k[:-1]).max().item())
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    o, lse = compressed_attention_core(q, k, v, kernel_size, kernel_stride, cu_seqlens_q, cu_seqlens_k, max_seqlen_k, sm_scale)
+    if topk <= 0:
+        warnings.warn("topk <= 0, returned topk_idx will be None")
+        return o, None
+    assert topk >= init_blocks + local_blocks
+    with torch.no_grad():
+        topk_idx = select_topk_blocks(q.detach(), k.detach(), lse, kernel_size, kernel_stride, block_size, topk, cu_seqlens_q,
+                                      cu_seqlens_k, max_seqlen_q, sm_scale, init_blocks, local_blocks, seqlens_q, seqlens_k)
+    return o, topk_idx

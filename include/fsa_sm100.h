@@ -127,6 +127,71 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
                 int64_t do_stride_n, int64_t do_stride_h, float sm_scale, void* dq, void* dk, void* dv,
                 void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Range attention: the compressed branch and the sliding-window branch
+ * ------------------------------------------------------------------------------------------- */
+
+/* Attention in which token n attends the K/V rows kv_lo[n] .. kv_hi[n] (global row ids of k / v, which may
+ * have their own packing cu_seqlens_k; nothing when kv_hi[n] < kv_lo[n]; kv_lo may be null = from the start of
+ * the sequence).  It runs on the selected-attention kernels: every token "selects" the block_size-row
+ * blocks its range touches (at most max_blocks <= 64 of them), rows outside the range are masked.
+ *   compressed branch  - replaces CompressedAttention forward/backward and their kernels
+ *       (nsa_ref/ops/compressed_attention.py:28-156, 160-545, 762-829): k/v are the compressed tokens,
+ *       kv_hi[n] = cu_k[b] + floor((t_local - kernel_size + 1) / kernel_stride), or -1 when t_local < kernel_size - 1
+ *       (the mask `t >= c * stride + kernel_size - 1`, :77-80); such rows get o = 0, lse = -inf (:548-553);
+ *   sliding window     - replaces flash_attn_varlen_func(causal=True, window_size=(W, -1)) as called in
+ *       fsa/module/fsa.py:149-159: kv_lo[n] = max(cu[b], n - W), kv_hi[n] = n.
+ * Tensors, strides, dtype, lse (log2 units), workspaces and return codes are as for fsa_sel_fwd / fsa_sel_bwd;
+ * fsa_range_attn_bytes returns the three workspace sizes (any out pointer may be null). */
+int fsa_range_attn_bytes(int64_t total_tokens, int64_t total_kv_rows, int batch, int num_q_heads, int num_kv_heads,
+                         int head_dim, int max_blocks, int block_size, int64_t* index_bytes_out,
+                         int64_t* fwd_scratch_bytes_out, int64_t* bwd_scratch_bytes_out);
+int fsa_range_attn_fwd(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                       const int32_t* cu_seqlens_k, const int32_t* kv_lo, const int32_t* kv_hi, int64_t total_tokens,
+                       int64_t total_kv_rows, int batch, int num_q_heads, int num_kv_heads, int head_dim, int max_blocks,
+                       int block_size, int dtype, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t v_stride_n, float sm_scale, void* o, int64_t o_stride_n, int64_t o_stride_h, float* lse,
+                       void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes, void* stream);
+int fsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                       const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* kv_lo,
+                       const int32_t* kv_hi, int64_t total_tokens, int64_t total_kv_rows, int batch, int num_q_heads,
+                       int num_kv_heads, int head_dim, int max_blocks, int block_size, int dtype, int64_t q_stride_n,
+                       int64_t q_stride_h, int64_t k_stride_n, int64_t v_stride_n, int64_t o_stride_n,
+                       int64_t o_stride_h, int64_t do_stride_n, int64_t do_stride_h, float sm_scale, void* dq, void* dk,
+                       void* dv, void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes,
+                       void* stream);
+
+/* Top-k block selection for one sequence.  Replaces _get_attention_score / score_kernel, transform_score /
+ * _transform_score_kernel and the topk + sort + mask tail (nsa_ref/ops/compressed_attention.py:833-1158,
+ * :1274-1315; per-KV-head path).
+ *   qk [Hk, seq_len, ld] fp32: raw dot products of the FIRST query head of each GQA group with the num_cmp
+ *   compressed keys of this sequence (a library GEMM); lse [Hq, total_tokens] of the compressed branch (log2);
+ *   topk_idx [Hk, total_tokens, topk_out] int32 receives, for the tokens of this sequence, ascending
+ *   sequence-local block ids, -1 padded.  Scores are rounded to bf16 as in the reference; ties go to the lower
+ *   block index (the reference leaves tie order to torch.topk).  topk_out = min(topk, max_blocks),
+ *   max_blocks = ceil(max_seqlen / block_size). */
+int fsa_select_topk_seq(const float* qk, int64_t ld, const float* lse, int64_t total_tokens, int seq_start, int seq_len,
+                        int num_cmp, int num_kv_heads, int group, float sm_scale, int kernel_size, int kernel_stride,
+                        int block_size, int init_blocks, int local_blocks, int max_blocks, int topk_out,
+                        int32_t* topk_idx, void* stream);
+
+/* Rotary embedding, half-split layout, positions restarting per sequence.  Replaces the flash-attn
+ * apply_rotary_emb call of RotaryEmbedding.forward (nsa_ref/module/rope.py:126-134).  x [total, heads, head_dim]
+ * with element strides; cos_tab / sin_tab [table_len, head_dim / 2] in the activation dtype, row p = position
+ * start + p * stride (the caller builds the table that way, rope.py:130); out is contiguous.  conj != 0
+ * applies the inverse rotation (backward). */
+int fsa_rope(const void* x, int64_t x_stride_n, int64_t x_stride_h, const void* cos_tab, const void* sin_tab,
+             const int32_t* cu_seqlens, int batch, int64_t total, int heads, int head_dim, int dtype, int conj, void* out,
+             void* stream);
+
+/* Gate mix of the three branches (fsa/module/fsa.py:162-167): out = g0 a + g1 b + g2 c with gate [total, 3]
+ * (already through the sigmoid) and a, b, c, out contiguous [total, row_elems].  The backward also returns
+ * dgate [total, 3] fp32 = row sums of d_out * branch. */
+int fsa_gate_mix_fwd(const void* gate, const void* a, const void* b, const void* c, int64_t total, int row_elems, int dtype,
+                     void* out, void* stream);
+int fsa_gate_mix_bwd(const void* gate, const void* a, const void* b, const void* c, const void* d_out, int64_t total,
+                     int row_elems, int dtype, void* da, void* db, void* dc, float* dgate, void* stream);
+
 /* Copy the device status word of an index workspace to the host (synchronises `stream`).
  * *status_out: 0 ok, 1 a bounded wait ran out, 2 an out-of-table index was skipped.
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */

@@ -1,0 +1,67 @@
+"""Compressed-branch and sliding-window attention on the GPU against the CPU oracle.
+Tolerances as in test_sel_attn_gpu.py (bf16 in/out vs fp32 oracle)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from fsa.ops.range_attention import compressed_attention_core, sliding_window_attention
+from fsa.synthetic import make_cu_seqlens
+from oracle import range_attn_oracle as orc
+
+DEV = "cuda:0"
+
+
+def _tol_ok(got, ref, name):
+    err = (got.float().cpu() - ref).abs()
+    scale = max(1.0, float(ref.abs().max()) / 2.0)
+    assert float(err.max()) <= 2e-2 * scale, f"{name}: max-abs {float(err.max()):.3e} (ref max {float(ref.abs().max()):.2f})"
+    assert float(err.mean()) <= 1e-3 * scale, f"{name}: mean-abs {float(err.mean()):.3e}"
+
+
+def _lse_ok(lse, ref):
+    fin = torch.isfinite(ref)
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    assert float((lse.cpu()[fin] - ref[fin]).abs().max()) <= 1e-4
+
+
+@pytest.mark.parametrize("seqlens,Hk,G,d,W", [([700, 45, 300], 2, 2, 128, 128), ([1500], 1, 4, 128, 512), ([333], 2, 1, 64, 64)])
+def test_sliding_window(seqlens, Hk, G, d, W):
+    N = sum(seqlens)
+    g = torch.Generator().manual_seed(N + W)
+    q = torch.randn(N, Hk * G, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(N, Hk, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(N, Hk, d, generator=g).to(torch.bfloat16)
+    do = torch.randn(N, Hk * G, d, generator=g).to(torch.bfloat16)
+    cu = make_cu_seqlens(seqlens)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.with_grads(orc.sliding_window_attention, q, k, v, do, cu, W)
+    qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    o, lse = sliding_window_attention(qc, kc, vc, cu.to(DEV), W)
+    o.backward(do.to(DEV))
+    _tol_ok(o, o_ref, "o")
+    _lse_ok(lse, lse_ref)
+    _tol_ok(qc.grad, dq_ref, "dq")
+    _tol_ok(kc.grad, dk_ref, "dk")
+    _tol_ok(vc.grad, dv_ref, "dv")
+
+
+@pytest.mark.parametrize("seqlens,Hk,G,d,ks,stride", [([2000, 20, 777], 2, 2, 128, 32, 16), ([4096], 1, 4, 128, 32, 16), ([500], 1, 1, 64, 16, 8)])
+def test_compressed_branch(seqlens, Hk, G, d, ks, stride):
+    N = sum(seqlens)
+    cmp_lens = [max((L - ks) // stride + 1, 0) if L >= ks else 0 for L in seqlens]
+    Nc = sum(cmp_lens)
+    g = torch.Generator().manual_seed(N + ks)
+    q = torch.randn(N, Hk * G, d, generator=g).to(torch.bfloat16)
+    ck = torch.randn(Nc, Hk, d, generator=g).to(torch.bfloat16)
+    cv = torch.randn(Nc, Hk, d, generator=g).to(torch.bfloat16)
+    do = torch.randn(N, Hk * G, d, generator=g).to(torch.bfloat16)
+    cu_q, cu_k = make_cu_seqlens(seqlens), make_cu_seqlens(cmp_lens)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.with_grads(orc.compressed_attention, q, ck, cv, do, ks, stride, cu_q, cu_k)
+    qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, ck, cv))
+    o, lse = compressed_attention_core(qc, kc, vc, ks, stride, cu_q.to(DEV), cu_k.to(DEV), max(cmp_lens))
+    o.backward(do.to(DEV))
+    _tol_ok(o, o_ref, "o")
+    _lse_ok(lse, lse_ref)
+    _tol_ok(qc.grad, dq_ref, "dq")
+    _tol_ok(kc.grad, dk_ref, "dk")
+    _tol_ok(vc.grad, dv_ref, "dv")

@@ -32,7 +32,7 @@ def _tol_ok(got, ref, name):
     err = (got.float().cpu() - ref).abs()
     scale = max(1.0, float(ref.abs().max()) / 2.0)
     assert float(err.max()) <= 2e-2 * scale, f"{name}: max-abs {float(err.max()):.3e} (ref max {float(ref.abs().max()):.2f})"
-    assert float(err.mean()) <= 1e-3, f"{name}: mean-abs {float(err.mean()):.3e}"
+    assert float(err.mean()) <= 1e-3 * scale, f"{name}: mean-abs {float(err.mean()):.3e}"
 
 
 CASES = [
