@@ -77,6 +77,21 @@ SIGNATURES = {
     "fsa_gate_mix_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "fsa_gate_mix_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_void_p]),
+    "fsa_decode_attn_partial": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p],
+    ),
+    "fsa_lse_merge": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fsa_decode_select_topk": (
+        c_int,
+        [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_int, c_int, c_void_p, c_void_p],
+    ),
+    "fsa_decode_ranges": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ),
     "fsa_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
     "fsa_sel_index_dump": (
         c_int,

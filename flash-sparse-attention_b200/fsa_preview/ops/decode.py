@@ -1,0 +1,196 @@
+"""Decode-step operators over the C ABI: partial attention over cache-row ranges, log-sum-exp merge,
+top-k block selection for the decoded token, range construction.
+
+``CudaDecodeOps`` is the only implementation the package ships; it raises when the sm_100a library
+is missing or a tensor is not on a CUDA device.  The step logic in ``nsa_decode_attention`` takes the
+operator set as an argument so that the sharding protocol can be exercised by CPU ranks in tests.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from fsa import _lib
+
+OUT_CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+class CudaDecodeOps:
+    """Thin wrappers: allocate outputs with torch, pass raw pointers to the library."""
+
+    @staticmethod
+    def _need_cuda(t):
+        if not t.is_cuda:
+            raise RuntimeError("the sm_100a decode kernels need CUDA tensors (there is no CPU fallback)")
+
+    def attn_partial(self, q, k, v, rng_lo, rng_hi, chunk, nchunk, sm_scale, want_scores=False):
+        """q [B,Hq,D]; k, v [rows,Hk,D]; rng_* [B,Hk,R] int32.  Returns o_part [B,Hq,P,D] fp32, ml [B,Hq,P,2],
+        scores [B,Hk,chunk*nchunk] fp32 or None."""
+        self._need_cuda(q)
+        B, Hq, D = q.shape
+        Hk = k.shape[1]
+        R = rng_lo.shape[-1]
+        P = R * nchunk
+        assert k.stride(2) == 1 and k.stride(1) == D and v.stride() == k.stride() and q.is_contiguous()
+        o_part = torch.empty((B, Hq, P, D), dtype=torch.float32, device=q.device)
+        ml = torch.empty((B, Hq, P, 2), dtype=torch.float32, device=q.device)
+        ld = chunk * nchunk
+        scores = torch.empty((B, Hk, ld), dtype=torch.float32, device=q.device) if want_scores else None
+        with torch.cuda.device(q.device):
+            rc = _lib.lib().fsa_decode_attn_partial(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), k.stride(0), _lib.ptr(rng_lo), _lib.ptr(rng_hi), B, Hq, Hk, D, R, chunk,
+                nchunk, _lib.DTYPE_CODE[q.dtype], float(sm_scale), _lib.ptr(o_part), _lib.ptr(ml), _lib.ptr(scores), ld,
+                _lib.current_stream(q.device))
+        _lib.check(rc, "fsa_decode_attn_partial")
+        return o_part, ml, scores
+
+    def lse_merge(self, o_part, ml, out_dtype, p0=0, pn=None):
+        """o_part [..., P, D] fp32, ml [..., P, 2] -> o [..., D] in out_dtype, lse [...] (log2 units); merges the
+        partials p0 .. p0+pn-1 of every row (all by default)."""
+        self._need_cuda(o_part)
+        *lead, P, D = o_part.shape
+        rows = math.prod(lead)
+        pn = P - p0 if pn is None else pn
+        assert o_part.is_contiguous() and ml.is_contiguous() and 0 <= p0 and p0 + pn <= P
+        o = torch.empty((*lead, D), dtype=out_dtype, device=o_part.device)
+        lse = torch.empty(tuple(lead), dtype=torch.float32, device=o_part.device)
+        with torch.cuda.device(o_part.device):
+            rc = _lib.lib().fsa_lse_merge(o_part.data_ptr() + p0 * D * 4, ml.data_ptr() + p0 * 8, rows, pn, P, D, OUT_CODE[out_dtype],
+                                          _lib.ptr(o), _lib.ptr(lse), _lib.current_stream(o_part.device))
+        _lib.check(rc, "fsa_lse_merge")
+        return o, lse
+
+    def select_topk(self, scores, ld, shard_len, shard_stride, lse, seq_len, num_cmp, num_kv_heads, kernel_size, kernel_stride,
+                    block_size, init_blocks, local_blocks, topk, max_blocks):
+        self._need_cuda(scores)
+        B, Hq = lse.shape
+        out = torch.empty((B, num_kv_heads, topk), dtype=torch.int32, device=scores.device)
+        with torch.cuda.device(scores.device):
+            rc = _lib.lib().fsa_decode_select_topk(
+                _lib.ptr(scores), ld, shard_len, shard_stride, _lib.ptr(lse), _lib.ptr(seq_len), _lib.ptr(num_cmp), B, Hq,
+                num_kv_heads, kernel_size, kernel_stride, block_size, init_blocks, local_blocks, topk, max_blocks, _lib.ptr(out),
+                _lib.current_stream(scores.device))
+        _lib.check(rc, "fsa_decode_select_topk")
+        return out
+
+    def ranges(self, topk_idx, seq_len, seq_row0, num_kv_heads, topk, block_size, window, piece, num_pieces, shard_lo, shard_hi):
+        self._need_cuda(seq_len)
+        B = seq_len.numel()
+        R = topk + num_pieces
+        lo = torch.empty((B, num_kv_heads, R), dtype=torch.int32, device=seq_len.device)
+        hi = torch.empty_like(lo)
+        with torch.cuda.device(seq_len.device):
+            rc = _lib.lib().fsa_decode_ranges(_lib.ptr(topk_idx), _lib.ptr(seq_len), _lib.ptr(seq_row0), B, num_kv_heads, topk,
+                                              block_size, window, piece, num_pieces, shard_lo, shard_hi, _lib.ptr(lo), _lib.ptr(hi),
+                                              _lib.current_stream(seq_len.device))
+        _lib.check(rc, "fsa_decode_ranges")
+        return lo, hi
+
+
+@dataclass
+class Shard:
+    """What one GPU holds when the KV sequence is split: tokens [tok_lo, tok_hi) and compressed tokens
+    [cmp_lo, cmp_hi) of EVERY sequence.  One GPU: everything."""
+    tok_lo: int = 0
+    tok_hi: int = 2**31 - 1
+    cmp_lo: int = 0
+    cmp_hi: int = 2**31 - 1
+    rank: int = 0
+    world: int = 1
+    group: object = None
+
+
+def shard_plan(max_len: int, kernel_size: int, kernel_stride: int, rank: int, world: int, group=None, align: int = 64) -> Shard:
+    """Contiguous equal slices of the token axis (multiples of ``align`` tokens) and of the compressed axis."""
+    per = -(-max_len // world)
+    per = -(-per // align) * align
+    max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
+    cper = max(-(-max_cmp // world), 1)
+    cper = -(-cper // 4) * 4
+    return Shard(rank * per, (rank + 1) * per, rank * cper, (rank + 1) * cper, rank, world, group)
+
+
+def _gather(t: torch.Tensor, shard: Shard) -> torch.Tensor:
+    """All-gather ``t`` from every rank of the shard's group: [world, *t.shape]."""
+    import torch.distributed as dist
+
+    out = torch.empty((shard.world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=shard.group)
+    return out.view(shard.world, *t.shape)
+
+
+def _merge_ranks(ops, o_loc, lse_loc, shard: Shard, out_dtype):
+    """Second-level merge across GPUs: every rank contributes its normalised fp32 output and its lse;
+    a rank with no visible key has lse = -inf and weight 0."""
+    if shard.world == 1:
+        return o_loc.to(out_dtype), lse_loc
+    o_all = _gather(o_loc, shard)                                # [W, B, Hq, D]
+    lse_all = _gather(lse_loc, shard)                            # [W, B, Hq]
+    o_part = o_all.permute(1, 2, 0, 3).contiguous()
+    m = lse_all.permute(1, 2, 0)
+    ml = torch.stack([m, torch.isfinite(m).to(torch.float32)], dim=-1).contiguous()
+    return ops.lse_merge(o_part, ml, out_dtype)
+
+
+def nsa_decode_attention(
+    q: torch.Tensor,                 # [B, Hq, D] (already rotated)
+    k: torch.Tensor, v: torch.Tensor,            # cache rows [rows, Hk, D] of this GPU (k rotated)
+    cmp_k: torch.Tensor, cmp_v: torch.Tensor,    # compressed cache rows of this GPU
+    seq_len: torch.Tensor,           # [B] int32: tokens per sequence INCLUDING the decoded one
+    seq_row0: torch.Tensor,          # [B] int32: cache row of token shard.tok_lo of each sequence
+    cmp_row0: torch.Tensor,          # [B] int32: compressed-cache row of compressed token shard.cmp_lo
+    *, kernel_size: int, kernel_stride: int, block_size: int, topk: int, init_blocks: int, local_blocks: int,
+    window_size: int, max_len: int, sm_scale: Optional[float] = None, shard: Optional[Shard] = None, ops=None,
+    cmp_chunk: int = 256,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The three NSA branches for ONE new token per sequence; the token is the last of its sequence and gets
+    what the prefill path gives that row.  Returns (o_cmp, o_sel, o_win [B,Hq,D], lse_cmp, lse_sel, lse_win
+    [B,Hq] log2 units, topk_idx [B,Hk,T]).  ``max_len`` (host int) bounds every sequence length."""
+    ops = ops or CudaDecodeOps()
+    shard = shard or Shard()
+    B, Hq, D = q.shape
+    Hk = k.shape[1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    # ---- compressed branch: compressed token c is visible when its window ends at or before t (c*stride + ks - 1 <= t)
+    num_cmp = torch.clamp((seq_len - kernel_size) // kernel_stride + 1, min=0).to(torch.int32) * (seq_len >= kernel_size)
+    num_cmp = num_cmp.to(torch.int32)
+    c_hi = torch.clamp(num_cmp, max=shard.cmp_hi) - shard.cmp_lo
+    has = c_hi > 0
+    lo_c = torch.where(has, cmp_row0, torch.full_like(cmp_row0, -1)).view(B, 1, 1).expand(B, Hk, 1).contiguous()
+    hi_c = torch.where(has, cmp_row0 + c_hi, torch.full_like(cmp_row0, -1)).view(B, 1, 1).expand(B, Hk, 1).contiguous()
+    max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
+    cmp_local = max(min(max_cmp, shard.cmp_hi) - shard.cmp_lo, 1)
+    nchunk = -(-cmp_local // cmp_chunk)
+    o_part, ml, scores = ops.attn_partial(q, cmp_k, cmp_v, lo_c, hi_c, cmp_chunk, nchunk, sm_scale, want_scores=True)
+    ld = cmp_chunk * nchunk
+    if shard.world == 1:
+        o_cmp, lse_cmp = ops.lse_merge(o_part, ml, q.dtype)
+        shard_len, shard_stride = ld, 0
+    else:
+        o_loc, lse_loc = ops.lse_merge(o_part, ml, torch.float32)
+        o_cmp, lse_cmp = _merge_ranks(ops, o_loc, lse_loc, shard, q.dtype)
+        scores = _gather(scores, shard)                          # [W, B, Hk, ld], kept shard-major
+        shard_len, shard_stride = shard.cmp_hi - shard.cmp_lo, B * Hk * ld
+    # ---- top-k blocks of the decoded token
+    max_blocks = -(-max_len // block_size)
+    topk_idx = ops.select_topk(scores, ld, shard_len, shard_stride, lse_cmp, seq_len, num_cmp, Hk, kernel_size, kernel_stride,
+                               block_size, init_blocks, local_blocks, topk, max_blocks)
+    # ---- selected blocks + sliding window in one launch (ranges 0..T-1 and T..)
+    piece = block_size
+    npieces = -(-(window_size + 1) // piece)
+    lo, hi = ops.ranges(topk_idx, seq_len, seq_row0, Hk, topk, block_size, window_size, piece, npieces, shard.tok_lo, shard.tok_hi)
+    o_part, ml, _ = ops.attn_partial(q, k, v, lo, hi, piece, 1, sm_scale)
+    first = torch.float32 if shard.world > 1 else q.dtype
+    o_sel, lse_sel = ops.lse_merge(o_part, ml, first, 0, topk)
+    o_win, lse_win = ops.lse_merge(o_part, ml, first, topk, npieces)
+    if shard.world > 1:
+        both, lse_both = _merge_ranks(ops, torch.stack([o_sel, o_win], 2).flatten(1, 2), torch.stack([lse_sel, lse_win], 2).flatten(1, 2),
+                                      shard, q.dtype)
+        both = both.view(B, Hq, 2, D)
+        lse_both = lse_both.view(B, Hq, 2)
+        o_sel, o_win, lse_sel, lse_win = both[:, :, 0], both[:, :, 1], lse_both[:, :, 0], lse_both[:, :, 1]
+    return o_cmp, o_sel, o_win, lse_cmp, lse_sel, lse_win, topk_idx

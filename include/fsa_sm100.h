@@ -192,6 +192,54 @@ int fsa_gate_mix_fwd(const void* gate, const void* a, const void* b, const void*
 int fsa_gate_mix_bwd(const void* gate, const void* a, const void* b, const void* c, const void* d_out, int64_t total,
                      int row_elems, int dtype, void* da, void* db, void* dc, float* dgate, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * One-step decode (fsa_preview)
+ * ------------------------------------------------------------------------------------------- */
+
+/* Partial attention of one query token per sequence over ranges of K/V cache rows.  Replaces
+ * forward_kernel_decode and score_kernel_decode (fsa_preview/ops/compressed_attention_decode.py:361-592),
+ * _topk_sparse_attention_decode (fsa_preview/ops/selected_attention_decode.py:8-42) and the window call
+ * (fsa_preview/module/fsa_decode.py:175-185).
+ *   q [B, Hq, D]; k, v [rows, Hk, D] with row stride kv_stride_n; rng_lo / rng_hi [B, Hk, R]: range r of
+ *   (sequence, kv head) covers the rows [lo, hi) (lo = -1: empty).  Every range is cut into num_chunks chunks
+ *   of `chunk` rows (chunk * num_chunks >= the longest range); partial (b, head, r * num_chunks + c) receives
+ *   o_part [B, Hq, P, D] fp32 (unnormalised) and ml [B, Hq, P, 2] = (max logit in log2 units, sum of exp2).
+ *   scores (optional) [B, Hk, scores_ld]: the scaled log2 logits of each group's FIRST head over range 0,
+ *   the input of fsa_decode_select_topk. */
+int fsa_decode_attn_partial(const void* q, const void* k, const void* v, int64_t kv_stride_n, const int32_t* rng_lo,
+                            const int32_t* rng_hi, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                            int num_ranges, int chunk, int num_chunks, int dtype, float sm_scale, float* o_part, float* ml,
+                            float* scores, int64_t scores_ld, void* stream);
+
+/* Log-sum-exp merge of P partials per row: o = sum w_p o_p / sum w_p l_p, w_p = exp2(m_p - max m), lse = max m +
+ * log2 sum w_p l_p.  Used inside one GPU (chunks, blocks) and across GPUs (after an all-gather of the partials;
+ * the reference has no multi-GPU path).  Row r reads partials o_part[(r * part_stride + p) * head_dim ...] and
+ * ml[(r * part_stride + p) * 2 ...], p < num_partials, so a sub-range of a wider partial buffer can be merged in
+ * place (offset the pointers).  out_dtype: 0 bf16, 1 fp16, 2 fp32; lse may be null. */
+int fsa_lse_merge(const float* o_part, const float* ml, int64_t rows, int num_partials, int part_stride, int head_dim,
+                  int out_dtype, void* o, float* lse, void* stream);
+
+/* Top-k block ids for the decoded token of every sequence, from the scores buffer of the compressed branch
+ * and its merged lse [B, Hq].  Same scoring, bf16 rounding and tie rule as fsa_select_topk_seq, evaluated at
+ * t = seq_len[b] - 1 (the reference evaluates the "local blocks" rule at t = 0,
+ * fsa_preview/ops/compressed_attention_decode.py:329-355, which does not match its own prefill).
+ * When the compressed cache is sharded over GPUs the gathered score buffers stay shard-major: compressed token c
+ * is read at scores[(c / shard_len) * shard_stride + row * scores_ld + c % shard_len] (one GPU: shard_len >= num_cmp).
+ * topk_idx [B, Hk, topk]: ascending block ids, -1 padded. */
+int fsa_decode_select_topk(const float* scores, int64_t scores_ld, int shard_len, int64_t shard_stride, const float* lse, const int32_t* seq_len,
+                           const int32_t* num_cmp, int batch, int num_q_heads, int num_kv_heads, int kernel_size,
+                           int kernel_stride, int block_size, int init_blocks, int local_blocks, int topk, int max_blocks,
+                           int32_t* topk_idx, void* stream);
+
+/* Cache-row ranges of the selected blocks (ranges 0..topk-1, from topk_idx [B, Hk, topk]) and of the sliding window
+ * [max(0, t - window), t] cut into num_window_pieces pieces of `piece` rows (ranges topk..), for t = seq_len[b] - 1,
+ * clipped to the tokens [shard_lo, shard_hi) this GPU stores; token tok of sequence b is cache row
+ * seq_row0[b] + tok - shard_lo.  Output rng_lo / rng_hi [B, Hk, topk + num_window_pieces] feed fsa_decode_attn_partial.
+ * Host-side arithmetic of the reference: fsa_preview/module/fsa_decode.py:160-185. */
+int fsa_decode_ranges(const int32_t* topk_idx, const int32_t* seq_len, const int32_t* seq_row0, int batch, int num_kv_heads,
+                      int topk, int block_size, int window, int piece, int num_window_pieces, int shard_lo, int shard_hi,
+                      int32_t* rng_lo, int32_t* rng_hi, void* stream);
+
 /* Copy the device status word of an index workspace to the host (synchronises `stream`).
  * *status_out: 0 ok, 1 a bounded wait ran out, 2 an out-of-table index was skipped.
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
