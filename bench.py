@@ -160,8 +160,193 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+DECODE_CFG = dict(batch=64, cache_len=131072, Hk=8, G=4, d=128, kernel_size=32, kernel_stride=16, block_size=64, topk=16,
+                  init_blocks=1, local_blocks=2, window_size=512)
+DECODE_METRIC = "NSA one-step decode tokens/s (batch 64 x 131072-token bf16 KV cache, Hk=8, G=4, d=128, ks=32/16, B_K=64, T=16, W=512)"
+
+
+def decode_cpu_baseline(threads, cache_len=8192):
+    """The decode oracle on the host cores: one sequence, one step."""
+    from oracle.decode_oracle import decode_branches_ref
+
+    c = DECODE_CFG
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1)
+    Hk, d, Hq = c["Hk"], c["d"], c["Hk"] * c["G"]
+    n_cmp = (cache_len - c["kernel_size"]) // c["kernel_stride"] + 1
+    k, v = torch.randn(cache_len, Hk, d, generator=g), torch.randn(cache_len, Hk, d, generator=g)
+    ck, cv = torch.randn(n_cmp, Hk, d, generator=g), torch.randn(n_cmp, Hk, d, generator=g)
+    q = torch.randn(1, Hq, d, generator=g)
+    t0 = time.perf_counter()
+    decode_branches_ref(q, [k], [v], [ck], [cv], c)
+    dt = time.perf_counter() - t0
+    return 1.0 / dt, dt, cache_len
+
+
+def run_decode(args, rank, world, local_rank):
+    """One decode step of the three NSA branches + gate mix over a resident KV cache; with N > 1 the KV sequence is
+    split over the ranks (same batch, same total cache: strong scaling) and partial outputs are merged by LSE after an
+    NCCL all-gather."""
+    import torch.distributed as dist
+
+    from fsa_preview.module import FlashSparseAttentionDecodeKernel, GraphedStep
+    from fsa_preview.ops.decode import CudaDecodeOps, nsa_decode_attention, shard_plan
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = dict(DECODE_CFG)
+    if args.case == "small":
+        c.update(batch=8, cache_len=32768)
+    B, Lc, Hk, G, d = c["batch"], c["cache_len"], c["Hk"], c["G"], c["d"]
+    Hq = Hk * G
+    nsa = {n: c[n] for n in ("kernel_size", "kernel_stride", "block_size", "topk", "init_blocks", "local_blocks", "window_size")}
+    margin = 64
+    max_len = Lc + margin
+    shard = shard_plan(max_len, c["kernel_size"], c["kernel_stride"], rank, world, align=64)
+    mod = FlashSparseAttentionDecodeKernel(Hq * d, Hq, Hk, d, **nsa).to(dev).to(torch.bfloat16)
+    torch.manual_seed(7)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.normal_(0, 0.02)
+    cache = mod.new_cache(B, max_len, shard=shard, device=dev)
+    torch.manual_seed(100 + rank)
+    for t in (cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.k_tail, cache.v_tail):
+        t.normal_()
+    cache.host_len = [Lc] * B
+    cache.seq_len.fill_(Lc)
+    g = torch.Generator().manual_seed(3)
+    qh = torch.randn(B, Hq, d, generator=g).to(torch.bfloat16).pin_memory()
+    knh = torch.randn(B, Hk, d, generator=g).to(torch.bfloat16).pin_memory()
+    vnh = torch.randn(B, Hk, d, generator=g).to(torch.bfloat16).pin_memory()
+    qd = qh.to(dev)
+    from fsa.ops.gate import gate_mix
+
+    def eager_step():
+        oc, os_, ow, *_ = nsa_decode_attention(qd, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0,
+                                               cache.cmp_row0, max_len=max_len, shard=shard, **nsa)
+        return gate_mix(mod.gate(qd.view(B, -1)), oc, os_.contiguous(), ow.contiguous())
+
+    use_graph = world == 1 and not args.no_graph
+    step = eager_step
+    if use_graph:
+        # the attention step at a fixed cache length, captured once and replayed
+        with torch.no_grad():
+            for _ in range(3):
+                eager_step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph), torch.no_grad():
+            eager_step()
+        step = graph.replay
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(n):
+            fn()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / n
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            step()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        ms_step = timed(step, args.steps)
+        clocks = sampler.stop()
+        # dominant kernel alone: the compressed branch's partial pass (all visible compressed K/V rows of this rank)
+        ops = CudaDecodeOps()
+        ks_, st_ = c["kernel_size"], c["kernel_stride"]
+        n_cmp = (Lc - ks_) // st_ + 1
+        n_loc = max(min(n_cmp, shard.cmp_hi) - shard.cmp_lo, 0)
+        lo = cache.cmp_row0.view(B, 1, 1).expand(B, Hk, 1).contiguous()
+        hi = (lo + n_loc).contiguous()
+        nchunk = max(-(-n_loc // 512), 1)
+        cmp_pass = lambda: ops.attn_partial(qd, cache.cmp_k, cache.cmp_v, lo, hi, 512, nchunk, d ** -0.5, want_scores=True)  # noqa: E731
+        for _ in range(3):
+            cmp_pass()
+        torch.cuda.synchronize()
+        g_cmp = torch.cuda.CUDAGraph()                    # replayed, so that the host cost of a launch is not in the figure
+        with torch.cuda.graph(g_cmp):
+            cmp_pass()
+        ms_cmp = timed(g_cmp.replay, args.steps)
+
+        # end to end: host q / k_new / v_new in, output row out, through the module's step (append + attention + gate mix)
+        gstep = GraphedStep(mod.step, cache, [qd, knh.to(dev), vnh.to(dev)]) if use_graph else None
+
+        def e2e_step():
+            if gstep is not None:
+                return gstep(qh, knh, vnh).cpu()
+            y = mod.step(qh.to(dev, non_blocking=True), knh.to(dev, non_blocking=True), vnh.to(dev, non_blocking=True), cache)
+            return y.cpu()
+
+        e2e_n = 0 if args.no_e2e else max(1, min(args.steps, margin // 2 - 4))
+        if e2e_n:
+            e2e_step()
+            e2e_ms = timed(e2e_step, e2e_n)
+    elem = 2
+    T, BK, W = c["topk"], c["block_size"], c["window_size"]
+    bytes_cmp = B * Hk * n_cmp * d * elem * 2
+    bytes_sel = B * Hk * T * BK * d * elem * 2
+    bytes_win = B * Hk * (W + 1) * d * elem * 2
+    bytes_step = bytes_cmp + bytes_sel + bytes_win
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 0) or 0)
+        src = "MEASURED_PEAKS.json hbm_gbs"
+        if not peak:
+            peak, src = 6650.0, "fallback"
+        achieved = B * Hk * n_loc * d * elem * 2 / (ms_cmp * 1e-3) / 1e9
+        cpu = None
+        if not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tps, dt, n = decode_cpu_baseline(threads)
+            cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                   "sample": f"decode oracle, one sequence with a {n}-token cache, one step ({dt:.2f} s); cost grows with the cache length"}
+        line = {
+            "metric": DECODE_METRIC, "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded N(0,1) cache and query)",
+            "config": {"workload": f"decode: batch {B} x {Lc}-token cache" + (" (small case)" if args.case == "small" else ""),
+                       "parallelism": f"kv-sequence shards x{world}, LSE merge after all-gather" if world > 1 else "one GPU",
+                       "l2": "the cache read per step exceeds L2", "algorithmic_bytes_per_step": bytes_step,
+                       "step_gbs": bytes_step / world / (ms_step * 1e-3) / 1e9},
+            "roofline": {"bound": "hbm", "kernel": "decode_partial_tma (compressed branch)", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": src, "ms": ms_cmp},
+            "cpu_baseline": cpu,
+            "e2e": ({"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": (qh.numel() + knh.numel() + vnh.numel()) * 2, "d2h_bytes_per_step": B * Hq * d * 2}
+                    if e2e_n else None),
+            "gpu_launches": 9 * args.steps, "cuda_graph": use_graph,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="sel_attn", choices=["sel_attn", "decode"],
+                    help="sel_attn (default): selected attention fwd+bwd, the headline; decode: one NSA decode step")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -170,6 +355,7 @@ def main():
     ap.add_argument("--case", default="cfg1", choices=["cfg1", "small"],
                     help="small = one 16384-token sequence of cfg1 (a quarter of it), for profiler captures")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="decode workload: launch the step's kernels one by one")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -178,6 +364,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "decode":
+        run_decode(args, rank, world, local_rank)
         return
 
     import torch.distributed as dist

@@ -13,6 +13,11 @@
 
 namespace fsa {
 
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int box_rows);
+
+// Set (atomicMax) by a decode kernel whose bounded wait ran out; read with fsa_decode_read_status.
+static __device__ int g_decode_status;
+
 struct DecodeParams {
     const void* q;          // [B, Hq, D]
     const void* k;          // [rows, Hk, D] (row stride kv_sn elements, head stride D)
@@ -26,15 +31,40 @@ struct DecodeParams {
     float2* ml;             // [B, Hq, P]
     float* scores;          // optional [B, Hk, scores_ld]: scaled logits (log2 units) of the group's FIRST head, range 0 only
     int64_t scores_ld;
+    int nst;                // pipeline stages of the TMA kernel
+    int rpp, NP;            // ranges per partial (one online softmax over rpp consecutive ranges), partial groups = ceil(R / rpp)
 };
 
-template <int D, int G, typename ET>
+// m16n8k16 tensor-core step on register fragments (the legacy warp-level path: this kernel is bound by HBM, the
+// tensor work is a few percent of a step; what matters is that the per-key instruction count stays far below the
+// issue budget of a memory-bound SM, which scalar FMAs do not manage for GQA groups of 4 and more).
+template <typename ET>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if constexpr (ElemTraits<ET>::kIsBF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One CTA = one chunk of one range of one (sequence, kv head); its 4 warps take the chunk's 16-key tiles round-robin.
+// Per tile a warp computes S = Q K^T (rows = the group's heads padded to 16, 8 keys per MMA) straight from 16-byte
+// global loads: the contraction index may be permuted freely, so the 8 consecutive head_dim elements a thread loads
+// of a key row serve as the (k, k+1, k+8, k+9) slots of two MMA k-steps, and Q is held in registers in the same
+// order.  P (rounded to the input type) is re-used in registers as the A operand of O += P V; the B operand pairs two
+// key rows per register, built with byte permutes from four 16-byte loads, and the 8 output columns of MMA i are the
+// head_dim columns {8 n + i}.  Online softmax per warp, warps merged through shared memory at the end.
+// HI: the group has more than 8 heads (rows 8..15 of the tiles are live).
+template <int D, bool HI, typename ET>
 __global__ void __launch_bounds__(128) decode_partial_kernel(const DecodeParams p) {
     extern __shared__ float dsm[];
-    float* sq = dsm;                       // [G][D]
-    float* ss = sq + G * D;                // [G][chunk]
-    float* so = ss + G * p.chunk;          // [G][D] reduction buffer
-    const int tid = threadIdx.x;
+    constexpr int NJ = D / 32;             // 16-byte K loads per key row and thread
+    constexpr int NS = D / 64;             // 64-column steps of the PV product
+    constexpr int NT = NS * 8;             // PV accumulator tiles
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int G = p.Hq / p.Hk;
     const int c = blockIdx.x % p.nchunk;
     const int r = (blockIdx.x / p.nchunk) % p.R;
     const int h = (blockIdx.x / (p.nchunk * p.R)) % p.Hk;
@@ -50,120 +80,468 @@ __global__ void __launch_bounds__(128) decode_partial_kernel(const DecodeParams 
         return;
     }
     const int n = hi - lo;
-    const ET* q = (const ET*)p.q + ((int64_t)b * p.Hq + h * G) * D;
-    for (int i = tid; i < G * D; i += 128) { sq[i] = (float)q[i]; so[i] = 0.f; }
-    __syncthreads();
-    constexpr int TPK = D / 8;             // threads per key row (16-byte loads)
-    constexpr int KPI = 128 / TPK;         // keys per iteration
-    const int part = tid % TPK, kg = tid / TPK;
-    // ---- scores
-    for (int k0 = 0; k0 < n; k0 += KPI) {
-        const int key = k0 + kg;
-        float acc[G];
+    const ET* kbase = (const ET*)p.k + (int64_t)lo * p.kv_sn + h * D;
+    const ET* vbase = (const ET*)p.v + (int64_t)lo * p.kv_sn + h * D;
+    // Q fragments: row gid (and gid + 8), this thread's 8 elements of every 32-element group
+    uint4 qa[NJ], qb[NJ];
+    {
+        const ET* q = (const ET*)p.q + ((int64_t)b * p.Hq + h * G) * D;
 #pragma unroll
-        for (int g = 0; g < G; ++g) acc[g] = 0.f;
-        if (key < n) {
-            uint4 u = *reinterpret_cast<const uint4*>((const ET*)p.k + (int64_t)(lo + key) * p.kv_sn + h * D + part * 8);
-            const uint32_t* pu = &u.x;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float2 x = ElemTraits<ET>::unpack2(pu[i]);
-#pragma unroll
-                for (int g = 0; g < G; ++g) acc[g] += x.x * sq[g * D + part * 8 + 2 * i] + x.y * sq[g * D + part * 8 + 2 * i + 1];
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-#pragma unroll
-            for (int o = TPK / 2; o; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
-            if (part == 0 && key < n) ss[g * p.chunk + key] = acc[g] * p.scale_log2;
+        for (int j = 0; j < NJ; ++j) {
+            qa[j] = gid < G ? *reinterpret_cast<const uint4*>(q + gid * D + j * 32 + tig * 8) : make_uint4(0, 0, 0, 0);
+            qb[j] = (HI && gid + 8 < G) ? *reinterpret_cast<const uint4*>(q + (gid + 8) * D + j * 32 + tig * 8) : make_uint4(0, 0, 0, 0);
         }
     }
-    __syncthreads();
-    if (p.scores && r == 0)
-        for (int i = tid; i < n; i += 128) p.scores[((int64_t)b * p.Hk + h) * p.scores_ld + (lo - lo_r) + i] = ss[i];
-    // ---- per-head max and sum (warp g handles head g, g + 4, ...)
-    __shared__ float sm_m[32], sm_l[32];
-    for (int g = tid >> 5; g < G; g += 4) {
-        const int lane = tid & 31;
-        float m = -INFINITY;
-        for (int i = lane; i < n; i += 32) m = fmaxf(m, ss[g * p.chunk + i]);
+    float acc[NT][4];
 #pragma unroll
-        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float l = 0.f;
-        for (int i = lane; i < n; i += 32) {
-            float e = exp2f(ss[g * p.chunk + i] - m);
-            ss[g * p.chunk + i] = e;
-            l += e;
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows gid and gid + 8
+    const bool want_scores = p.scores != nullptr && r == 0 && gid == 0;
+    float* srow = want_scores ? p.scores + ((int64_t)b * p.Hk + h) * p.scores_ld + (lo - lo_r) : nullptr;
+
+    for (int k0 = warp * 16; k0 < n; k0 += 64) {
+        // ---- loads of the tile (rows past the end re-read the last row; their logits are masked)
+        uint4 kf[2][NJ], vf[NS][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int key = min(k0 + nt * 8 + gid, n - 1);
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) kf[nt][j] = *reinterpret_cast<const uint4*>(kbase + (int64_t)key * p.kv_sn + j * 32 + tig * 8);
         }
 #pragma unroll
-        for (int o = 16; o; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        if (lane == 0) { sm_m[g] = m; sm_l[g] = l; }
-    }
-    __syncthreads();
-    // ---- o = sum_key p[key] v[key]
-    float acc[G][8];
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int key = min(k0 + tig * 2 + (q4 & 1) + (q4 >> 1) * 8, n - 1);
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+            for (int s = 0; s < NS; ++s) vf[s][q4] = *reinterpret_cast<const uint4*>(vbase + (int64_t)key * p.kv_sn + s * 64 + gid * 8);
+        }
+        // ---- S = Q K^T
+        float sc[2][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
-    for (int k0 = 0; k0 < n; k0 += KPI) {
-        const int key = k0 + kg;
-        if (key < n) {
-            uint4 u = *reinterpret_cast<const uint4*>((const ET*)p.v + (int64_t)(lo + key) * p.kv_sn + h * D + part * 8);
-            const uint32_t* pu = &u.x;
-            float x[8];
+        for (int nt = 0; nt < 2; ++nt) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float2 t2 = ElemTraits<ET>::unpack2(pu[i]);
-                x[2 * i] = t2.x; x[2 * i + 1] = t2.y;
+            for (int j = 0; j < NJ; ++j) {
+                mma16816<ET>(sc[nt], qa[j].x, qb[j].x, qa[j].y, qb[j].y, kf[nt][j].x, kf[nt][j].y);
+                mma16816<ET>(sc[nt], qa[j].z, qb[j].z, qa[j].w, qb[j].w, kf[nt][j].z, kf[nt][j].w);
             }
+        }
+        // ---- scale, mask, running max
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float w = ss[g * p.chunk + key];
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(w, x[i], acc[g][i]);
+            for (int e = 0; e < 2; ++e) {
+                const int key = k0 + nt * 8 + tig * 2 + e;
+                const bool ok = key < n;
+                sc[nt][e] = ok ? sc[nt][e] * p.scale_log2 : -INFINITY;
+                sc[nt][2 + e] = ok ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
+                if (want_scores && ok) srow[key] = sc[nt][e];
+                tmax0 = fmaxf(tmax0, sc[nt][e]);
+                tmax1 = fmaxf(tmax1, sc[nt][2 + e]);
+            }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        if (HI) {
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        }
+        const float mn0 = fmaxf(m0, tmax0), mn1 = HI ? fmaxf(m1, tmax1) : m1;      // finite: key k0 of the tile is valid
+        if (__any_sync(0xffffffffu, mn0 > m0 || (HI && mn1 > m1))) {
+            const float a0 = exp2f(m0 - mn0), a1 = HI ? exp2f(m1 - mn1) : 1.f;   // exp2(-inf) = 0 on the first tile
+            l0 *= a0;
+            l1 *= a1;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                acc[i][0] *= a0; acc[i][1] *= a0;
+                if (HI) { acc[i][2] *= a1; acc[i][3] *= a1; }
+            }
+            m0 = mn0;
+            m1 = mn1;
+        }
+        // ---- P (rounded to the input type; the sums use the rounded values' fp32 originals as the prefill kernels do)
+        uint32_t pa[4];
+        {
+            float e00 = exp2f(sc[0][0] - m0), e01 = exp2f(sc[0][1] - m0), e10 = exp2f(sc[1][0] - m0), e11 = exp2f(sc[1][1] - m0);
+            l0 += e00 + e01 + e10 + e11;
+            pa[0] = ElemTraits<ET>::pack2(e00, e01);
+            pa[2] = ElemTraits<ET>::pack2(e10, e11);
+            if (HI) {
+                float f00 = exp2f(sc[0][2] - m1), f01 = exp2f(sc[0][3] - m1), f10 = exp2f(sc[1][2] - m1), f11 = exp2f(sc[1][3] - m1);
+                l1 += f00 + f01 + f10 + f11;
+                pa[1] = ElemTraits<ET>::pack2(f00, f01);
+                pa[3] = ElemTraits<ET>::pack2(f10, f11);
+            } else {
+                pa[1] = pa[3] = 0u;
+            }
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const uint32_t* r0 = &vf[s][0].x;
+            const uint32_t* r1 = &vf[s][1].x;
+            const uint32_t* r2 = &vf[s][2].x;
+            const uint32_t* r3 = &vf[s][3].x;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                mma16816<ET>(acc[s * 8 + 2 * w], pa[0], pa[1], pa[2], pa[3], __byte_perm(r0[w], r1[w], 0x5410), __byte_perm(r2[w], r3[w], 0x5410));
+                mma16816<ET>(acc[s * 8 + 2 * w + 1], pa[0], pa[1], pa[2], pa[3], __byte_perm(r0[w], r1[w], 0x7632), __byte_perm(r2[w], r3[w], 0x7632));
             }
         }
     }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // ---- merge the four warps: so [4][G][D], sm [4][G], sl [4][G]
+    float* so = dsm;
+    float* smm = so + 4 * G * D;
+    float* sll = smm + 4 * G;
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int half = 0; half < (HI ? 2 : 1); ++half) {
+        const int g = gid + half * 8;
+        if (g < G) {
+            float* dst = so + ((size_t)warp * G + g) * D;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) atomicAdd(&so[g * D + part * 8 + i], acc[g][i]);
+            for (int i = 0; i < NT; ++i) {
+                // tile i = s * 8 + e: columns s * 64 + (tig * 2 + {0, 1}) * 8 + e
+                const int s = i >> 3, e = i & 7;
+                dst[s * 64 + (tig * 2) * 8 + e] = acc[i][half * 2];
+                dst[s * 64 + (tig * 2 + 1) * 8 + e] = acc[i][half * 2 + 1];
+            }
+            if (tig == 0) {
+                smm[warp * G + g] = half ? m1 : m0;
+                sll[warp * G + g] = half ? l1 : l0;
+            }
+        }
+    }
     __syncthreads();
     for (int i = tid; i < G * D; i += 128) {
         const int g = i / D;
-        p.o_part[(pbase + (int64_t)g * P) * D + (i - g * D)] = so[i];
+        float M = fmaxf(fmaxf(smm[g], smm[G + g]), fmaxf(smm[2 * G + g], smm[3 * G + g]));
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = smm[w * G + g];
+            if (mw > -INFINITY) o += exp2f(mw - M) * so[(size_t)w * G * D + i];
+        }
+        p.o_part[(pbase + (int64_t)g * P) * D + (i - g * D)] = o;
     }
-    if (tid < G) p.ml[pbase + (int64_t)tid * P] = make_float2(sm_m[tid], sm_l[tid]);
+    if (tid < G) {
+        const int g = tid;
+        float M = fmaxf(fmaxf(smm[g], smm[G + g]), fmaxf(smm[2 * G + g], smm[3 * G + g]));
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = smm[w * G + g];
+            if (mw > -INFINITY) L += exp2f(mw - M) * sll[w * G + g];
+        }
+        p.ml[pbase + (int64_t)g * P] = make_float2(M, L);
+    }
 }
 
-// o[row, :] = sum_p exp2(m_p - M) o_p / sum_p exp2(m_p - M) l_p ; lse = M + log2(...).  One warp per row.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+// The same partial attention with the K/V rows of the chunk streamed by TMA: a producer warp keeps `nst` stages of
+// 64 keys (K and V, 128-byte swizzled 64-column halves) in flight on full/empty mbarriers, so the bytes in flight per
+// SM do not depend on registers or occupancy; the four consumer warps each take 16 keys of a stage, read their MMA
+// fragments with ldmatrix (transposed for V) and keep the online softmax in registers.  Every wait is bounded.
+constexpr int kDecKT = 64;
+template <int D, bool HI, typename ET>
+__global__ void __launch_bounds__(160) decode_partial_tma(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
+                                                          const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ __align__(1024) unsigned char dsm_raw[];
+    constexpr int HALF_BYTES = 64 * 128;                 // one 64-column half of 64 rows
+    constexpr int KV_BYTES = (D / 64) * HALF_BYTES;
+    constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    constexpr int NK = D / 16;                           // k-steps of Q K^T
+    constexpr int NO = D / 8;                            // 8-column output tiles of P V
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(dsm_raw) + 1023) & ~uintptr_t(1023));
+    const int nst = p.nst;
+    uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)nst * STAGE_BYTES);
+    uint64_t* empty = full + 4;
+    float* smm = reinterpret_cast<float*>(empty + 4);    // [4][16]
+    float* sll = smm + 64;
+    float* so = reinterpret_cast<float*>(base);          // [4][G][D], aliases stage 0 after the loop
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int G = p.Hq / p.Hk;
+    const int c = blockIdx.x % p.nchunk;
+    const int pr = (blockIdx.x / p.nchunk) % p.NP;
+    const int h = (blockIdx.x / (p.nchunk * p.NP)) % p.Hk;
+    const int b = blockIdx.x / (p.nchunk * p.NP * p.Hk);
+    const int P = p.NP * p.nchunk, pidx = pr * p.nchunk + c;
+    const int j0 = pr * p.rpp, j1 = min(p.R, j0 + p.rpp);
+    const int* rlo = p.rng_lo + ((int64_t)b * p.Hk + h) * p.R;
+    const int* rhi = p.rng_hi + ((int64_t)b * p.Hk + h) * p.R;
+    // rows [lo, lo + n) of range j that fall into this CTA's chunk
+    auto bounds = [&](int j, int& lo, int& n) {
+        const int lo_r = rlo[j], hi_r = rhi[j];
+        lo = lo_r + c * p.chunk;
+        n = lo_r < 0 ? 0 : max(min(hi_r, lo + p.chunk) - lo, 0);
+    };
+    const int64_t pbase = ((int64_t)b * p.Hq + h * G) * P + pidx;
+    int total = 0;
+    for (int j = j0; j < j1; ++j) {
+        int lo, n;
+        bounds(j, lo, n);
+        total += n;
+    }
+    if (total == 0) {
+        if (tid < G) p.ml[pbase + (int64_t)tid * P] = make_float2(-INFINITY, 0.f);
+        return;
+    }
+    if (tid == 0) {
+        for (int s = 0; s < nst; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const uint32_t sbase = smem_u32(base);
+    float acc[NO][4];
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    if (warp == 4) {
+        if (elect_one()) {
+            int it = 0;
+            bool ok = true;
+            for (int j = j0; j < j1 && ok; ++j) {
+                int lo, n;
+                bounds(j, lo, n);
+                for (int i = 0; i * kDecKT < n; ++i, ++it) {
+                    const int s = it % nst;
+                    if (it >= nst && !mbar_wait(&empty[s], ((it / nst) - 1) & 1, &g_decode_status)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    const uint32_t kb = sbase + s * STAGE_BYTES;
+#pragma unroll
+                    for (int hf = 0; hf < D / 64; ++hf) {
+                        tma_load_2d(kb + hf * HALF_BYTES, &kmap, h * D + hf * 64, lo + i * kDecKT, &full[s]);
+                        tma_load_2d(kb + KV_BYTES + hf * HALF_BYTES, &vmap, h * D + hf * 64, lo + i * kDecKT, &full[s]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        uint32_t qf[NK][2], qh[NK][2];
+        {
+            const ET* q = (const ET*)p.q + ((int64_t)b * p.Hq + h * G) * D;
+#pragma unroll
+            for (int kk = 0; kk < NK; ++kk) {
+                qf[kk][0] = gid < G ? *reinterpret_cast<const uint32_t*>(q + gid * D + kk * 16 + tig * 2) : 0u;
+                qf[kk][1] = gid < G ? *reinterpret_cast<const uint32_t*>(q + gid * D + kk * 16 + 8 + tig * 2) : 0u;
+                qh[kk][0] = (HI && gid + 8 < G) ? *reinterpret_cast<const uint32_t*>(q + (gid + 8) * D + kk * 16 + tig * 2) : 0u;
+                qh[kk][1] = (HI && gid + 8 < G) ? *reinterpret_cast<const uint32_t*>(q + (gid + 8) * D + kk * 16 + 8 + tig * 2) : 0u;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NO; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        const bool want_scores = p.scores != nullptr && p.rpp == 1 && pr == 0 && gid == 0;
+        const int lrow = lane & 7, lmat = lane >> 3;
+        int it = 0;
+        bool ok_wait = true;
+        for (int j = j0; j < j1 && ok_wait; ++j) {
+        int lo, n;
+        bounds(j, lo, n);
+        float* srow = want_scores ? p.scores + ((int64_t)b * p.Hk + h) * p.scores_ld + c * p.chunk : nullptr;
+        for (int i = 0; i * kDecKT < n; ++i, ++it) {
+            const int s = it % nst;
+            if (!mbar_wait(&full[s], (it / nst) & 1, &g_decode_status)) { ok_wait = false; break; }
+            const int k0 = i * kDecKT + warp * 16;               // first key of this warp's tile
+            if (k0 < n) {
+                const uint32_t kb = sbase + s * STAGE_BYTES, vb = kb + KV_BYTES;
+                float sc[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+                    const int row = warp * 16 + nt * 8 + lrow;
+#pragma unroll
+                    for (int c0 = 0; c0 < D / 8; c0 += 4) {
+                        const int cg = c0 + lmat;
+                        uint32_t r0, r1, r2, r3;
+                        ldsm_x4(kb + (cg >> 3) * HALF_BYTES + row * 128 + (((cg & 7) ^ (row & 7)) << 4), r0, r1, r2, r3);
+                        mma16816<ET>(sc[nt], qf[c0 / 2][0], qh[c0 / 2][0], qf[c0 / 2][1], qh[c0 / 2][1], r0, r1);
+                        mma16816<ET>(sc[nt], qf[c0 / 2 + 1][0], qh[c0 / 2 + 1][0], qf[c0 / 2 + 1][1], qh[c0 / 2 + 1][1], r2, r3);
+                    }
+                }
+                float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = k0 + nt * 8 + tig * 2 + e;
+                        const bool ok = key < n;
+                        sc[nt][e] = ok ? sc[nt][e] * p.scale_log2 : -INFINITY;
+                        sc[nt][2 + e] = ok ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
+                        if (want_scores && ok) srow[key] = sc[nt][e];
+                        tmax0 = fmaxf(tmax0, sc[nt][e]);
+                        tmax1 = fmaxf(tmax1, sc[nt][2 + e]);
+                    }
+                tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+                tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+                if (HI) {
+                    tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+                    tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+                }
+                const float mn0 = fmaxf(m0, tmax0), mn1 = HI ? fmaxf(m1, tmax1) : m1;
+                if (__any_sync(0xffffffffu, mn0 > m0 || (HI && mn1 > m1))) {
+                    const float a0 = exp2f(m0 - mn0), a1 = HI ? exp2f(m1 - mn1) : 1.f;
+                    l0 *= a0;
+                    l1 *= a1;
+#pragma unroll
+                    for (int t = 0; t < NO; ++t) {
+                        acc[t][0] *= a0; acc[t][1] *= a0;
+                        if (HI) { acc[t][2] *= a1; acc[t][3] *= a1; }
+                    }
+                    m0 = mn0;
+                    m1 = mn1;
+                }
+                uint32_t pa[4];
+                {
+                    float e00 = exp2f(sc[0][0] - m0), e01 = exp2f(sc[0][1] - m0), e10 = exp2f(sc[1][0] - m0), e11 = exp2f(sc[1][1] - m0);
+                    l0 += e00 + e01 + e10 + e11;
+                    pa[0] = ElemTraits<ET>::pack2(e00, e01);
+                    pa[2] = ElemTraits<ET>::pack2(e10, e11);
+                    if (HI) {
+                        float f00 = exp2f(sc[0][2] - m1), f01 = exp2f(sc[0][3] - m1), f10 = exp2f(sc[1][2] - m1), f11 = exp2f(sc[1][3] - m1);
+                        l1 += f00 + f01 + f10 + f11;
+                        pa[1] = ElemTraits<ET>::pack2(f00, f01);
+                        pa[3] = ElemTraits<ET>::pack2(f10, f11);
+                    } else {
+                        pa[1] = pa[3] = 0u;
+                    }
+                }
+                {
+                    const int row = warp * 16 + (lmat & 1) * 8 + lrow;
+#pragma unroll
+                    for (int c0 = 0; c0 < D / 8; c0 += 2) {
+                        const int cg = c0 + (lmat >> 1);
+                        uint32_t r0, r1, r2, r3;
+                        ldsm_x4_trans(vb + (cg >> 3) * HALF_BYTES + row * 128 + (((cg & 7) ^ (row & 7)) << 4), r0, r1, r2, r3);
+                        mma16816<ET>(acc[c0], pa[0], pa[1], pa[2], pa[3], r0, r1);
+                        mma16816<ET>(acc[c0 + 1], pa[0], pa[1], pa[2], pa[3], r2, r3);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        }
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+    __syncthreads();                                     // every stage has been consumed: stage memory is free
+    if (warp < 4) {
+#pragma unroll
+        for (int half = 0; half < (HI ? 2 : 1); ++half) {
+            const int g = gid + half * 8;
+            if (g < G) {
+                float* dst = so + ((size_t)warp * G + g) * D;
+#pragma unroll
+                for (int t = 0; t < NO; ++t)
+                    *reinterpret_cast<float2*>(dst + t * 8 + tig * 2) = make_float2(acc[t][half * 2], acc[t][half * 2 + 1]);
+                if (tig == 0) {
+                    smm[warp * 16 + g] = half ? m1 : m0;
+                    sll[warp * 16 + g] = half ? l1 : l0;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * D; i += 160) {
+        const int g = i / D;
+        const float M = fmaxf(fmaxf(smm[g], smm[16 + g]), fmaxf(smm[32 + g], smm[48 + g]));
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = smm[w * 16 + g];
+            if (mw > -INFINITY) o += exp2f(mw - M) * so[(size_t)w * G * D + i];
+        }
+        p.o_part[(pbase + (int64_t)g * P) * D + (i - g * D)] = o;
+    }
+    if (tid < G) {
+        const int g = tid;
+        const float M = fmaxf(fmaxf(smm[g], smm[16 + g]), fmaxf(smm[32 + g], smm[48 + g]));
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = smm[w * 16 + g];
+            if (mw > -INFINITY) L += exp2f(mw - M) * sll[w * 16 + g];
+        }
+        p.ml[pbase + (int64_t)g * P] = make_float2(M, L);
+    }
+}
+
+// o[row, :] = sum_p exp2(m_p - M) o_p / sum_p exp2(m_p - M) l_p ; lse = M + log2(...).  One warp per row; a lane owns 4
+// consecutive columns per 128-column slab and keeps several 128-bit loads in flight.
+template <typename OT>
+__device__ __forceinline__ void store4(OT* dst, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float4 v) {
+    uint2 u = make_uint2(ElemTraits<__nv_bfloat16>::pack2(v.x, v.y), ElemTraits<__nv_bfloat16>::pack2(v.z, v.w));
+    *reinterpret_cast<uint2*>(dst) = u;
+}
+template <> __device__ __forceinline__ void store4<__half>(__half* dst, float4 v) {
+    uint2 u = make_uint2(ElemTraits<__half>::pack2(v.x, v.y), ElemTraits<__half>::pack2(v.z, v.w));
+    *reinterpret_cast<uint2*>(dst) = u;
+}
+
 template <typename OT>
 __global__ void __launch_bounds__(256) lse_merge_kernel(const float* __restrict__ o_part, const float2* __restrict__ ml, int64_t rows, int P,
                                                         int PS, int D, OT* __restrict__ o, float* __restrict__ lse) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
+    const float2* mlr = ml + row * PS;
     float M = -INFINITY;
-    for (int i = lane; i < P; i += 32) M = fmaxf(M, ml[row * PS + i].x);
+    for (int i = lane; i < P; i += 32) {
+        float2 v = mlr[i];
+        if (v.y > 0.f) M = fmaxf(M, v.x);
+    }
 #pragma unroll
     for (int o_ = 16; o_; o_ >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o_));
     float L = 0.f;
     for (int i = lane; i < P; i += 32) {
-        float2 v = ml[row * PS + i];
+        float2 v = mlr[i];
         if (v.y > 0.f) L += exp2f(v.x - M) * v.y;
     }
 #pragma unroll
     for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int d = lane; d < D; d += 32) {
-        float acc = 0.f;
-        for (int i = 0; i < P; ++i) {
-            float2 v = ml[row * PS + i];
-            if (v.y > 0.f) acc += exp2f(v.x - M) * o_part[(row * PS + i) * D + d];
+    const float* src = o_part + row * PS * D;
+    for (int d = lane * 4; d < D; d += 128) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int i = 0;
+        for (; i + 4 <= P; i += 4) {
+            float4 x[4];
+            float w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 v = mlr[i + j];
+                w[j] = v.y > 0.f ? exp2f(v.x - M) : 0.f;
+                x[j] = v.y > 0.f ? *reinterpret_cast<const float4*>(src + (int64_t)(i + j) * D + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc.x = fmaf(w[j], x[j].x, acc.x); acc.y = fmaf(w[j], x[j].y, acc.y);
+                acc.z = fmaf(w[j], x[j].z, acc.z); acc.w = fmaf(w[j], x[j].w, acc.w);
+            }
         }
-        o[row * D + d] = (OT)(acc * inv);
+        for (; i < P; ++i) {
+            const float2 v = mlr[i];
+            if (v.y > 0.f) {
+                const float w = exp2f(v.x - M);
+                const float4 x = *reinterpret_cast<const float4*>(src + (int64_t)i * D + d);
+                acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y); acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+            }
+        }
+        store4<OT>(o + row * D + d, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
     }
     if (lane == 0 && lse) lse[row] = L > 0.f ? M + log2f(L) : -INFINITY;
 }
@@ -186,22 +564,22 @@ struct DecodeTopkParams {
     int32_t* out;            // [B, Hk, T]
 };
 
-__global__ void __launch_bounds__(128) decode_topk_kernel(const DecodeTopkParams p) {
+__global__ void __launch_bounds__(256) decode_topk_kernel(const DecodeTopkParams p) {
     extern __shared__ float tsm[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* bs = tsm + (size_t)warp * (p.max_blocks + 64);
-    int* sel = reinterpret_cast<int*>(bs + p.max_blocks);
-    const int wid = blockIdx.x * 4 + warp;
-    if (wid >= p.B * p.Hk) return;
-    const int b = wid / p.Hk, h = wid % p.Hk;
+    float* bs = tsm;                                         // [max_blocks] bf16-rounded block scores
+    int* sel = reinterpret_cast<int*>(bs + p.max_blocks);    // [64] winners in selection order
+    __shared__ float wbest[8];
+    __shared__ int wbi[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x / p.Hk, h = blockIdx.x % p.Hk;
     const int t = p.seq_len[b] - 1;
     const int ncmp = p.ncmp[b];
     const float lse = p.lse[(int64_t)b * p.Hq + h * p.G];
     const float* row = p.scores + ((int64_t)b * p.Hk + h) * p.ld;
     const int bq = t / p.BK;
-    const int nb = min(bq + 1, p.max_blocks);
+    const int nb = t >= 0 ? min(bq + 1, p.max_blocks) : 0;
     const int bstride = p.BK / p.stride, pad = p.ks / p.stride - 1;
-    for (int blk = lane; blk < nb; blk += 32) {
+    for (int blk = tid; blk < nb; blk += 256) {
         float s = 0.f;
         for (int o = 0; o < p.nw; ++o) {
             int c = blk * bstride - pad + o;
@@ -211,11 +589,11 @@ __global__ void __launch_bounds__(128) decode_topk_kernel(const DecodeTopkParams
         if (blk < p.init_blocks || (bq >= blk && bq < blk + p.local_blocks)) s = INFINITY;
         bs[blk] = __bfloat162float(__float2bfloat16(s));
     }
-    __syncwarp();
+    __syncthreads();
     const int nsel = min(p.T, nb);
     for (int r = 0; r < nsel; ++r) {
         float best = -INFINITY; int bi = 0x7fffffff;
-        for (int blk = lane; blk < nb; blk += 32) {
+        for (int blk = tid; blk < nb; blk += 256) {
             float v = bs[blk];
             if (v > best || (v == best && blk < bi)) { best = v; bi = blk; }
         }
@@ -225,13 +603,21 @@ __global__ void __launch_bounds__(128) decode_topk_kernel(const DecodeTopkParams
             int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
-        if (lane == 0) { sel[r] = bi; bs[bi] = -INFINITY; }
-        __syncwarp();
+        if (lane == 0) { wbest[warp] = best; wbi[warp] = bi; }
+        __syncthreads();
+        if (tid == 0) {
+#pragma unroll
+            for (int w = 1; w < 8; ++w)
+                if (wbest[w] > best || (wbest[w] == best && wbi[w] < bi)) { best = wbest[w]; bi = wbi[w]; }
+            sel[r] = bi;
+            bs[bi] = -INFINITY;      // taken (a block whose score is -inf can only win once nothing else is left)
+        }
+        __syncthreads();
     }
     int32_t* out = p.out + ((int64_t)b * p.Hk + h) * p.T;
-    for (int i = lane; i < p.T; i += 32)
+    for (int i = tid; i < p.T; i += 256)
         if (i >= nsel) out[i] = -1;
-    for (int i = lane; i < nsel; i += 32) {
+    for (int i = tid; i < nsel; i += 256) {
         int v = sel[i], rank = 0;
         for (int j = 0; j < nsel; ++j) rank += sel[j] < v;
         out[rank] = v;
@@ -272,59 +658,102 @@ __global__ void decode_ranges_kernel(const int32_t* __restrict__ topk_idx, const
     }
 }
 
-template <int D, int G, typename ET>
-static cudaError_t launch_partial(const DecodeParams& p, cudaStream_t stream) {
-    size_t smem = (size_t)(2 * G * D + G * p.chunk) * sizeof(float);
-    auto kern = decode_partial_kernel<D, G, ET>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+// Visible compressed tokens of the decoded row and the cache rows of this GPU's share of them.
+__global__ void decode_cmp_ranges_kernel(const int* __restrict__ seq_len, const int* __restrict__ cmp_row0, int B, int Hk, int ks, int stride,
+                                         int cmp_lo, int cmp_hi, int* __restrict__ num_cmp, int* __restrict__ lo_out, int* __restrict__ hi_out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B * Hk) return;
+    const int b = i / Hk;
+    const int len = seq_len[b];
+    const int n = len >= ks ? (len - ks) / stride + 1 : 0;
+    if (i % Hk == 0) num_cmp[b] = n;
+    const int e = min(n, cmp_hi) - cmp_lo;
+    lo_out[i] = e > 0 ? cmp_row0[b] : -1;
+    hi_out[i] = e > 0 ? cmp_row0[b] + e : -1;
+}
+
+template <int D, bool HI, typename ET>
+static cudaError_t launch_partial(int G, const DecodeParams& p, cudaStream_t stream) {
+    size_t smem = (size_t)(4 * G * D + 8 * G) * sizeof(float);
+    auto kern = decode_partial_kernel<D, HI, ET>;
     kern<<<(unsigned)((int64_t)p.B * p.Hk * p.R * p.nchunk), 128, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
-template <int D, typename ET>
-static cudaError_t dispatch_g(int G, const DecodeParams& p, cudaStream_t stream) {
-    switch (G) {
-        case 1: return launch_partial<D, 1, ET>(p, stream);
-        case 2: return launch_partial<D, 2, ET>(p, stream);
-        case 4: return launch_partial<D, 4, ET>(p, stream);
-        case 8: return launch_partial<D, 8, ET>(p, stream);
-        case 16: return launch_partial<D, 16, ET>(p, stream);
-        default: return cudaErrorInvalidValue;
+template <int D, bool HI, typename ET>
+static cudaError_t launch_partial_tma(DecodeParams p, const CUtensorMap& kmap, const CUtensorMap& vmap, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = 2 * (D / 64) * 64 * 128;
+    p.nst = min(max((p.chunk + kDecKT - 1) / kDecKT * p.rpp, 1), 3);
+    const size_t smem = (size_t)p.nst * STAGE_BYTES + 1024 /* alignment slack */ + 1024 /* barriers, statistics */;
+    auto kern = decode_partial_tma<D, HI, ET>;
+    static int attr_dev_mask = 0;                          // the attribute is per device; set it once for each
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!(attr_dev_mask >> (dev & 31) & 1)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * STAGE_BYTES + 2048);
+        if (e != cudaSuccess) return e;
+        attr_dev_mask |= 1 << (dev & 31);
     }
+    kern<<<(unsigned)((int64_t)p.B * p.Hk * p.NP * p.nchunk), 160, smem, stream>>>(p, kmap, vmap);
+    return cudaGetLastError();
+}
+
+template <int D, typename ET>
+static cudaError_t dispatch_g(int G, const DecodeParams& p, const CUtensorMap* kmap, const CUtensorMap* vmap, cudaStream_t stream) {
+    if (G < 1 || G > 16) return cudaErrorInvalidValue;
+    if (kmap) return G > 8 ? launch_partial_tma<D, true, ET>(p, *kmap, *vmap, stream) : launch_partial_tma<D, false, ET>(p, *kmap, *vmap, stream);
+    return G > 8 ? launch_partial<D, true, ET>(G, p, stream) : launch_partial<D, false, ET>(G, p, stream);
 }
 
 }  // namespace fsa
 
 using namespace fsa;
 
-extern "C" int fsa_decode_attn_partial(const void* q, const void* k, const void* v, int64_t kv_stride_n, const int32_t* rng_lo,
+extern "C" int fsa_decode_attn_partial(const void* q, const void* k, const void* v, int64_t kv_rows, int64_t kv_stride_n, const int32_t* rng_lo,
                                        const int32_t* rng_hi, int batch, int num_q_heads, int num_kv_heads, int head_dim,
-                                       int num_ranges, int chunk, int num_chunks, int dtype, float sm_scale, float* o_part,
+                                       int num_ranges, int ranges_per_partial, int chunk, int num_chunks, int dtype, float sm_scale, float* o_part,
                                        float* ml, float* scores, int64_t scores_ld, void* stream) {
     if (!q || !k || !v || !rng_lo || !rng_hi || !o_part || !ml) return FSA_ERR_BAD_ARG;
     if (batch <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_ranges <= 0 || chunk <= 0 || num_chunks <= 0)
         return FSA_ERR_BAD_ARG;
-    if (chunk > 1024 || (kv_stride_n % 8) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15)) return FSA_ERR_BAD_ARG;
+    if ((kv_stride_n % 8) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15)) return FSA_ERR_BAD_ARG;
     const int G = num_q_heads / num_kv_heads;
     DecodeParams p;
     p.q = q; p.k = k; p.v = v; p.kv_sn = kv_stride_n; p.rng_lo = rng_lo; p.rng_hi = rng_hi;
     p.B = batch; p.Hq = num_q_heads; p.Hk = num_kv_heads; p.R = num_ranges; p.chunk = chunk; p.nchunk = num_chunks;
     p.scale_log2 = sm_scale * 1.4426950408889634f;
-    p.o_part = o_part; p.ml = (float2*)ml; p.scores = scores; p.scores_ld = scores_ld;
+    p.o_part = o_part; p.ml = (float2*)ml; p.scores = scores; p.scores_ld = scores_ld; p.nst = 1;
+    if (ranges_per_partial < 1 || (ranges_per_partial > 1 && num_chunks != 1)) return FSA_ERR_BAD_ARG;
+    p.rpp = ranges_per_partial;
+    p.NP = (num_ranges + ranges_per_partial - 1) / ranges_per_partial;
+    if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
+    if (head_dim != 128 && head_dim != 64) return FSA_ERR_UNSUPPORTED;
     (void)cudaGetLastError();
+    // K/V rows are streamed by TMA (tensor maps over [kv_rows, Hk * D]); FSA_DECODE_LDG=1 selects the kernel that
+    // loads its fragments straight from global memory instead (kept for comparison).
+    static const bool use_ldg = [] { const char* v = getenv("FSA_DECODE_LDG"); return v && *v == '1'; }();
+    CUtensorMap kmap, vmap;
+    const CUtensorMap *km = nullptr, *vm = nullptr;
+    if (use_ldg && ranges_per_partial != 1) return FSA_ERR_UNSUPPORTED;
+    if (!use_ldg) {
+        if (kv_rows <= 0) return FSA_ERR_BAD_ARG;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return FSA_ERR_CUDA;   // binds the context
+        int rc = make_tile_map(&kmap, k, dtype, kv_rows, (int64_t)num_kv_heads * head_dim, kv_stride_n, kDecKT);
+        if (rc) return rc;
+        rc = make_tile_map(&vmap, v, dtype, kv_rows, (int64_t)num_kv_heads * head_dim, kv_stride_n, kDecKT);
+        if (rc) return rc;
+        km = &kmap;
+        vm = &vmap;
+    }
     cudaError_t e = cudaErrorInvalidValue;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == FSA_DTYPE_BF16) {
-        if (head_dim == 128) e = dispatch_g<128, __nv_bfloat16>(G, p, st);
-        else if (head_dim == 64) e = dispatch_g<64, __nv_bfloat16>(G, p, st);
-        else return FSA_ERR_UNSUPPORTED;
-    } else if (dtype == FSA_DTYPE_FP16) {
-        if (head_dim == 128) e = dispatch_g<128, __half>(G, p, st);
-        else if (head_dim == 64) e = dispatch_g<64, __half>(G, p, st);
-        else return FSA_ERR_UNSUPPORTED;
+        if (head_dim == 128) e = dispatch_g<128, __nv_bfloat16>(G, p, km, vm, st);
+        else e = dispatch_g<64, __nv_bfloat16>(G, p, km, vm, st);
     } else {
-        return FSA_ERR_BAD_ARG;
+        if (head_dim == 128) e = dispatch_g<128, __half>(G, p, km, vm, st);
+        else e = dispatch_g<64, __half>(G, p, km, vm, st);
     }
     if (e == cudaErrorInvalidValue) return FSA_ERR_UNSUPPORTED;
     return e == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
@@ -332,7 +761,8 @@ extern "C" int fsa_decode_attn_partial(const void* q, const void* k, const void*
 
 extern "C" int fsa_lse_merge(const float* o_part, const float* ml, int64_t rows, int num_partials, int part_stride, int head_dim, int out_dtype,
                              void* o, float* lse, void* stream) {
-    if (!o_part || !ml || !o || rows < 0 || num_partials <= 0 || part_stride < num_partials || head_dim <= 0) return FSA_ERR_BAD_ARG;
+    if (!o_part || !ml || !o || rows < 0 || num_partials <= 0 || part_stride < num_partials || head_dim <= 0 || head_dim % 4) return FSA_ERR_BAD_ARG;
+    if (((uintptr_t)o_part & 15) || ((uintptr_t)o & 7)) return FSA_ERR_BAD_ARG;
     if (rows == 0) return FSA_OK;
     (void)cudaGetLastError();
     unsigned grid = (unsigned)((rows + 7) / 8);
@@ -368,12 +798,14 @@ extern "C" int fsa_decode_select_topk(const float* scores, int64_t scores_ld, in
     for (int i = 0; i < a; ++i)
         for (int j = 0; j < bb; ++j) p.w[i + j] += 1.f;
     p.out = topk_idx;
-    size_t smem = (size_t)4 * (max_blocks + 64) * sizeof(float);
+    size_t smem = (size_t)(max_blocks + 64) * sizeof(float);
     if (smem > 200 * 1024) return FSA_ERR_UNSUPPORTED;
     (void)cudaGetLastError();
-    cudaError_t e = cudaFuncSetAttribute(decode_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return FSA_ERR_CUDA;
-    decode_topk_kernel<<<(unsigned)((batch * num_kv_heads + 3) / 4), 128, smem, (cudaStream_t)stream>>>(p);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(decode_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return FSA_ERR_CUDA;
+    }
+    decode_topk_kernel<<<(unsigned)(batch * num_kv_heads), 256, smem, (cudaStream_t)stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
 }
 
@@ -390,4 +822,21 @@ extern "C" int fsa_decode_ranges(const int32_t* topk_idx, const int32_t* seq_len
                                                                              block_size, window, piece, num_window_pieces, shard_lo,
                                                                              shard_hi, rng_lo, rng_hi);
     return cudaGetLastError() == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
+}
+
+extern "C" int fsa_decode_cmp_ranges(const int32_t* seq_len, const int32_t* cmp_row0, int batch, int num_kv_heads, int kernel_size,
+                                     int kernel_stride, int cmp_lo, int cmp_hi, int32_t* num_cmp, int32_t* rng_lo, int32_t* rng_hi,
+                                     void* stream) {
+    if (!seq_len || !cmp_row0 || !num_cmp || !rng_lo || !rng_hi || batch <= 0 || num_kv_heads <= 0 || kernel_size <= 0 || kernel_stride <= 0)
+        return FSA_ERR_BAD_ARG;
+    (void)cudaGetLastError();
+    const int total = batch * num_kv_heads;
+    decode_cmp_ranges_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(seq_len, cmp_row0, batch, num_kv_heads, kernel_size,
+                                                                                 kernel_stride, cmp_lo, cmp_hi, num_cmp, rng_lo, rng_hi);
+    return cudaGetLastError() == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
+}
+
+extern "C" int fsa_decode_read_status(int* status_out) {
+    if (!status_out) return FSA_ERR_BAD_ARG;
+    return cudaMemcpyFromSymbol(status_out, g_decode_status, sizeof(int)) == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
 }

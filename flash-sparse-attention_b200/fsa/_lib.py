@@ -79,15 +79,18 @@ SIGNATURES = {
                                  c_void_p, c_void_p, c_void_p]),
     "fsa_decode_attn_partial": (
         c_int,
-        [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p],
     ),
+    "fsa_decode_read_status": (c_int, [c_void_p]),
     "fsa_lse_merge": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fsa_decode_select_topk": (
         c_int,
         [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_int, c_int, c_void_p, c_void_p],
     ),
+    "fsa_decode_cmp_ranges": (
+        c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "fsa_decode_ranges": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],

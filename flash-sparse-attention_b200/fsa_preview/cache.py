@@ -44,6 +44,8 @@ class DecodeCache:
         self.cmp_row0 = ar * self.cmp_cap
         self.tail_row0 = (ar * kernel_size).long()
         self.host_len = [0] * batch
+        # True: always run the compressor with masked writes, so that every step issues the same launches (graph capture)
+        self.always_compress = False
 
     # ---------------------------------------------------------------- bulk load after a prefill
     @torch.no_grad()
@@ -92,7 +94,7 @@ class DecodeCache:
         self.seq_len += 1
         new_host = [L + 1 for L in self.host_len]
         self.host_len = new_host
-        if not any(L >= self.ks and (L - self.ks) % self.stride == 0 for L in new_host):
+        if not self.always_compress and not any(L >= self.ks and (L - self.ks) % self.stride == 0 for L in new_host):
             return
         n = t + 1
         emit = (n >= self.ks) & ((n - self.ks) % self.stride == 0)

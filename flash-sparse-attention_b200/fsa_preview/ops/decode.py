@@ -26,14 +26,14 @@ class CudaDecodeOps:
         if not t.is_cuda:
             raise RuntimeError("the sm_100a decode kernels need CUDA tensors (there is no CPU fallback)")
 
-    def attn_partial(self, q, k, v, rng_lo, rng_hi, chunk, nchunk, sm_scale, want_scores=False):
-        """q [B,Hq,D]; k, v [rows,Hk,D]; rng_* [B,Hk,R] int32.  Returns o_part [B,Hq,P,D] fp32, ml [B,Hq,P,2],
-        scores [B,Hk,chunk*nchunk] fp32 or None."""
+    def attn_partial(self, q, k, v, rng_lo, rng_hi, chunk, nchunk, sm_scale, want_scores=False, rpp=1):
+        """q [B,Hq,D]; k, v [rows,Hk,D]; rng_* [B,Hk,R] int32.  ``rpp`` consecutive ranges share one partial.  Returns
+        o_part [B,Hq,P,D] fp32, ml [B,Hq,P,2] with P = ceil(R/rpp)*nchunk, scores [B,Hk,chunk*nchunk] fp32 or None."""
         self._need_cuda(q)
         B, Hq, D = q.shape
         Hk = k.shape[1]
         R = rng_lo.shape[-1]
-        P = R * nchunk
+        P = -(-R // rpp) * nchunk
         assert k.stride(2) == 1 and k.stride(1) == D and v.stride() == k.stride() and q.is_contiguous()
         o_part = torch.empty((B, Hq, P, D), dtype=torch.float32, device=q.device)
         ml = torch.empty((B, Hq, P, 2), dtype=torch.float32, device=q.device)
@@ -41,7 +41,7 @@ class CudaDecodeOps:
         scores = torch.empty((B, Hk, ld), dtype=torch.float32, device=q.device) if want_scores else None
         with torch.cuda.device(q.device):
             rc = _lib.lib().fsa_decode_attn_partial(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), k.stride(0), _lib.ptr(rng_lo), _lib.ptr(rng_hi), B, Hq, Hk, D, R, chunk,
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), k.shape[0], k.stride(0), _lib.ptr(rng_lo), _lib.ptr(rng_hi), B, Hq, Hk, D, R, rpp, chunk,
                 nchunk, _lib.DTYPE_CODE[q.dtype], float(sm_scale), _lib.ptr(o_part), _lib.ptr(ml), _lib.ptr(scores), ld,
                 _lib.current_stream(q.device))
         _lib.check(rc, "fsa_decode_attn_partial")
@@ -75,6 +75,20 @@ class CudaDecodeOps:
                 _lib.current_stream(scores.device))
         _lib.check(rc, "fsa_decode_select_topk")
         return out
+
+    def cmp_ranges(self, seq_len, cmp_row0, num_kv_heads, kernel_size, kernel_stride, cmp_lo, cmp_hi):
+        """num_cmp [B] and the compressed-cache row range [B, Hk, 1] of this GPU's visible compressed tokens."""
+        self._need_cuda(seq_len)
+        B = seq_len.numel()
+        num_cmp = torch.empty(B, dtype=torch.int32, device=seq_len.device)
+        lo = torch.empty((B, num_kv_heads, 1), dtype=torch.int32, device=seq_len.device)
+        hi = torch.empty_like(lo)
+        with torch.cuda.device(seq_len.device):
+            rc = _lib.lib().fsa_decode_cmp_ranges(_lib.ptr(seq_len), _lib.ptr(cmp_row0), B, num_kv_heads, kernel_size, kernel_stride,
+                                                  cmp_lo, min(cmp_hi, 2**31 - 1), _lib.ptr(num_cmp), _lib.ptr(lo), _lib.ptr(hi),
+                                                  _lib.current_stream(seq_len.device))
+        _lib.check(rc, "fsa_decode_cmp_ranges")
+        return num_cmp, lo, hi
 
     def ranges(self, topk_idx, seq_len, seq_row0, num_kv_heads, topk, block_size, window, piece, num_pieces, shard_lo, shard_hi):
         self._need_cuda(seq_len)
@@ -144,7 +158,57 @@ def nsa_decode_attention(
     cmp_row0: torch.Tensor,          # [B] int32: compressed-cache row of compressed token shard.cmp_lo
     *, kernel_size: int, kernel_stride: int, block_size: int, topk: int, init_blocks: int, local_blocks: int,
     window_size: int, max_len: int, sm_scale: Optional[float] = None, shard: Optional[Shard] = None, ops=None,
-    cmp_chunk: int = 256,
+    cmp_chunk: int = 512,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The three NSA branches for ONE new token per sequence; the token is the last of its sequence and gets
+    what the prefill path gives that row.  Returns (o_cmp, o_sel, o_win [B,Hq,D], lse_cmp, lse_sel, lse_win
+    [B,Hq] log2 units, topk_idx [B,Hk,T]).  ``max_len`` (host int) bounds every sequence length."""
+    ops = ops or CudaDecodeOps()
+    shard = shard or Shard()
+    B, Hq, D = q.shape
+    Hk = k.shape[1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    # ---- compressed branch: compressed token c is visible when its window ends at or before t (c*stride + ks - 1 <= t)
+    num_cmp, lo_c, hi_c = ops.cmp_ranges(seq_len, cmp_row0, Hk, kernel_size, kernel_stride, shard.cmp_lo, shard.cmp_hi)
+    max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
+    cper = max(-(-max_cmp // world), 1)
+    cper = -(-cper // 4) * 4
+    return Shard(rank * per, (rank + 1) * per, rank * cper, (rank + 1) * cper, rank, world, group)
+
+
+def _gather(t: torch.Tensor, shard: Shard) -> torch.Tensor:
+    """All-gather ``t`` from every rank of the shard's group: [world, *t.shape]."""
+    import torch.distributed as dist
+
+    out = torch.empty((shard.world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=shard.group)
+    return out.view(shard.world, *t.shape)
+
+
+def _merge_ranks(ops, o_loc, lse_loc, shard: Shard, out_dtype):
+    """Second-level merge across GPUs: every rank contributes its normalised fp32 output and its lse;
+    a rank with no visible key has lse = -inf and weight 0."""
+    if shard.world == 1:
+        return o_loc.to(out_dtype), lse_loc
+    o_all = _gather(o_loc, shard)                                # [W, B, Hq, D]
+    lse_all = _gather(lse_loc, shard)                            # [W, B, Hq]
+    o_part = o_all.permute(1, 2, 0, 3).contiguous()
+    m = lse_all.permute(1, 2, 0)
+    ml = torch.stack([m, torch.isfinite(m).to(torch.float32)], dim=-1).contiguous()
+    return ops.lse_merge(o_part, ml, out_dtype)
+
+
+def nsa_decode_attention(
+    q: torch.Tensor,                 # [B, Hq, D] (already rotated)
+    k: torch.Tensor, v: torch.Tensor,            # cache rows [rows, Hk, D] of this GPU (k rotated)
+    cmp_k: torch.Tensor, cmp_v: torch.Tensor,    # compressed cache rows of this GPU
+    seq_len: torch.Tensor,           # [B] int32: tokens per sequence INCLUDING the decoded one
+    seq_row0: torch.Tensor,          # [B] int32: cache row of token shard.tok_lo of each sequence
+    cmp_row0: torch.Tensor,          # [B] int32: compressed-cache row of compressed token shard.cmp_lo
+    *, kernel_size: int, kernel_stride: int, block_size: int, topk: int, init_blocks: int, local_blocks: int,
+    window_size: int, max_len: int, sm_scale: Optional[float] = None, shard: Optional[Shard] = None, ops=None,
+    cmp_chunk: int = 512,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """The three NSA branches for ONE new token per sequence; the token is the last of its sequence and gets
     what the prefill path gives that row.  Returns (o_cmp, o_sel, o_win [B,Hq,D], lse_cmp, lse_sel, lse_win
@@ -183,10 +247,11 @@ def nsa_decode_attention(
     piece = block_size
     npieces = -(-(window_size + 1) // piece)
     lo, hi = ops.ranges(topk_idx, seq_len, seq_row0, Hk, topk, block_size, window_size, piece, npieces, shard.tok_lo, shard.tok_hi)
-    o_part, ml, _ = ops.attn_partial(q, k, v, lo, hi, piece, 1, sm_scale)
+    rpp = 4 if topk % 4 == 0 else (2 if topk % 2 == 0 else 1)     # a partial never mixes selected blocks and window pieces
+    o_part, ml, _ = ops.attn_partial(q, k, v, lo, hi, piece, 1, sm_scale, rpp=rpp)
     first = torch.float32 if shard.world > 1 else q.dtype
-    o_sel, lse_sel = ops.lse_merge(o_part, ml, first, 0, topk)
-    o_win, lse_win = ops.lse_merge(o_part, ml, first, topk, npieces)
+    o_sel, lse_sel = ops.lse_merge(o_part, ml, first, 0, topk // rpp)
+    o_win, lse_win = ops.lse_merge(o_part, ml, first, topk // rpp, -(-npieces // rpp))
     if shard.world > 1:
         both, lse_both = _merge_ranks(ops, torch.stack([o_sel, o_win], 2).flatten(1, 2), torch.stack([lse_sel, lse_win], 2).flatten(1, 2),
                                       shard, q.dtype)

@@ -200,16 +200,23 @@ int fsa_gate_mix_bwd(const void* gate, const void* a, const void* b, const void*
  * forward_kernel_decode and score_kernel_decode (fsa_preview/ops/compressed_attention_decode.py:361-592),
  * _topk_sparse_attention_decode (fsa_preview/ops/selected_attention_decode.py:8-42) and the window call
  * (fsa_preview/module/fsa_decode.py:175-185).
- *   q [B, Hq, D]; k, v [rows, Hk, D] with row stride kv_stride_n; rng_lo / rng_hi [B, Hk, R]: range r of
+ *   q [B, Hq, D]; k, v [kv_rows, Hk, D] with row stride kv_stride_n (kv_rows bounds the TMA tensor map); rng_lo / rng_hi [B, Hk, R]: range r of
  *   (sequence, kv head) covers the rows [lo, hi) (lo = -1: empty).  Every range is cut into num_chunks chunks
- *   of `chunk` rows (chunk * num_chunks >= the longest range); partial (b, head, r * num_chunks + c) receives
+ *   of `chunk` rows (chunk * num_chunks >= the longest range); with ranges_per_partial = n > 1 (num_chunks must
+ *   be 1) n consecutive ranges share one softmax and one partial, P = ceil(R / n) * num_chunks; partial
+ *   (b, head, (r / n) * num_chunks + c) receives
  *   o_part [B, Hq, P, D] fp32 (unnormalised) and ml [B, Hq, P, 2] = (max logit in log2 units, sum of exp2).
  *   scores (optional) [B, Hk, scores_ld]: the scaled log2 logits of each group's FIRST head over range 0,
  *   the input of fsa_decode_select_topk. */
-int fsa_decode_attn_partial(const void* q, const void* k, const void* v, int64_t kv_stride_n, const int32_t* rng_lo,
+int fsa_decode_attn_partial(const void* q, const void* k, const void* v, int64_t kv_rows, int64_t kv_stride_n, const int32_t* rng_lo,
                             const int32_t* rng_hi, int batch, int num_q_heads, int num_kv_heads, int head_dim,
-                            int num_ranges, int chunk, int num_chunks, int dtype, float sm_scale, float* o_part, float* ml,
+                            int num_ranges, int ranges_per_partial, int chunk, int num_chunks, int dtype, float sm_scale,
+                            float* o_part, float* ml,
                             float* scores, int64_t scores_ld, void* stream);
+
+/* Device status word of the decode kernels: 0, or 1 after a bounded wait ran out (the step's results are then
+ * invalid).  Synchronises with the device.  No reference counterpart. */
+int fsa_decode_read_status(int* status_out);
 
 /* Log-sum-exp merge of P partials per row: o = sum w_p o_p / sum w_p l_p, w_p = exp2(m_p - max m), lse = max m +
  * log2 sum w_p l_p.  Used inside one GPU (chunks, blocks) and across GPUs (after an all-gather of the partials;
@@ -230,6 +237,13 @@ int fsa_decode_select_topk(const float* scores, int64_t scores_ld, int shard_len
                            const int32_t* num_cmp, int batch, int num_q_heads, int num_kv_heads, int kernel_size,
                            int kernel_stride, int block_size, int init_blocks, int local_blocks, int topk, int max_blocks,
                            int32_t* topk_idx, void* stream);
+
+/* Visible compressed tokens of the decoded row, num_cmp[b] = floor((seq_len - kernel_size) / kernel_stride) + 1 (0 when
+ * the sequence is shorter than a window; fsa_preview/module/fsa_decode.py:87-91), and this GPU's rows of them: compressed
+ * tokens [cmp_lo, cmp_hi) are stored from row cmp_row0[b] on.  rng_lo / rng_hi [B, Hk, 1]. */
+int fsa_decode_cmp_ranges(const int32_t* seq_len, const int32_t* cmp_row0, int batch, int num_kv_heads, int kernel_size,
+                          int kernel_stride, int cmp_lo, int cmp_hi, int32_t* num_cmp, int32_t* rng_lo, int32_t* rng_hi,
+                          void* stream);
 
 /* Cache-row ranges of the selected blocks (ranges 0..topk-1, from topk_idx [B, Hk, topk]) and of the sliding window
  * [max(0, t - window), t] cut into num_window_pieces pieces of `piece` rows (ranges topk..), for t = seq_len[b] - 1,

@@ -80,12 +80,14 @@ def decode_branches_ref(q, k_seqs, v_seqs, ck_seqs, cv_seqs, cfg, sm_scale=None,
 class OracleDecodeOps:
     """CPU restatement of the decode step's device operators (same call signatures as the CUDA operator set)."""
 
-    def attn_partial(self, q, k, v, rng_lo, rng_hi, chunk, nchunk, sm_scale, want_scores=False):
+    def attn_partial(self, q, k, v, rng_lo, rng_hi, chunk, nchunk, sm_scale, want_scores=False, rpp=1):
         B, Hq, D = q.shape
         Hk = k.shape[1]
         G = Hq // Hk
         R = rng_lo.shape[-1]
-        P = R * nchunk
+        NP = -(-R // rpp)
+        assert rpp == 1 or nchunk == 1
+        P = NP * nchunk
         o_part = torch.zeros(B, Hq, P, D)
         ml = torch.zeros(B, Hq, P, 2)
         ml[..., 0] = float("-inf")
@@ -93,22 +95,25 @@ class OracleDecodeOps:
         for b in range(B):
             for h in range(Hk):
                 qg = q[b, h * G : (h + 1) * G].float()
-                for r in range(R):
-                    lo_r, hi_r = int(rng_lo[b, h, r]), int(rng_hi[b, h, r])
-                    if lo_r < 0:
-                        continue
+                for pr in range(NP):
                     for c in range(nchunk):
-                        lo, hi = lo_r + c * chunk, min(hi_r, lo_r + (c + 1) * chunk)
-                        if lo >= hi:
+                        rows = []
+                        for r in range(pr * rpp, min(R, pr * rpp + rpp)):
+                            lo_r, hi_r = int(rng_lo[b, h, r]), int(rng_hi[b, h, r])
+                            if lo_r < 0:
+                                continue
+                            lo, hi = lo_r + c * chunk, min(hi_r, lo_r + (c + 1) * chunk)
+                            rows += list(range(lo, hi))
+                            if want_scores and r == 0 and lo < hi:
+                                scores[b, h, lo - lo_r : hi - lo_r] = (qg[0] @ k[lo:hi, h].float().t()) * (sm_scale * LOG2E)
+                        if not rows:
                             continue
-                        s = (qg @ k[lo:hi, h].float().t()) * (sm_scale * LOG2E)
+                        s = (qg @ k[rows, h].float().t()) * (sm_scale * LOG2E)
                         m = s.max(1).values
                         p = torch.exp2(s - m[:, None])
-                        o_part[b, h * G : (h + 1) * G, r * nchunk + c] = p @ v[lo:hi, h].float()
-                        ml[b, h * G : (h + 1) * G, r * nchunk + c, 0] = m
-                        ml[b, h * G : (h + 1) * G, r * nchunk + c, 1] = p.sum(1)
-                        if want_scores and r == 0:
-                            scores[b, h, lo - lo_r : hi - lo_r] = s[0]
+                        o_part[b, h * G : (h + 1) * G, pr * nchunk + c] = p @ v[rows, h].float()
+                        ml[b, h * G : (h + 1) * G, pr * nchunk + c, 0] = m
+                        ml[b, h * G : (h + 1) * G, pr * nchunk + c, 1] = p.sum(1)
         return o_part, ml, scores
 
     def lse_merge(self, o_part, ml, out_dtype, p0=0, pn=None):
@@ -141,6 +146,20 @@ class OracleDecodeOps:
                 bs = block_scores_ref(p, t, kernel_size, kernel_stride, block_size, init_blocks, local_blocks)
                 out[b, h] = torch.tensor(topk_from_block_scores(bs[:max_blocks], topk), dtype=torch.int32)
         return out
+
+    def cmp_ranges(self, seq_len, cmp_row0, num_kv_heads, kernel_size, kernel_stride, cmp_lo, cmp_hi):
+        B = seq_len.numel()
+        num_cmp = torch.zeros(B, dtype=torch.int32)
+        lo = torch.full((B, num_kv_heads, 1), -1, dtype=torch.int32)
+        hi = torch.full((B, num_kv_heads, 1), -1, dtype=torch.int32)
+        for b in range(B):
+            L = int(seq_len[b])
+            n = (L - kernel_size) // kernel_stride + 1 if L >= kernel_size else 0
+            num_cmp[b] = n
+            e = min(n, cmp_hi) - cmp_lo
+            if e > 0:
+                lo[b], hi[b] = int(cmp_row0[b]), int(cmp_row0[b]) + e
+        return num_cmp, lo, hi
 
     def ranges(self, topk_idx, seq_len, seq_row0, num_kv_heads, topk, block_size, window, piece, num_pieces, shard_lo, shard_hi):
         B = seq_len.numel()

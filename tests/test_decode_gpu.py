@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 from fsa.module.fsa import FlashSparseAttention  # noqa: E402
 from fsa.module.rope import RopeConfig  # noqa: E402
 from fsa.ops.linear_compress import compressed_seqlens, linear_compress  # noqa: E402
-from fsa_preview.module import FlashSparseAttentionDecode, FlashSparseAttentionDecodeKernel  # noqa: E402
+from fsa_preview.module import FlashSparseAttentionDecode, FlashSparseAttentionDecodeKernel, GraphedStep  # noqa: E402
 from fsa_preview.ops import _compressed_attention_decode, _topk_sparse_attention_decode  # noqa: E402
 from fsa_preview.ops.decode import CudaDecodeOps  # noqa: E402
 from oracle.decode_oracle import OracleDecodeOps, decode_branches_ref  # noqa: E402
@@ -19,7 +19,7 @@ DEV = "cuda:0"
 
 def _close(got, ref, what, max_tol=2e-2, mean_tol=1e-3):
     got, ref = got.float().cpu(), ref.float().cpu()
-    scale = max(1.0, float(ref.abs().max()) / 2)
+    scale = max(1.0, float(ref.detach().abs().max()) / 2)
     err = (got - ref).abs()
     assert float(err.max()) <= max_tol * scale, f"{what}: max-abs {float(err.max()):.3e}"
     assert float(err.mean()) <= mean_tol * scale, f"{what}: mean-abs {float(err.mean()):.3e}"
@@ -47,7 +47,8 @@ def test_attn_partial_and_merge(G, D, dtype):
     live = ref_ml[..., 1] > 0
     assert torch.equal((ml[..., 1] > 0).cpu(), live)
     torch.testing.assert_close(ml.cpu()[live], ref_ml[live], rtol=1e-4, atol=1e-4)
-    torch.testing.assert_close(o.cpu()[live], ref_o[live], rtol=1e-3, atol=1e-3)
+    # P is rounded to the input type before P V (as the prefill kernels and the reference do): bf16-sized errors
+    torch.testing.assert_close(o.cpu()[live], ref_o[live], rtol=2e-2, atol=3e-2)
     for b in range(B):
         for h in range(Hk):
             n = int(hi[b, h, 0] - lo[b, h, 0]) if lo[b, h, 0] >= 0 else 0
@@ -59,6 +60,71 @@ def test_attn_partial_and_merge(G, D, dtype):
         fin = torch.isfinite(rlse)
         assert torch.equal(torch.isfinite(glse).cpu(), fin)
         torch.testing.assert_close(glse.cpu()[fin], rlse[fin], rtol=1e-4, atol=1e-4)
+
+
+def test_decode_status_word_is_clean():
+    from ctypes import byref, c_int
+
+    from fsa import _lib
+
+    st = c_int(-1)
+    _lib.check(_lib.lib().fsa_decode_read_status(byref(st)), "fsa_decode_read_status")
+    assert st.value == 0
+
+
+@pytest.mark.parametrize("G,D,chunk,nchunk", [(4, 128, 512, 2), (16, 128, 256, 3), (2, 64, 192, 2), (8, 64, 64, 1)])
+def test_attn_partial_long_chunks(G, D, chunk, nchunk):
+    """Chunks of several 64-key pipeline stages (more stages than the ring holds), ragged tails."""
+    torch.manual_seed(G + D + chunk)
+    B, Hk, R, rows = 2, 2, 2, 3000
+    Hq = Hk * G
+    q = torch.randn(B, Hq, D).to(torch.bfloat16)
+    k = torch.randn(rows, Hk, D).to(torch.bfloat16)
+    v = torch.randn(rows, Hk, D).to(torch.bfloat16)
+    lo = torch.randint(0, rows - chunk * nchunk, (B, Hk, R), dtype=torch.int32)
+    ln = torch.randint(1, chunk * nchunk + 1, (B, Hk, R), dtype=torch.int32)
+    ln[0, 0, 0] = chunk * nchunk
+    lo[1, 1, 1] = rows - 37                                             # a range that ends at the last row of the tensor
+    ln[1, 1, 1] = 37
+    hi = lo + ln
+    ref_o, ref_ml, ref_s = OracleDecodeOps().attn_partial(q, k, v, lo, hi, chunk, nchunk, D ** -0.5, want_scores=True)
+    ops = CudaDecodeOps()
+    o, ml, s = ops.attn_partial(q.to(DEV), k.to(DEV), v.to(DEV), lo.to(DEV), hi.to(DEV), chunk, nchunk, D ** -0.5, want_scores=True)
+    go, glse = ops.lse_merge(o, ml, torch.float32)
+    ro, rlse = OracleDecodeOps().lse_merge(ref_o, ref_ml, torch.float32)
+    _close(go, ro, "merged o")
+    torch.testing.assert_close(glse.cpu(), rlse, rtol=1e-4, atol=1e-4)
+    for b in range(B):
+        for h in range(Hk):
+            n = int(ln[b, h, 0])
+            torch.testing.assert_close(s[b, h, :n].cpu(), ref_s[b, h, :n], rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("rpp,R", [(2, 5), (4, 8), (4, 25)])
+def test_attn_partial_ranges_per_partial(rpp, R):
+    """Several ranges folded into one partial (one online softmax over their keys), empty ranges in between."""
+    torch.manual_seed(rpp * 10 + R)
+    B, Hk, G, D, rows, piece = 2, 2, 4, 128, 2000, 64
+    Hq = Hk * G
+    q = torch.randn(B, Hq, D).to(torch.bfloat16)
+    k = torch.randn(rows, Hk, D).to(torch.bfloat16)
+    v = torch.randn(rows, Hk, D).to(torch.bfloat16)
+    lo = torch.randint(0, rows - piece, (B, Hk, R), dtype=torch.int32)
+    ln = torch.randint(1, piece + 1, (B, Hk, R), dtype=torch.int32)
+    lo[0, 0, 1] = -1
+    lo[1, 1, :rpp] = -1                                                  # a partial with no key at all
+    hi = torch.where(lo >= 0, lo + ln, lo)
+    ref_o, ref_ml, _ = OracleDecodeOps().attn_partial(q, k, v, lo, hi, piece, 1, D ** -0.5, rpp=rpp)
+    ops = CudaDecodeOps()
+    o, ml, _ = ops.attn_partial(q.to(DEV), k.to(DEV), v.to(DEV), lo.to(DEV), hi.to(DEV), piece, 1, D ** -0.5, rpp=rpp)
+    assert o.shape == ref_o.shape
+    live = ref_ml[..., 1] > 0
+    assert torch.equal((ml[..., 1] > 0).cpu(), live)
+    torch.testing.assert_close(ml.cpu()[live], ref_ml[live], rtol=1e-4, atol=1e-4)
+    go, glse = ops.lse_merge(o, ml, torch.float32)
+    ro, rlse = OracleDecodeOps().lse_merge(ref_o, ref_ml, torch.float32)
+    _close(go, ro, "merged o")
+    torch.testing.assert_close(glse.cpu(), rlse, rtol=1e-4, atol=1e-4)
 
 
 def test_select_topk_and_ranges_bit_exact():
@@ -217,3 +283,37 @@ def test_reference_named_ops():
     o_sel = _topk_sparse_attention_decode(q.to(DEV), torch.cat(k).to(DEV), torch.cat(v).to(DEV), idx, BK, cuq, cuk, 1, max(lens))
     ref = decode_branches_ref(q.float(), k, v, ck, cv, cfg, topk_idx=idx.transpose(0, 1).cpu())
     _close(o_sel, ref[1], "o_sel")
+
+
+def test_graphed_step_matches_eager_step():
+    """The captured step replays to the same outputs and cache state as the eager step, across a compression boundary."""
+    torch.manual_seed(21)
+    Hk, G, D, steps = 2, 4, 128, 20
+    Hq = Hk * G
+    seqlens = [100, 45, 31]
+    B = len(seqlens)
+    mod = FlashSparseAttentionDecodeKernel(Hq * D, Hq, Hk, D, **CFG).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(torch.randn_like(p) * 0.05)
+    ks, st = CFG["kernel_size"], CFG["kernel_stride"]
+    kp = torch.randn(sum(seqlens), Hk, D).to(torch.bfloat16).to(DEV)
+    vp = torch.randn(sum(seqlens), Hk, D).to(torch.bfloat16).to(DEV)
+    cu = torch.tensor([0] + list(torch.tensor(seqlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ck, _ = linear_compress(kp, mod.compress_key, cu, ks, st, mod.intra_block_pe, seqlens)
+    cv, _ = linear_compress(vp, mod.compress_value, cu, ks, st, None, seqlens)
+    caches = []
+    for _ in range(2):
+        c = mod.new_cache(B, 256, device=DEV)
+        c.load(kp, kp, vp, ck.detach(), cv.detach(), seqlens, compressed_seqlens(seqlens, ks, st))
+        caches.append(c)
+    ins = [torch.randn(steps, B, H, D).to(torch.bfloat16).to(DEV) for H in (Hq, Hk, Hk)]
+    graphed = GraphedStep(mod.step, caches[1], [x[0] for x in ins])
+    for s in range(steps):
+        a = mod.step(ins[0][s], ins[1][s], ins[2][s], caches[0])
+        b = graphed(ins[0][s], ins[1][s], ins[2][s])
+        assert torch.equal(a, b), f"step {s}"
+    assert torch.equal(caches[0].seq_len, caches[1].seq_len) and caches[0].host_len == caches[1].host_len
+    for n in ("k", "v", "cmp_k", "cmp_v"):
+        x, y = getattr(caches[0], n), getattr(caches[1], n)
+        assert torch.equal(x[:-1], y[:-1]), n
