@@ -200,7 +200,7 @@ def run_decode(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
     c = dict(DECODE_CFG)
     if args.case == "small":
-        c.update(batch=8, cache_len=32768)
+        c.update(batch=8)                   # 4.3 GB of cache: small enough for a profiler capture, larger than L2
     B, Lc, Hk, G, d = c["batch"], c["cache_len"], c["Hk"], c["G"], c["d"]
     Hq = Hk * G
     nsa = {n: c[n] for n in ("kernel_size", "kernel_stride", "block_size", "topk", "init_blocks", "local_blocks", "window_size")}
@@ -230,6 +230,7 @@ def run_decode(args, rank, world, local_rank):
                                                cache.cmp_row0, max_len=max_len, shard=shard, **nsa)
         return gate_mix(mod.gate(qd.view(B, -1)), oc, os_.contiguous(), ow.contiguous())
 
+    # N > 1: the step holds two NCCL all-gathers; capturing them in a graph stalled here, so the sharded step is launched eagerly
     use_graph = world == 1 and not args.no_graph
     step = eager_step
     if use_graph:
@@ -239,7 +240,7 @@ def run_decode(args, rank, world, local_rank):
                 eager_step()
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph), torch.no_grad():
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"), torch.no_grad():
             eager_step()
         step = graph.replay
 
@@ -281,7 +282,7 @@ def run_decode(args, rank, world, local_rank):
             cmp_pass()
         torch.cuda.synchronize()
         g_cmp = torch.cuda.CUDAGraph()                    # replayed, so that the host cost of a launch is not in the figure
-        with torch.cuda.graph(g_cmp):
+        with torch.cuda.graph(g_cmp, capture_error_mode="thread_local"):
             cmp_pass()
         ms_cmp = timed(g_cmp.replay, args.steps)
 
@@ -343,10 +344,113 @@ def run_decode(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+LAYER_CFG = dict(hidden=4096, Hq=32, Hk=8, d=128, kernel_size=32, kernel_stride=16, block_size=64, topk=16, init_blocks=1,
+                 local_blocks=2, window_size=512, rope_theta=500000.0, seqlens=[32768, 32768])
+LAYER_METRIC = "NSA layer fwd+bwd tokens/s (2x32768 tok, hidden 4096, 32 Q / 8 KV heads, d=128, ks=32/16, B_K=64, T=16, W=512)"
+
+
+def run_layer(args, rank, world, local_rank):
+    """Forward + backward of the whole FlashSparseAttention layer.  With N > 1 the heads are split over the ranks
+    (8/N KV heads and 32/N query heads each: the attention kernels need no collective); the layer output and the
+    gradient of the input are summed over the ranks with one NCCL all-reduce each, as any head-parallel layer does."""
+    import torch.distributed as dist
+
+    from fsa.module.fsa import FlashSparseAttention, RopeConfig
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = dict(LAYER_CFG)
+    if args.case == "small":
+        c["seqlens"] = [8192, 8192]
+    if c["Hk"] % world:
+        raise SystemExit(f"--gpus must divide the {c['Hk']} KV heads")
+    seqlens = c["seqlens"]
+    N = sum(seqlens)
+    rope = RopeConfig(max_position_embeddings=131072, head_dim=c["d"], rope_theta=c["rope_theta"])
+    layer = FlashSparseAttention(c["hidden"], c["Hq"] // world, c["Hk"] // world, c["d"], c["kernel_size"], c["kernel_stride"],
+                                 c["block_size"], c["topk"], c["init_blocks"], c["local_blocks"], c["window_size"], rope)
+    torch.manual_seed(11 + rank)
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.normal_(0, 0.02)
+    layer = layer.to(dev).to(torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    xh = torch.randn(N, c["hidden"], generator=g).to(torch.bfloat16).pin_memory()
+    dyh = torch.randn(N, c["hidden"], generator=g).to(torch.bfloat16).pin_memory()
+    cu = torch.tensor([0] + list(torch.tensor(seqlens).cumsum(0)), dtype=torch.int32, device=dev)
+    xd, dyd = xh.to(dev), dyh.to(dev)
+
+    def step(x=None, dy=None):
+        x = (xd if x is None else x).detach().requires_grad_(True)
+        y = layer(x, cu, seqlens)
+        if world > 1:
+            dist.all_reduce(y.data)
+        y.backward(dyd if dy is None else dy)
+        if world > 1:
+            dist.all_reduce(x.grad)
+        layer.zero_grad(set_to_none=True)
+        return y, x.grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(n):
+            fn()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / n
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_step = timed(step, args.steps)
+    clocks = sampler.stop()
+
+    def e2e_step():
+        y, gx = step(xh.to(dev, non_blocking=True), dyh.to(dev, non_blocking=True))
+        return torch.stack([y.float().norm(), gx.float().norm()]).cpu()
+
+    e2e_n = 0 if args.no_e2e else max(1, min(args.steps, 3))
+    if e2e_n:
+        e2e_step()
+        e2e_ms = timed(e2e_step, e2e_n)
+    if rank == 0:
+        line = {
+            "metric": LAYER_METRIC, "value": N / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded N(0,1) hidden states, N(0,0.02) weights)",
+            "config": {"workload": f"layer fwd+bwd: {len(seqlens)}x{seqlens[0]} tokens" + (" (small case)" if args.case == "small" else ""),
+                       "parallelism": f"head-parallel x{world}: {c['Hk'] // world} KV heads per GPU, all-reduce of the output and of dX only",
+                       "l2": "activations exceed L2"},
+            "roofline": None, "cpu_baseline": None,
+            "e2e": ({"value": N / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": 2 * xh.numel() * 2, "d2h_bytes_per_step": 8} if e2e_n else None),
+            "gpu_launches": None, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="sel_attn", choices=["sel_attn", "decode"],
-                    help="sel_attn (default): selected attention fwd+bwd, the headline; decode: one NSA decode step")
+    ap.add_argument("--workload", default="sel_attn", choices=["sel_attn", "decode", "layer"],
+                    help="sel_attn (default): selected attention fwd+bwd, the headline; decode: one NSA decode step; "
+                         "layer: the whole NSA layer fwd+bwd")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -367,6 +471,9 @@ def main():
         return
     if args.workload == "decode":
         run_decode(args, rank, world, local_rank)
+        return
+    if args.workload == "layer":
+        run_layer(args, rank, world, local_rank)
         return
 
     import torch.distributed as dist

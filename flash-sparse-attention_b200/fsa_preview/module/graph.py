@@ -34,7 +34,8 @@ class GraphedStep:
         cache.k_tail.copy_(tails[0])
         cache.v_tail.copy_(tails[1])
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph), torch.no_grad():
+        # thread_local: other threads of the process (a collective library's watchdog) may call into CUDA meanwhile
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"), torch.no_grad():
             self.static_out = fn(*self.static_in, cache)
         cache.seq_len.copy_(len0)                 # capture does not execute, but keep the invariant explicit
         cache.host_len = host0

@@ -127,24 +127,28 @@ def shard_plan(max_len: int, kernel_size: int, kernel_stride: int, rank: int, wo
     return Shard(rank * per, (rank + 1) * per, rank * cper, (rank + 1) * cper, rank, world, group)
 
 
-def _gather(t: torch.Tensor, shard: Shard) -> torch.Tensor:
-    """All-gather ``t`` from every rank of the shard's group: [world, *t.shape]."""
+def _gather(shard: Shard, *tensors: torch.Tensor):
+    """All-gather several fp32 tensors from every rank of the shard's group with ONE collective (they are packed
+    into one flat buffer): returns, per input, a view ``[world, *t.shape]``."""
     import torch.distributed as dist
 
-    out = torch.empty((shard.world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(out, t.contiguous(), group=shard.group)
-    return out.view(shard.world, *t.shape)
+    flat = torch.cat([t.reshape(-1) for t in tensors])
+    out = torch.empty((shard.world * flat.numel(),), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(out, flat, group=shard.group)
+    out = out.view(shard.world, flat.numel())
+    views, off = [], 0
+    for t in tensors:
+        views.append(out[:, off : off + t.numel()].reshape(shard.world, *t.shape))
+        off += t.numel()
+    return views
 
 
-def _merge_ranks(ops, o_loc, lse_loc, shard: Shard, out_dtype):
-    """Second-level merge across GPUs: every rank contributes its normalised fp32 output and its lse;
-    a rank with no visible key has lse = -inf and weight 0."""
-    if shard.world == 1:
-        return o_loc.to(out_dtype), lse_loc
-    o_all = _gather(o_loc, shard)                                # [W, B, Hq, D]
-    lse_all = _gather(lse_loc, shard)                            # [W, B, Hq]
-    o_part = o_all.permute(1, 2, 0, 3).contiguous()
-    m = lse_all.permute(1, 2, 0)
+def _merge_gathered(ops, o_all, lse_all, out_dtype):
+    """Second-level merge across GPUs: every rank contributed its normalised fp32 output ``[W, ..., D]`` and its lse
+    ``[W, ...]``; a rank with no visible key has lse = -inf and weight 0."""
+    nd = o_all.dim()
+    o_part = o_all.permute(*range(1, nd - 1), 0, nd - 1).contiguous()         # [..., W, D]
+    m = lse_all.permute(*range(1, nd - 1), 0)
     ml = torch.stack([m, torch.isfinite(m).to(torch.float32)], dim=-1).contiguous()
     return ops.lse_merge(o_part, ml, out_dtype)
 
@@ -172,61 +176,6 @@ def nsa_decode_attention(
     # ---- compressed branch: compressed token c is visible when its window ends at or before t (c*stride + ks - 1 <= t)
     num_cmp, lo_c, hi_c = ops.cmp_ranges(seq_len, cmp_row0, Hk, kernel_size, kernel_stride, shard.cmp_lo, shard.cmp_hi)
     max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
-    cper = max(-(-max_cmp // world), 1)
-    cper = -(-cper // 4) * 4
-    return Shard(rank * per, (rank + 1) * per, rank * cper, (rank + 1) * cper, rank, world, group)
-
-
-def _gather(t: torch.Tensor, shard: Shard) -> torch.Tensor:
-    """All-gather ``t`` from every rank of the shard's group: [world, *t.shape]."""
-    import torch.distributed as dist
-
-    out = torch.empty((shard.world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(out, t.contiguous(), group=shard.group)
-    return out.view(shard.world, *t.shape)
-
-
-def _merge_ranks(ops, o_loc, lse_loc, shard: Shard, out_dtype):
-    """Second-level merge across GPUs: every rank contributes its normalised fp32 output and its lse;
-    a rank with no visible key has lse = -inf and weight 0."""
-    if shard.world == 1:
-        return o_loc.to(out_dtype), lse_loc
-    o_all = _gather(o_loc, shard)                                # [W, B, Hq, D]
-    lse_all = _gather(lse_loc, shard)                            # [W, B, Hq]
-    o_part = o_all.permute(1, 2, 0, 3).contiguous()
-    m = lse_all.permute(1, 2, 0)
-    ml = torch.stack([m, torch.isfinite(m).to(torch.float32)], dim=-1).contiguous()
-    return ops.lse_merge(o_part, ml, out_dtype)
-
-
-def nsa_decode_attention(
-    q: torch.Tensor,                 # [B, Hq, D] (already rotated)
-    k: torch.Tensor, v: torch.Tensor,            # cache rows [rows, Hk, D] of this GPU (k rotated)
-    cmp_k: torch.Tensor, cmp_v: torch.Tensor,    # compressed cache rows of this GPU
-    seq_len: torch.Tensor,           # [B] int32: tokens per sequence INCLUDING the decoded one
-    seq_row0: torch.Tensor,          # [B] int32: cache row of token shard.tok_lo of each sequence
-    cmp_row0: torch.Tensor,          # [B] int32: compressed-cache row of compressed token shard.cmp_lo
-    *, kernel_size: int, kernel_stride: int, block_size: int, topk: int, init_blocks: int, local_blocks: int,
-    window_size: int, max_len: int, sm_scale: Optional[float] = None, shard: Optional[Shard] = None, ops=None,
-    cmp_chunk: int = 512,
-) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """The three NSA branches for ONE new token per sequence; the token is the last of its sequence and gets
-    what the prefill path gives that row.  Returns (o_cmp, o_sel, o_win [B,Hq,D], lse_cmp, lse_sel, lse_win
-    [B,Hq] log2 units, topk_idx [B,Hk,T]).  ``max_len`` (host int) bounds every sequence length."""
-    ops = ops or CudaDecodeOps()
-    shard = shard or Shard()
-    B, Hq, D = q.shape
-    Hk = k.shape[1]
-    if sm_scale is None:
-        sm_scale = D ** -0.5
-    # ---- compressed branch: compressed token c is visible when its window ends at or before t (c*stride + ks - 1 <= t)
-    num_cmp = torch.clamp((seq_len - kernel_size) // kernel_stride + 1, min=0).to(torch.int32) * (seq_len >= kernel_size)
-    num_cmp = num_cmp.to(torch.int32)
-    c_hi = torch.clamp(num_cmp, max=shard.cmp_hi) - shard.cmp_lo
-    has = c_hi > 0
-    lo_c = torch.where(has, cmp_row0, torch.full_like(cmp_row0, -1)).view(B, 1, 1).expand(B, Hk, 1).contiguous()
-    hi_c = torch.where(has, cmp_row0 + c_hi, torch.full_like(cmp_row0, -1)).view(B, 1, 1).expand(B, Hk, 1).contiguous()
-    max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
     cmp_local = max(min(max_cmp, shard.cmp_hi) - shard.cmp_lo, 1)
     nchunk = -(-cmp_local // cmp_chunk)
     o_part, ml, scores = ops.attn_partial(q, cmp_k, cmp_v, lo_c, hi_c, cmp_chunk, nchunk, sm_scale, want_scores=True)
@@ -236,9 +185,9 @@ def nsa_decode_attention(
         shard_len, shard_stride = ld, 0
     else:
         o_loc, lse_loc = ops.lse_merge(o_part, ml, torch.float32)
-        o_cmp, lse_cmp = _merge_ranks(ops, o_loc, lse_loc, shard, q.dtype)
-        scores = _gather(scores, shard)                          # [W, B, Hk, ld], kept shard-major
-        shard_len, shard_stride = shard.cmp_hi - shard.cmp_lo, B * Hk * ld
+        o_all, lse_all, scores = _gather(shard, o_loc, lse_loc, scores)     # scores [W, B, Hk, ld] stay shard-major
+        o_cmp, lse_cmp = _merge_gathered(ops, o_all, lse_all, q.dtype)
+        shard_len, shard_stride = shard.cmp_hi - shard.cmp_lo, scores.stride(0)
     # ---- top-k blocks of the decoded token
     max_blocks = -(-max_len // block_size)
     topk_idx = ops.select_topk(scores, ld, shard_len, shard_stride, lse_cmp, seq_len, num_cmp, Hk, kernel_size, kernel_stride,
@@ -253,9 +202,7 @@ def nsa_decode_attention(
     o_sel, lse_sel = ops.lse_merge(o_part, ml, first, 0, topk // rpp)
     o_win, lse_win = ops.lse_merge(o_part, ml, first, topk // rpp, -(-npieces // rpp))
     if shard.world > 1:
-        both, lse_both = _merge_ranks(ops, torch.stack([o_sel, o_win], 2).flatten(1, 2), torch.stack([lse_sel, lse_win], 2).flatten(1, 2),
-                                      shard, q.dtype)
-        both = both.view(B, Hq, 2, D)
-        lse_both = lse_both.view(B, Hq, 2)
-        o_sel, o_win, lse_sel, lse_win = both[:, :, 0], both[:, :, 1], lse_both[:, :, 0], lse_both[:, :, 1]
+        o_all, lse_all = _gather(shard, torch.stack([o_sel, o_win]), torch.stack([lse_sel, lse_win]))   # [W, 2, B, Hq, (D)]
+        both, lse_both = _merge_gathered(ops, o_all, lse_all, q.dtype)
+        o_sel, o_win, lse_sel, lse_win = both[0], both[1], lse_both[0], lse_both[1]
     return o_cmp, o_sel, o_win, lse_cmp, lse_sel, lse_win, topk_idx
