@@ -29,6 +29,12 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
+# DRAM bytes (read + write) per launch of the main kernels from one ncu capture of the small case (one 16384-token
+# sequence; profiles/sel_attn_kernels_small_case_ncu.md); traffic grows with the token count, so cfg1 is 4 x that.
+NCU_TRAFFIC_SMALL = {"sel_bwd_main": 178.6e6 + 538.6e6, "sel_fwd_main": 76.4e6 + 494.9e6}
+# the compressed pass of the decode step at batch 8 (profiles/decode_kernels_small_case_ncu.md); grows with the batch
+NCU_TRAFFIC_DECODE_B8 = 268.5e6 + 6.7e6
+
 METRIC = "sel-attn fwd+bwd effective TFLOPS @64K (4x16384 tok, Hk=4, G=2, d=128, B_K=64, T=16)"
 UNIT = "TFLOP/s"
 CFG = dict(seqlens=[16384] * 4, Hk=4, G=2, d=128, bs=64, T=16)
@@ -331,7 +337,9 @@ def run_decode(args, rank, world, local_rank):
                        "l2": "the cache read per step exceeds L2", "algorithmic_bytes_per_step": bytes_step,
                        "step_gbs": bytes_step / world / (ms_step * 1e-3) / 1e9},
             "roofline": {"bound": "hbm", "kernel": "decode_partial_tma (compressed branch)", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": src, "ms": ms_cmp},
+                         "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_DECODE_B8 * B / 8 / world,
+                         "traffic_source": "ncu capture at batch 8 scaled by the batch", "peak_source": src, "ms": ms_cmp},
             "cpu_baseline": cpu,
             "e2e": ({"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": (qh.numel() + knh.numel() + vnh.numel()) * 2, "d2h_bytes_per_step": B * Hq * d * 2}
@@ -606,11 +614,13 @@ def main():
                        "useful_flops_per_step": flops_step, "tokens_per_s": world * N / (ms_step * 1e-3)},
             "kernels": kern,
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                         "frac": (achieved / peak_tf if achieved else None), "traffic": None, "peak_source": peak_src},
+                         "frac": (achieved / peak_tf if achieved else None),
+                         "traffic": NCU_TRAFFIC_SMALL[dom] * (4 if args.case == "cfg1" else 1),
+                         "traffic_source": "ncu capture of the small case scaled by the token count", "peak_source": peak_src},
             "cpu_baseline": cpu,
             "e2e": {"value": world * flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12},
-            "gpu_launches": 9 * args.steps,
+            "gpu_launches": 10 * args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
