@@ -341,6 +341,13 @@ static int sel_bwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const vo
     char* sp = (char*)scratch;
     a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 1024);
     a.dq_part = (void*)sp;  sp += bwd_dq_part_bytes(s);
+    CUtensorMap dqmap;
+    a.dqmap = nullptr;
+    if (D == 128 && BK <= 64) {
+        rc = make_tile_map(&dqmap, a.dq_part, dtype, sel_max_tiles(s) * kTileRows, D, D, 32);
+        if (rc) return rc;
+        a.dqmap = &dqmap;
+    }
     a.dk_acc = (float*)sp;
     a.dv_acc = a.dk_acc + Nk * Hk * (int64_t)D;
     a.bd = bd;

@@ -468,8 +468,8 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.s = s; p.ix = ix; p.nsub = nsub; p.bd = a.bd;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
-    if (D == 128 && s.BK <= kKT && !a.force_simple) {
-        e = launch_sel_bwd_pipe(ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16, a, s, ix, kmap, vmap, num_sms, stream);
+    if (D == 128 && s.BK <= kKT && !a.force_simple && a.dqmap) {
+        e = launch_sel_bwd_pipe(ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16, a, s, ix, kmap, vmap, *a.dqmap, num_sms, stream);
         if (e != cudaSuccess) return e;
     } else {
         auto kern = sel_bwd_main<D, ET>;

@@ -3,16 +3,18 @@
 // sel_bwd.cu.  Same math and same outputs: per tile of <= 128 (head, token) rows of one KV block
 //     S = Q K^T, dP = dO V^T | P = exp2(S c - lse), dS = scale P (dP - delta) | dQ = dS K,
 //     dK^T += Q^T dS, dV^T += dO^T P
-// Warp roles (512 threads, one CTA per SM, persistent over a round-robin run schedule):
-//   warps 0,1    gather Q and dO rows with 16-byte async copies (two stages), load K/V blocks by
-//                TMA (two stages);
-//   warp 2       issues S and dP (tcgen05, fp32 in TMEM, two buffers);
-//   warp 3       issues dQ, dK^T, dV^T;
-//   warps 4..7   move the finished dK^T / dV^T accumulators of a block from TMEM to registers
+// Warp roles (768 threads in six warpgroups whose register budgets are rebalanced with setmaxnreg; one CTA per SM,
+// persistent over a round-robin run schedule):
+//   warps 0..7   gather Q and dO rows with 16-byte async copies (two stages), load the K/V block by
+//                TMA (one stage: a block serves ~16 tiles, and the shared memory goes to the dQ staging);
+//   warp 8       issues S and dP (tcgen05, fp32 in TMEM, two buffers);
+//   warp 9       issues dQ, dK^T, dV^T (warps 10, 11 idle);
+//   warps 12..15 move the finished dK^T / dV^T accumulators of a block from TMEM to registers
 //                (freeing them for the next block at once) and add them to the fp32 global
 //                accumulators (red.add) while the next block computes;
-//   warps 8..15  two groups, one row per thread, alternate tiles: P / dS to swizzled smem, then the
-//                dQ partial of the tile from TMEM to global memory (input dtype, tile order).
+//   warps 16..23 two groups, one row per thread, alternate tiles: P / dS to swizzled smem, then the
+//                dQ partial of the tile from TMEM through a swizzled staging area to global memory by TMA
+//                store (input dtype, tile order): the load/store unit is left to the row gathers.
 #include "sel_launch.cuh"
 
 namespace fsa {
@@ -28,24 +30,53 @@ struct SelBwdPipeParams {
     float scale, scale_log2;
     int run;
     SelBounds bd;      // visible K/V rows per token
-    ET* dq_part;       // [max_tiles * 128, D]
+    ET* dq_part;       // [max_tiles * 128, D] (written through dqmap)
     float* dk_acc;     // [N, Hk, D] fp32, zero-initialised
     float* dv_acc;
 };
 
+// 1: dQ partials leave through a staging area and TMA stores, K/V single-buffered; 0: dQ partials by plain stores,
+// K/V double-buffered (the staging area and the second K/V stage compete for the same 32 KB).
+#ifndef FSA_BWD_DQ_TMA
+#define FSA_BWD_DQ_TMA 1
+#endif
+
 namespace bwdpipe {
 constexpr int D = 128, KT = 64;
-constexpr int kThreads = 512, kLoaders = 64;
+constexpr bool kDqTma = FSA_BWD_DQ_TMA != 0;
+constexpr int kKVStages = kDqTma ? 1 : 2;
+constexpr int kThreads = 768, kLoaders = 256;
+constexpr int kWLoad = kLoaders / 32, kWMma1 = kWLoad, kWMma2 = kWLoad + 1, kWFlush = kWLoad + 4, kWGroups = kWLoad + 8;
+// registers per thread of each role (multiples of 8); 32 * sum over warps <= 768 * 80 = the CTA's allocation
+constexpr int kRegLoad = 40, kRegMma = 48, kRegFlush = 96, kRegGroup = 128;
+static_assert(8 * kRegLoad + 4 * kRegMma + 4 * kRegFlush + 8 * kRegGroup <= 24 * 80, "register budget");
 constexpr int kKV = 2 * KT * D * 2;              // K then V: 32 KB
 constexpr int kQD = 2 * kTileRows * D * 2;       // Q then dO: 64 KB
 constexpr int kPS = 2 * kTileRows * KT * 2;      // P then dS: 32 KB
+constexpr int kDQ = kTileRows * D * 2;           // dQ staging: 32 KB, 8 KB per TMEM lane quarter
 constexpr int kTail = 2560;
-constexpr int kBytes = 2 * kKV + 2 * kQD + kPS + kTail;
+constexpr int kBytes = kKVStages * kKV + 2 * kQD + kPS + (kDqTma ? kDQ : 0) + kTail;
 constexpr int cS = 0, cDP = 64;                  // + 128 * buffer
 constexpr int cDQ = 256, cDK = 384, cDV = 448;
 constexpr uint32_t kCols = 512;
 static_assert(kBytes <= 227 * 1024, "smem budget");
 }  // namespace bwdpipe
+
+// Optional cycle accounting per role (debug builds only, -DFSA_TIMING): a table [gridDim.x][64] of accumulated
+// clock64() deltas, read back with fsa_debug_read_bwd_timing.
+#ifdef FSA_TIMING
+__device__ unsigned long long g_bwd_timing[512 * 64];
+#define BT_DECL unsigned long long _t0 = clock64(), _acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define BT_TOC(i) do { unsigned long long _t1 = clock64(); _acc[i] += _t1 - _t0; _t0 = _t1; } while (0)
+#define BT_DUMP(base, n) do { for (int _i = 0; _i < (n); ++_i) g_bwd_timing[blockIdx.x * 64 + (base) + _i] = _acc[_i]; } while (0)
+#else
+#define BT_DECL
+#define BT_TOC(i)
+#define BT_DUMP(base, n)
+#endif
+
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __device__ __forceinline__ float ex2_approx_b(float x) {
     float y;
@@ -56,14 +87,16 @@ __device__ __forceinline__ float ex2_approx_b(float x) {
 template <typename ET>
 __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBwdPipeParams<ET> p,
                                                                      const __grid_constant__ CUtensorMap kmap,
-                                                                     const __grid_constant__ CUtensorMap vmap) {
+                                                                     const __grid_constant__ CUtensorMap vmap,
+                                                                     const __grid_constant__ CUtensorMap dqmap) {
     using namespace bwdpipe;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sKV = smem;
-    uint8_t* sQD = sKV + 2 * kKV;
+    uint8_t* sQD = sKV + kKVStages * kKV;
     uint8_t* sP = sQD + 2 * kQD;
     uint8_t* sDS = sP + kTileRows * KT * 2;
-    uint8_t* tail = sP + kPS;
+    uint8_t* sDQ = sP + kPS;
+    uint8_t* tail = sDQ + (kDqTma ? kDQ : 0);
     int (*s_offq)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail);               // [2][128] q row offset / 8, -1 padding
     int (*s_offd)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail + 1024);        // [2][128] dO row offset / 8
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
@@ -82,6 +115,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     uint64_t* acc_empty = bars + 19;
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 20);
     int* s_nb = reinterpret_cast<int*>(bars + 21);   // [2]
+    uint64_t* stg_free = bars + 22;      // [4] dQ staging rows of a lane quarter have been read by the TMA store
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const SelShape& s = p.s;
@@ -99,9 +133,11 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
         mbar_init(dq_full, 1); mbar_init(dq_empty, 128);
         mbar_init(acc_full, 1); mbar_init(acc_empty, 128);
+        for (int i = 0; i < 4; ++i) mbar_init(&stg_free[i], 1);
         mbar_init_fence();
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
+        tma_prefetch_desc(&dqmap);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, kCols);
     tc_fence_before();
@@ -112,39 +148,41 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     const int nloc = sched.nloc;
     const int key_lim = min(KT, s.BK);
 
-    if (warp < 2) {
+    if (warp < kWLoad) {
         // ------------------------------------------------------------------ loaders
+        reg_dec<kRegLoad>();
         const int t = tid;
         bool ok = true;
         int kvn = -1;
-        // rows t and t + 64 of every tile
-        const int g0 = t / s.TPT, e0 = t - g0 * s.TPT;
-        const int g1 = (t + 64) / s.TPT, e1 = (t + 64) - g1 * s.TPT;
-        const bool ex0 = g0 < s.G, ex1 = g1 < s.G;
+        // thread t < 128 prepares the offsets of row t of every tile
+        const int g0 = (t & 127) / s.TPT, e0 = (t & 127) - g0 * s.TPT;
+        const bool ex0 = g0 < s.G && t < kTileRows;
         TileInfo m1{0, 0, 0, -1}, m2{0, 0, 0, -1};
-        uint32_t ent1a = 0xFFFFFFFFu, ent1b = 0xFFFFFFFFu, ent2a = 0xFFFFFFFFu, ent2b = 0xFFFFFFFFu;
-        auto fetch = [&](int k, TileInfo& ti, uint32_t& ea, uint32_t& eb) {
+        uint32_t ent1a = 0xFFFFFFFFu, ent2a = 0xFFFFFFFFu;
+        auto fetch = [&](int k, TileInfo& ti, uint32_t& ea) {
             const int j = sched.tile(k);
             ti = load_tile(p.ix, j);
-            ea = 0xFFFFFFFFu; eb = 0xFFFFFFFFu;
+            ea = 0xFFFFFFFFu;
             if (ex0) ea = __ldg(p.ix.entries + (int64_t)j * s.TPT + e0);
-            if (ex1) eb = __ldg(p.ix.entries + (int64_t)j * s.TPT + e1);
         };
-        if (nloc > 0) fetch(0, m1, ent1a, ent1b);
-        if (nloc > 1) fetch(1, m2, ent2a, ent2b);
+        if (nloc > 0) fetch(0, m1, ent1a);
+        if (nloc > 1) fetch(1, m2, ent2a);
         int prev_hg = -1;
         constexpr int CPR = D / 8, RSTEP = kLoaders / CPR;   // 16 chunks per row, 4 rows per step
         const int cchunk = t % CPR, rbase = t / CPR;
         const uint32_t slab_off = (uint32_t)(cchunk >> 3) * (kTileRows * 128);
+        BT_DECL;
         for (int k = 0; k < nloc && ok; ++k) {
             const int st = k & 1;
             const TileInfo cur = m1;
-            const uint32_t c_ea = ent1a, c_eb = ent1b;
+            const uint32_t c_ea = ent1a;
             const bool c_nb = cur.hg != prev_hg;
             prev_hg = cur.hg;
-            m1 = m2; ent1a = ent2a; ent1b = ent2b;
-            if (k + 2 < nloc) fetch(k + 2, m2, ent2a, ent2b);
+            m1 = m2; ent1a = ent2a;
+            if (k + 2 < nloc) fetch(k + 2, m2, ent2a);
+            BT_TOC(0);
             ok = mbar_wait(&qd_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
+            BT_TOC(1);
             if (t == 0) {
                 s_nb[st] = c_nb ? 1 : 0;
                 mbar_arrive(&meta_full[st]);
@@ -152,8 +190,8 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             if (c_nb) {
                 ++kvn;
                 if (t == 0) {
-                    const int ks = kvn & 1;
-                    ok = mbar_wait(&kv_empty[ks], ((kvn >> 1) & 1) ^ 1, status) && ok;
+                    const int ks = kvn % kKVStages;
+                    ok = mbar_wait(&kv_empty[ks], ((kvn / kKVStages) & 1) ^ 1, status) && ok;
                     mbar_expect_tx(&kv_full[ks], (uint32_t)kKV);
                     uint8_t* dK = sKV + ks * kKV;
                     uint8_t* dV = dK + KT * D * 2;
@@ -164,22 +202,22 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                     }
                 }
             }
-            {
-                const bool va = c_ea != 0xFFFFFFFFu, vb = c_eb != 0xFFFFFFFFu;
-                const long long ta = c_ea >> kSlotBits, tb = c_eb >> kSlotBits;
-                const int ha = cur.h * s.G + g0, hb = cur.h * s.G + g1;
+            if (t < kTileRows) {
+                const bool va = c_ea != 0xFFFFFFFFu;
+                const long long ta = c_ea >> kSlotBits;
+                const int ha = cur.h * s.G + g0;
                 s_offq[st][t] = va ? (int)((ta * p.q_sn + (long long)ha * p.q_sh) >> 3) : -1;
                 s_offd[st][t] = va ? (int)((ta * p.do_sn + (long long)ha * p.do_sh) >> 3) : -1;
-                s_offq[st][t + 64] = vb ? (int)((tb * p.q_sn + (long long)hb * p.q_sh) >> 3) : -1;
-                s_offd[st][t + 64] = vb ? (int)((tb * p.do_sn + (long long)hb * p.do_sh) >> 3) : -1;
             }
+            BT_TOC(2);
             named_bar_sync(1, kLoaders);
+            BT_TOC(3);
             {
                 const uint32_t dq_ = smem_u32(sQD + st * kQD) + slab_off;
                 const uint32_t dd_ = dq_ + kTileRows * D * 2;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    constexpr int NIT = kTileRows / RSTEP / 2;     // 16 rows per half
+                for (int half = 0; half < 1; ++half) {
+                    constexpr int NIT = kTileRows / RSTEP;         // 8 rows per thread
                     int oq[NIT], od[NIT];
 #pragma unroll
                     for (int it = 0; it < NIT; ++it) {
@@ -197,22 +235,28 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 }
             }
             cp_async_mbar_arrive_noinc(&qd_full[st]);
+            BT_TOC(4);
         }
-    } else if (warp >= 4 && warp < 8) {
+        if (t == 0) BT_DUMP(0, 5);
+    } else if (warp >= kWFlush && warp < kWFlush + 4) {
         // ------------------------------------------------------------------ accumulator flush
         // Walks the CTA's tiles to find the block boundaries; for every finished block: wait for its
         // last products, pull dK^T / dV^T (lane = head-dim index, columns = keys) into registers,
         // release the TMEM accumulators, then add to the fp32 global accumulators.
+        reg_inc<kRegFlush>();
         const int d_idx = (warp & 3) * 32 + lane;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         bool ok = true;
         int nflush = 0;
         int k = 0;
+        BT_DECL;
         while (k < nloc && ok) {
             const TileInfo ti = load_tile(p.ix, sched.tile(k));
             int k2 = k + 1;
             while (k2 < nloc && load_tile(p.ix, sched.tile(k2)).hg == ti.hg) ++k2;   // tiles [k, k2) form the block
+            BT_TOC(0);
             ok = mbar_wait(acc_full, nflush & 1, status) && ok;
+            BT_TOC(1);
             tc_fence_after();
             const int nkeys = (int)min((int64_t)key_lim, s.Nk - ti.row0);
 #pragma unroll
@@ -234,8 +278,12 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                     if (key < nkeys) atomicAdd(dst + (int64_t)key * s.Hk * D, __uint_as_float(v[key]));
             }
             k = k2;
+            BT_TOC(2);
         }
-    } else if (warp == 2) {
+        if (warp == kWFlush && lane == 0) BT_DUMP(8, 3);
+    } else if (warp < kWFlush) {
+      reg_dec<kRegMma>();
+      if (warp == kWMma1) {
         // ------------------------------------------------------------------ MMA issuer 1: S and dP
         const bool leader = elect_one();
         constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, KT, false, false);
@@ -244,20 +292,26 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         const uint32_t kv_lo = umma_desc_lo(smem_u32(sKV), 16);
         int kvn = -1;
         bool ok = true;
+        BT_DECL;
         for (int k = 0; k < nloc && ok; ++k) {
             const int st = k & 1;
+            BT_TOC(0);
             ok = mbar_wait(&meta_full[st], (k >> 1) & 1, status) && ok;
+            BT_TOC(1);
             if (s_nb[st] != 0) {
                 ++kvn;
-                ok = mbar_wait(&kv_full[kvn & 1], (kvn >> 1) & 1, status) && ok;
+                ok = mbar_wait(&kv_full[kvn % kKVStages], (kvn / kKVStages) & 1, status) && ok;
             }
+            BT_TOC(2);
             ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;
+            BT_TOC(3);
             fence_async_smem();
             ok = mbar_wait(&sdp_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
+            BT_TOC(4);
             tc_fence_after();
             const uint32_t aq = qd_lo + (uint32_t)(st * (kQD >> 4));
             const uint32_t ad = aq + (uint32_t)((kTileRows * D * 2) >> 4);
-            const uint32_t bk = kv_lo + (uint32_t)((kvn & 1) * (kKV >> 4));
+            const uint32_t bk = kv_lo + (uint32_t)((kvn % kKVStages) * (kKV >> 4));
             const uint32_t bv = bk + (uint32_t)((KT * D * 2) >> 4);
             const uint32_t dS_ = tbase + cS + st * 128, dP_ = tbase + cDP + st * 128;
             if (leader) {
@@ -273,8 +327,10 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 umma_commit(&sdp_full[st]);
             }
             __syncwarp();
+            BT_TOC(5);
         }
-    } else if (warp == 3) {
+        if (lane == 0) BT_DUMP(16, 6);
+      } else if (warp == kWMma2) {
         // ------------------------------------------------------------------ MMA issuer 2: dQ, dK^T, dV^T
         const bool leader = elect_one();
         constexpr uint32_t idesc_dq = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);     // dS (K-major) x K (MN-major)
@@ -290,6 +346,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         int hg0 = -1, hg1 = -1, hg2 = -1;
         if (nloc > 0) hg1 = load_tile(p.ix, sched.tile(0)).hg;
         if (nloc > 1) hg2 = load_tile(p.ix, sched.tile(1)).hg;
+        BT_DECL;
         for (int k = 0; k < nloc && ok; ++k) {
             const int st = k & 1;
             const int prev_hg = hg0;
@@ -298,14 +355,19 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             const bool first_of_block = hg0 != prev_hg;
             const bool last_of_block = (k + 1 >= nloc) || (hg1 != hg0);
             if (first_of_block) { ++kvn; ++blk; }
+            BT_TOC(0);
             ok = mbar_wait(pds_full, k & 1, status) && ok;
+            BT_TOC(1);
             ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
+            BT_TOC(2);
             ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;     // already complete: acquire only
-            ok = mbar_wait(&kv_full[kvn & 1], (kvn >> 1) & 1, status) && ok;
+            ok = mbar_wait(&kv_full[kvn % kKVStages], (kvn / kKVStages) & 1, status) && ok;
+            BT_TOC(3);
             if (first_of_block && blk > 0) ok = mbar_wait(acc_empty, (blk - 1) & 1, status) && ok;
+            BT_TOC(4);
             fence_async_smem();
             tc_fence_after();
-            const uint32_t bk = k_mn_lo + (uint32_t)((kvn & 1) * (kKV >> 4));
+            const uint32_t bk = k_mn_lo + (uint32_t)((kvn % kKVStages) * (kKV >> 4));
             const uint32_t aq = qd_mn_lo + (uint32_t)(st * (kQD >> 4));
             const uint32_t ad = aq + (uint32_t)((kTileRows * D * 2) >> 4);
             if (leader) {
@@ -325,15 +387,19 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 umma_commit(&qd_empty[st]);
                 umma_commit(dq_full);
                 if (last_of_block) {
-                    umma_commit(&kv_empty[kvn & 1]);
+                    umma_commit(&kv_empty[kvn % kKVStages]);
                     umma_commit(acc_full);
                 }
             }
             __syncwarp();
+            BT_TOC(5);
         }
+        if (lane == 0) BT_DUMP(24, 6);
+      }
     } else {
         // ------------------------------------------------------------------ P / dS and dQ epilogue
-        const int sb = (warp - 8) >> 2;
+        reg_inc<kRegGroup>();
+        const int sb = (warp - kWGroups) >> 2;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
@@ -369,6 +435,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
         }
         if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B, hB);
+        BT_DECL;
         for (int k = sb; k < nloc && ok; k += 2) {
             const int j = sched.tile(k);
             const uint32_t ent = entA;
@@ -378,8 +445,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             entA = entB; row0A = row0B; hA = hB;
             if (k + 2 < nloc) fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
             if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B, hB);
-            const bool row_valid = ent != 0xFFFFFFFFu;
+            BT_TOC(0);
             ok = mbar_wait(&sdp_full[sb], (k >> 1) & 1, status) && ok;
+            BT_TOC(1);
             tc_fence_after();
             uint32_t pp[KT / 2], dd[KT / 2];
 #pragma unroll
@@ -400,7 +468,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             }
             tc_fence_before();
             mbar_arrive(&sdp_empty[sb]);
+            BT_TOC(2);
             ok = mbar_wait(pds_empty, (k & 1) ^ 1, status) && ok;
+            BT_TOC(3);
 #pragma unroll
             for (int ch = 0; ch < KT / 8; ++ch) {
                 const uint32_t off = sw128_chunk_off(r, ch);
@@ -409,30 +479,70 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             }
             fence_async_smem();
             mbar_arrive(pds_full);
+            BT_TOC(4);
             // ---- dQ partial of this tile
             ok = mbar_wait(dq_full, k & 1, status) && ok;
+            BT_TOC(5);
             tc_fence_after();
-            uint4* dst = reinterpret_cast<uint4*>(p.dq_part + ((int64_t)j * kTileRows + r) * D);
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tbase + lane_off + cDQ + c0, v);
-                tmem_ld_wait();
-                if (row_valid) {
-#pragma unroll
+            if constexpr (kDqTma) {
+                // staging rows of this lane quarter: free once the store of the previous tile (other group) has read them
+                ok = mbar_wait(&stg_free[quarter], (k - 1) & 1, status) && ok;
+                uint8_t* my_stage = sDQ + quarter * (32 * 256);
+    #pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tbase + lane_off + cDQ + c0, v);
+                    tmem_ld_wait();
+    #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint4 u;
                         u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
                         u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
                         u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
                         u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
-                        dst[(c0 >> 3) + q4] = u;
+                        const int chunk = (c0 >> 3) + q4;
+                        *reinterpret_cast<uint4*>(my_stage + (chunk >> 3) * (32 * 128) + sw128_chunk_off(lane, chunk & 7)) = u;
                     }
                 }
+                tc_fence_before();
+                mbar_arrive(dq_empty);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+    #pragma unroll
+                    for (int b = 0; b < D / 64; ++b)
+                        tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
+                    bulk_commit();
+                    bulk_wait_read0();
+                    mbar_arrive(&stg_free[quarter]);
+                }
+                __syncwarp();
+            } else {
+                const bool row_valid = ent != 0xFFFFFFFFu;
+                uint4* dst = reinterpret_cast<uint4*>(p.dq_part + ((int64_t)j * kTileRows + r) * D);
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tbase + lane_off + cDQ + c0, v);
+                    tmem_ld_wait();
+                    if (row_valid) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 u;
+                            u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                            u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                            u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                            u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                            dst[(c0 >> 3) + q4] = u;
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(dq_empty);
             }
-            tc_fence_before();
-            mbar_arrive(dq_empty);
+            BT_TOC(6);
         }
+        if (quarter == 0 && lane == 0) BT_DUMP(32 + sb * 8, 7);
     }
     tc_fence_before();
     __syncthreads();
@@ -441,7 +551,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
 
 template <typename ET>
 static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const SelIndex& ix, const CUtensorMap& kmap,
-                               const CUtensorMap& vmap, int num_sms, cudaStream_t stream) {
+                               const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms, cudaStream_t stream) {
     SelBwdPipeParams<ET> p;
     p.q = (const ET*)a.q; p.q_sn = a.q_sn; p.q_sh = a.q_sh;
     p.d_o = (const ET*)a.d_o; p.do_sn = a.do_sn; p.do_sh = a.do_sh;
@@ -455,15 +565,24 @@ static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const Sel
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwdpipe::kBytes);
     if (e != cudaSuccess) return e;
     prof_begin(2, stream);
-    kern<<<num_sms, bwdpipe::kThreads, bwdpipe::kBytes, stream>>>(p, kmap, vmap);
+    kern<<<num_sms, bwdpipe::kThreads, bwdpipe::kBytes, stream>>>(p, kmap, vmap, dqmap);
     prof_end(2, stream);
     return cudaGetLastError();
 }
 
+#ifdef FSA_TIMING
+}  // namespace fsa
+extern "C" int fsa_debug_read_bwd_timing(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, fsa::g_bwd_timing, (size_t)n * sizeof(unsigned long long));
+}
+namespace fsa {
+#endif
+
 cudaError_t launch_sel_bwd_pipe(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
-                                const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream) {
-    return dtype == kBF16 ? launch_pipe<__nv_bfloat16>(a, s, ix, kmap, vmap, num_sms, stream)
-                          : launch_pipe<__half>(a, s, ix, kmap, vmap, num_sms, stream);
+                                const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms,
+                                cudaStream_t stream) {
+    return dtype == kBF16 ? launch_pipe<__nv_bfloat16>(a, s, ix, kmap, vmap, dqmap, num_sms, stream)
+                          : launch_pipe<__half>(a, s, ix, kmap, vmap, dqmap, num_sms, stream);
 }
 
 }  // namespace fsa

@@ -49,6 +49,7 @@ struct SelBwdArgs {
     // scratch
     float* delta;      // [Hq, N]
     void* dq_part;     // [max_tiles * nsub * 128, D] input dtype
+    const CUtensorMap* dqmap;   // over dq_part, box {64, 32}: partial stores of the pipelined kernel (null: not built)
     float* dk_acc;     // [N, Hk, D]; dv_acc follows immediately
     float* dv_acc;
     // outputs (contiguous)
@@ -58,7 +59,8 @@ struct SelBwdArgs {
 
 // pipelined main kernel for head_dim 128, block size <= 64 (sel_bwd_pipe.cu)
 cudaError_t launch_sel_bwd_pipe(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
-                                const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream);
+                                const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms,
+                                cudaStream_t stream);
 
 cudaError_t dispatch_sel_bwd(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
                              const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream);
