@@ -392,27 +392,19 @@ __global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const ET* __restrict__ 
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    for (int sl = 0; sl < s.T; ++sl) {
-        const long long pr = __shfl_sync(0xffffffffu, sl < 32 ? pr0 : pr1, sl & 31);
-        if (pr < 0) continue;
-        for (int u = 0; u < nsub; ++u) {
-            const ET* src = dq_part + (pr + (long long)u * kTileRows) * D + lane * V;
-            if constexpr (V == 2) {
-                float2 x = ElemTraits<ET>::unpack2(*reinterpret_cast<const uint32_t*>(src));
-                acc[0] += x.x; acc[1] += x.y;
-            } else if constexpr (V == 4) {
-                uint2 w = *reinterpret_cast<const uint2*>(src);
-                float2 x = ElemTraits<ET>::unpack2(w.x), y = ElemTraits<ET>::unpack2(w.y);
-                acc[0] += x.x; acc[1] += x.y; acc[2] += y.x; acc[3] += y.y;
-            } else {
-                uint4 w = *reinterpret_cast<const uint4*>(src);
-                const uint32_t* ww = &w.x;
+    // eight partial rows in flight per warp: all loads of a batch are issued before the first is used
+    for (int u_ = 0; u_ < nsub; ++u_) {
+        for (int sl0 = 0; sl0 < s.T; sl0 += 8) {
+            uint4 x[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float2 x = ElemTraits<ET>::unpack2(ww[i]);
-                    acc[2 * i] += x.x; acc[2 * i + 1] += x.y;
-                }
+            for (int j = 0; j < 8; ++j) {
+                const int sl = sl0 + j;
+                const long long pr = __shfl_sync(0xffffffffu, sl < 32 ? pr0 : pr1, sl & 31);
+                x[j] = (sl < s.T && pr >= 0) ? ld_row_vec<V, ET>(dq_part + (pr + (long long)u_ * kTileRows) * D + lane * V)
+                                             : make_uint4(0u, 0u, 0u, 0u);
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) fma_row_vec<V, ET>(acc, x[j], 1.f);
         }
     }
     ET* dst = dq + row * D + lane * V;

@@ -199,4 +199,24 @@ struct TileWalker {
     }
 };
 
+// One lane's share of a partial row: V = D / 32 elements (4, 8 or 16 bytes), as raw words.
+template <int V, typename ET>
+__device__ __forceinline__ uint4 ld_row_vec(const ET* src) {
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (V == 2) u.x = *reinterpret_cast<const uint32_t*>(src);
+    else if constexpr (V == 4) { uint2 t = *reinterpret_cast<const uint2*>(src); u.x = t.x; u.y = t.y; }
+    else u = *reinterpret_cast<const uint4*>(src);
+    return u;
+}
+template <int V, typename ET>
+__device__ __forceinline__ void fma_row_vec(float (&acc)[V], const uint4& u, float w) {
+    const uint32_t* uu = &u.x;
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+        float2 x = ElemTraits<ET>::unpack2(uu[i]);
+        acc[2 * i] = fmaf(w, x.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(w, x.y, acc[2 * i + 1]);
+    }
+}
+
 }  // namespace fsa

@@ -701,7 +701,7 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> 
 }
 
 // ------------------------------------------------------------------------------------------
-template <int D, typename ET>
+template <int D, typename ET, int MODE>
 __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opart, const float2* __restrict__ ml,
                                                       const int* __restrict__ pos, SelShape s, ET* __restrict__ o,
                                                       int64_t o_sn, int64_t o_sh, float* __restrict__ lse) {
@@ -711,59 +711,87 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
     const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);
     const int h = hq / s.G, g = hq - h * s.G;
     const int* prow = pos + ((int64_t)h * s.N + n) * s.T;
-    // lane handles slots lane and lane + 32: partial row index and statistics
-    int64_t pr0 = -1, pr1 = -1;
-    float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
-    if (lane < s.T) {
-        int ps = __ldg(prow + lane);
-        if (ps >= 0) {
-            pr0 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
-            float2 v = ml[pr0];
-            m0 = v.x; l0 = v.y;
-        }
-    }
-    if (lane + 32 < s.T) {
-        int ps = __ldg(prow + lane + 32);
-        if (ps >= 0) {
-            pr1 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
-            float2 v = ml[pr1];
-            m1 = v.x; l1 = v.y;
-        }
-    }
-    float M = fmaxf(m0, m1);
-#pragma unroll
-    for (int o_ = 16; o_; o_ >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o_));
-    float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
-    float w1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - M);
-    float L = w0 * l0 + w1 * l1;
-#pragma unroll
-    for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
-
     constexpr int V = D / 32;   // elements per lane
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    for (int sl = 0; sl < s.T; ++sl) {
-        const float w = __shfl_sync(0xffffffffu, sl < 32 ? w0 : w1, sl & 31);
-        const long long pr = __shfl_sync(0xffffffffu, (long long)(sl < 32 ? pr0 : pr1), sl & 31);
-        if (w == 0.f) continue;
-        const ET* src = opart + pr * D + lane * V;
-        if constexpr (V == 2) {
-            float2 x = ElemTraits<ET>::unpack2(*reinterpret_cast<const uint32_t*>(src));
-            acc[0] = fmaf(w, x.x, acc[0]); acc[1] = fmaf(w, x.y, acc[1]);
-        } else if constexpr (V == 4) {
-            uint2 u = *reinterpret_cast<const uint2*>(src);
-            float2 x = ElemTraits<ET>::unpack2(u.x), y = ElemTraits<ET>::unpack2(u.y);
-            acc[0] = fmaf(w, x.x, acc[0]); acc[1] = fmaf(w, x.y, acc[1]);
-            acc[2] = fmaf(w, y.x, acc[2]); acc[3] = fmaf(w, y.y, acc[3]);
-        } else {
-            uint4 u = *reinterpret_cast<const uint4*>(src);
-            const uint32_t* uu = &u.x;
+    float L, M;
+    if (MODE == 2 && s.T <= 16) {
+        // Up to 16 slots: the row loads depend only on the positions, so they are issued together with the loads of
+        // the statistics (one round trip less, 16 rows in flight per warp); weights are applied afterwards.
+        int ps = lane < s.T ? __ldg(prow + lane) : -1;
+        long long pr = -1;
+        float m0 = -INFINITY, l0 = 0.f;
+        if (ps >= 0) pr = (long long)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
+        uint4 u[16];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float2 x = ElemTraits<ET>::unpack2(uu[i]);
-                acc[2 * i] = fmaf(w, x.x, acc[2 * i]); acc[2 * i + 1] = fmaf(w, x.y, acc[2 * i + 1]);
+        for (int j = 0; j < 16; ++j) {
+            const long long prj = __shfl_sync(0xffffffffu, pr, j);
+            u[j] = prj >= 0 ? ld_row_vec<V, ET>(opart + prj * D + lane * V) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (pr >= 0) {
+            float2 v = ml[pr];
+            m0 = v.x; l0 = v.y;
+        }
+        M = m0;
+#pragma unroll
+        for (int o_ = 16; o_; o_ >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o_));
+        const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
+        L = w0 * l0;
+#pragma unroll
+        for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) fma_row_vec<V, ET>(acc, u[j], __shfl_sync(0xffffffffu, w0, j));
+    } else {
+        // lane handles slots lane and lane + 32: partial row index and statistics
+        int64_t pr0 = -1, pr1 = -1;
+        float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
+        if (lane < s.T) {
+            int ps = __ldg(prow + lane);
+            if (ps >= 0) {
+                pr0 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
+                float2 v = ml[pr0];
+                m0 = v.x; l0 = v.y;
             }
+        }
+        if (lane + 32 < s.T) {
+            int ps = __ldg(prow + lane + 32);
+            if (ps >= 0) {
+                pr1 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
+                float2 v = ml[pr1];
+                m1 = v.x; l1 = v.y;
+            }
+        }
+        M = fmaxf(m0, m1);
+#pragma unroll
+        for (int o_ = 16; o_; o_ >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o_));
+        float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
+        float w1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - M);
+        L = w0 * l0 + w1 * l1;
+#pragma unroll
+        for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
+        if (MODE == 0) {
+            for (int sl = 0; sl < s.T; ++sl) {
+                const float w = __shfl_sync(0xffffffffu, sl < 32 ? w0 : w1, sl & 31);
+                const long long pr = __shfl_sync(0xffffffffu, (long long)(sl < 32 ? pr0 : pr1), sl & 31);
+                if (w == 0.f) continue;
+                fma_row_vec<V, ET>(acc, ld_row_vec<V, ET>(opart + pr * D + lane * V), w);
+            }
+        } else {
+        for (int sl0 = 0; sl0 < s.T; sl0 += 8) {
+            uint4 u[8];
+            float w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int sl = sl0 + j;
+                w[j] = __shfl_sync(0xffffffffu, sl < 32 ? w0 : w1, sl & 31);
+                const long long pr = __shfl_sync(0xffffffffu, (long long)(sl < 32 ? pr0 : pr1), sl & 31);
+                if (sl >= s.T) w[j] = 0.f;
+                u[j] = w[j] != 0.f ? ld_row_vec<V, ET>(opart + pr * D + lane * V) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) fma_row_vec<V, ET>(acc, u[j], w[j]);
+        }
         }
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -832,7 +860,13 @@ static cudaError_t launch_sel_fwd(const SelFwdArgs& a, const SelShape& s, const 
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(1, stream);
-        sel_fwd_reduce<D, ET><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
+        static const int mode = [] { const char* v = getenv("FSA_FWD_REDUCE_MODE"); return v && *v ? atoi(v) : 0; }();
+        if (mode == 2)
+            sel_fwd_reduce<D, ET, 2><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
+        else if (mode == 1)
+            sel_fwd_reduce<D, ET, 1><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
+        else
+            sel_fwd_reduce<D, ET, 0><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
         prof_end(1, stream);
     }
     return cudaGetLastError();
