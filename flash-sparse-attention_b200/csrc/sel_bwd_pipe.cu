@@ -5,10 +5,12 @@
 //     dK^T += Q^T dS, dV^T += dO^T P
 // Warp roles (768 threads in six warpgroups whose register budgets are rebalanced with setmaxnreg; one CTA per SM,
 // persistent over a round-robin run schedule):
-//   warps 0..7   gather Q and dO rows with 16-byte async copies (two stages), load the K/V block by
-//                TMA (one stage: a block serves ~16 tiles, and the shared memory goes to the dQ staging);
+//   warps 0..7   gather Q and dO rows with 16-byte async copies (two stages);
 //   warp 8       issues S and dP (tcgen05, fp32 in TMEM, two buffers);
-//   warp 9       issues dQ, dK^T, dV^T (warps 10, 11 idle);
+//   warp 9       issues dQ, dK^T, dV^T;
+//   warp 10      prepares, up to four tiles ahead, the token of every tile row (the gather warps then run without
+//                any global load of their own: a plain load issued behind a burst of async copies waits for it);
+//   warp 11      loads the K/V block of every run of tiles by TMA;
 //   warps 12..15 move the finished dK^T / dV^T accumulators of a block from TMEM to registers
 //                (freeing them for the next block at once) and add them to the fp32 global
 //                accumulators (red.add) while the next block computes;
@@ -97,14 +99,12 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     uint8_t* sDS = sP + kTileRows * KT * 2;
     uint8_t* sDQ = sP + kPS;
     uint8_t* tail = sDQ + (kDqTma ? kDQ : 0);
-    int (*s_offq)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail);               // [2][128] q row offset / 8, -1 padding
-    int (*s_offd)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail + 1024);        // [2][128] dO row offset / 8
+    int (*s_tok)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail);                // [4][128] token of every tile row, -1 padding
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
     uint64_t* qd_full = bars;            // [2]
     uint64_t* qd_empty = bars + 2;       // [2]
     uint64_t* kv_full = bars + 4;        // [2]
     uint64_t* kv_empty = bars + 6;       // [2]
-    uint64_t* meta_full = bars + 8;      // [2]
     uint64_t* sdp_full = bars + 10;      // [2]
     uint64_t* sdp_empty = bars + 12;     // [2]
     uint64_t* pds_full = bars + 14;
@@ -114,8 +114,11 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     uint64_t* acc_full = bars + 18;
     uint64_t* acc_empty = bars + 19;
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 20);
-    int* s_nb = reinterpret_cast<int*>(bars + 21);   // [2]
     uint64_t* stg_free = bars + 22;      // [4] dQ staging rows of a lane quarter have been read by the TMA store
+    uint64_t* off_full = bars + 26;      // [4] ring of prepared tiles: tokens, kv head and new-block flag are valid
+    uint64_t* off_empty = bars + 30;     // [4] ... have been read by the eight gather warps and the S/dP issuer
+    int* s_h = reinterpret_cast<int*>(bars + 34);    // [4] kv head of the prepared tile
+    int* s_nb = s_h + 4;                             // [4] 1: the tile starts a new K/V block
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const SelShape& s = p.s;
@@ -127,13 +130,13 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&qd_full[i], kLoaders); mbar_init(&qd_empty[i], 1);
-            mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&meta_full[i], 1);
+            mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
             mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 128);
         }
         mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
         mbar_init(dq_full, 1); mbar_init(dq_empty, 128);
         mbar_init(acc_full, 1); mbar_init(acc_empty, 128);
-        for (int i = 0; i < 4; ++i) mbar_init(&stg_free[i], 1);
+        for (int i = 0; i < 4; ++i) { mbar_init(&stg_free[i], 1); mbar_init(&off_full[i], 1); mbar_init(&off_empty[i], kWLoad + 1); }
         mbar_init_fence();
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
@@ -149,90 +152,50 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     const int key_lim = min(KT, s.BK);
 
     if (warp < kWLoad) {
-        // ------------------------------------------------------------------ loaders
+        // ------------------------------------------------------------------ gather warps
+        // Thread t copies 16-byte chunk t % 16 of the rows t / 16 + 16 i (a half-warp covers one 256-byte row) of Q and
+        // dO.  Tokens come from the prepared ring; the head part of every row offset is a thread constant.
         reg_dec<kRegLoad>();
         const int t = tid;
         bool ok = true;
-        int kvn = -1;
-        // thread t < 128 prepares the offsets of row t of every tile
-        const int g0 = (t & 127) / s.TPT, e0 = (t & 127) - g0 * s.TPT;
-        const bool ex0 = g0 < s.G && t < kTileRows;
-        TileInfo m1{0, 0, 0, -1}, m2{0, 0, 0, -1};
-        uint32_t ent1a = 0xFFFFFFFFu, ent2a = 0xFFFFFFFFu;
-        auto fetch = [&](int k, TileInfo& ti, uint32_t& ea) {
-            const int j = sched.tile(k);
-            ti = load_tile(p.ix, j);
-            ea = 0xFFFFFFFFu;
-            if (ex0) ea = __ldg(p.ix.entries + (int64_t)j * s.TPT + e0);
-        };
-        if (nloc > 0) fetch(0, m1, ent1a);
-        if (nloc > 1) fetch(1, m2, ent2a);
-        int prev_hg = -1;
-        constexpr int CPR = D / 8, RSTEP = kLoaders / CPR;   // 16 chunks per row, 4 rows per step
+        constexpr int CPR = D / 8, RSTEP = kLoaders / CPR, NIT = kTileRows / RSTEP;   // 16 chunks per row, 8 rows per thread
         const int cchunk = t % CPR, rbase = t / CPR;
         const uint32_t slab_off = (uint32_t)(cchunk >> 3) * (kTileRows * 128);
+        int gq[NIT], gd[NIT];                   // (head-in-group * head stride) / 8 of this thread's rows
+#pragma unroll
+        for (int it = 0; it < NIT; ++it) {
+            const int g = (rbase + it * RSTEP) / s.TPT;
+            gq[it] = (int)((g * p.q_sh) >> 3);
+            gd[it] = (int)((g * p.do_sh) >> 3);
+        }
+        const int qsn8 = (int)(p.q_sn >> 3), dsn8 = (int)(p.do_sn >> 3);
+        const ET* qc = p.q + cchunk * 8;
+        const ET* dc = p.d_o + cchunk * 8;
         BT_DECL;
         for (int k = 0; k < nloc && ok; ++k) {
-            const int st = k & 1;
-            const TileInfo cur = m1;
-            const uint32_t c_ea = ent1a;
-            const bool c_nb = cur.hg != prev_hg;
-            prev_hg = cur.hg;
-            m1 = m2; ent1a = ent2a;
-            if (k + 2 < nloc) fetch(k + 2, m2, ent2a);
+            const int st = k & 1, slot = k & 3;
             BT_TOC(0);
             ok = mbar_wait(&qd_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
             BT_TOC(1);
-            if (t == 0) {
-                s_nb[st] = c_nb ? 1 : 0;
-                mbar_arrive(&meta_full[st]);
-            }
-            if (c_nb) {
-                ++kvn;
-                if (t == 0) {
-                    const int ks = kvn % kKVStages;
-                    ok = mbar_wait(&kv_empty[ks], ((kvn / kKVStages) & 1) ^ 1, status) && ok;
-                    mbar_expect_tx(&kv_full[ks], (uint32_t)kKV);
-                    uint8_t* dK = sKV + ks * kKV;
-                    uint8_t* dV = dK + KT * D * 2;
-#pragma unroll
-                    for (int b = 0; b < D / 64; ++b) {
-                        tma_load_2d(smem_u32(dK + b * KT * 128), &kmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
-                        tma_load_2d(smem_u32(dV + b * KT * 128), &vmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
-                    }
-                }
-            }
-            if (t < kTileRows) {
-                const bool va = c_ea != 0xFFFFFFFFu;
-                const long long ta = c_ea >> kSlotBits;
-                const int ha = cur.h * s.G + g0;
-                s_offq[st][t] = va ? (int)((ta * p.q_sn + (long long)ha * p.q_sh) >> 3) : -1;
-                s_offd[st][t] = va ? (int)((ta * p.do_sn + (long long)ha * p.do_sh) >> 3) : -1;
-            }
+            ok = mbar_wait(&off_full[slot], (k >> 2) & 1, status) && ok;
             BT_TOC(2);
-            named_bar_sync(1, kLoaders);
+            const int hq0 = (int)(((long long)s_h[slot] * s.G * p.q_sh) >> 3), hd0 = (int)(((long long)s_h[slot] * s.G * p.do_sh) >> 3);
+            int tok[NIT];
+#pragma unroll
+            for (int it = 0; it < NIT; ++it) tok[it] = s_tok[slot][rbase + it * RSTEP];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&off_empty[slot]);
             BT_TOC(3);
-            {
-                const uint32_t dq_ = smem_u32(sQD + st * kQD) + slab_off;
-                const uint32_t dd_ = dq_ + kTileRows * D * 2;
+            const uint32_t dq_ = smem_u32(sQD + st * kQD) + slab_off;
+            const uint32_t dd_ = dq_ + kTileRows * D * 2;
 #pragma unroll
-                for (int half = 0; half < 1; ++half) {
-                    constexpr int NIT = kTileRows / RSTEP;         // 8 rows per thread
-                    int oq[NIT], od[NIT];
-#pragma unroll
-                    for (int it = 0; it < NIT; ++it) {
-                        oq[it] = s_offq[st][rbase + (half * NIT + it) * RSTEP];
-                        od[it] = s_offd[st][rbase + (half * NIT + it) * RSTEP];
-                    }
-#pragma unroll
-                    for (int it = 0; it < NIT; ++it) {
-                        const int r = rbase + (half * NIT + it) * RSTEP;
-                        const bool valid = oq[it] >= 0;
-                        const uint32_t so = sw128_chunk_off(r, cchunk & 7);
-                        cp_async16(dq_ + so, p.q + ((long long)(valid ? oq[it] : 0) << 3) + cchunk * 8, valid);
-                        cp_async16(dd_ + so, p.d_o + ((long long)(valid ? od[it] : 0) << 3) + cchunk * 8, valid);
-                    }
-                }
+            for (int it = 0; it < NIT; ++it) {
+                const int r = rbase + it * RSTEP;
+                const bool valid = tok[it] >= 0;
+                const int tk = valid ? tok[it] : 0;
+                const uint32_t so = sw128_chunk_off(r, cchunk & 7);
+                cp_async16(dq_ + so, qc + ((long long)(tk * qsn8 + hq0 + gq[it]) << 3), valid);
+                cp_async16(dd_ + so, dc + ((long long)(tk * dsn8 + hd0 + gd[it]) << 3), valid);
             }
             cp_async_mbar_arrive_noinc(&qd_full[st]);
             BT_TOC(4);
@@ -296,9 +259,12 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         for (int k = 0; k < nloc && ok; ++k) {
             const int st = k & 1;
             BT_TOC(0);
-            ok = mbar_wait(&meta_full[st], (k >> 1) & 1, status) && ok;
+            ok = mbar_wait(&off_full[k & 3], (k >> 2) & 1, status) && ok;
             BT_TOC(1);
-            if (s_nb[st] != 0) {
+            const int new_block = s_nb[k & 3];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&off_empty[k & 3]);
+            if (new_block != 0) {
                 ++kvn;
                 ok = mbar_wait(&kv_full[kvn % kKVStages], (kvn / kKVStages) & 1, status) && ok;
             }
@@ -395,6 +361,74 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             BT_TOC(5);
         }
         if (lane == 0) BT_DUMP(24, 6);
+      } else if (warp == kWMma2 + 1) {
+        // ------------------------------------------------------------------ tile preparation (tokens of the rows)
+        // lane l owns rows l, l + 32, l + 64, l + 96; records and entries are fetched three tiles ahead
+        bool ok = true;
+        int gg[4], ee[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = lane + 32 * i;
+            gg[i] = r / s.TPT;
+            ee[i] = r - gg[i] * s.TPT;
+        }
+        struct Pre { int h, hg; uint32_t e[4]; };
+        auto fetch = [&](int k, Pre& m) {
+            const int j = sched.tile(k);
+            const TileInfo ti = load_tile(p.ix, j);
+            m.h = ti.h; m.hg = ti.hg;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m.e[i] = gg[i] < s.G ? __ldg(p.ix.entries + (int64_t)j * s.TPT + ee[i]) : 0xFFFFFFFFu;
+        };
+        Pre m1{0, -1, {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}}, m2 = m1, m3 = m1;
+        if (nloc > 0) fetch(0, m1);
+        if (nloc > 1) fetch(1, m2);
+        if (nloc > 2) fetch(2, m3);
+        int prev_hg = -1;
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int slot = k & 3;
+            const Pre cur = m1;
+            m1 = m2; m2 = m3;
+            if (k + 3 < nloc) fetch(k + 3, m3);
+            ok = mbar_wait(&off_empty[slot], ((k >> 2) & 1) ^ 1, status) && ok;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s_tok[slot][lane + 32 * i] = cur.e[i] != 0xFFFFFFFFu ? (int)(cur.e[i] >> kSlotBits) : -1;
+            if (lane == 0) {
+                s_h[slot] = cur.h;
+                s_nb[slot] = cur.hg != prev_hg ? 1 : 0;
+            }
+            prev_hg = cur.hg;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&off_full[slot]);
+        }
+      } else {
+        // ------------------------------------------------------------------ K/V blocks by TMA
+        bool ok = true;
+        int kvn = -1, prev_hg = -1;
+        TileInfo t1{0, 0, 0, -1}, t2 = t1;
+        if (nloc > 0) t1 = load_tile(p.ix, sched.tile(0));
+        if (nloc > 1) t2 = load_tile(p.ix, sched.tile(1));
+        for (int k = 0; k < nloc && ok; ++k) {
+            const TileInfo cur = t1;
+            t1 = t2;
+            if (k + 2 < nloc) t2 = load_tile(p.ix, sched.tile(k + 2));
+            if (cur.hg == prev_hg) continue;
+            prev_hg = cur.hg;
+            ++kvn;
+            if (lane == 0) {
+                const int ks = kvn % kKVStages;
+                ok = mbar_wait(&kv_empty[ks], ((kvn / kKVStages) & 1) ^ 1, status) && ok;
+                mbar_expect_tx(&kv_full[ks], (uint32_t)kKV);
+                uint8_t* dK = sKV + ks * kKV;
+                uint8_t* dV = dK + KT * D * 2;
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b) {
+                    tma_load_2d(smem_u32(dK + b * KT * 128), &kmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
+                    tma_load_2d(smem_u32(dV + b * KT * 128), &vmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
       }
     } else {
         // ------------------------------------------------------------------ P / dS and dQ epilogue
@@ -413,57 +447,88 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         int row0A = 0, row0B = 0, hA = 0, hB = 0;
         float lseA = 0.f, deltaA = 0.f;
         int cloA = 0, chiA = 0;
-        auto fetch_ent = [&](int k, uint32_t& ent, int& row0, int& h) {
-            const int j = sched.tile(k);
+        // tile indices of this group's tiles k, k + 2, k + 4 without a division per tile: a cursor (run index, offset
+        // in the run) that advances by two
+        int cq = sb / sched.run, cr = sb % sched.run;
+        auto cursor_next = [&]() {
+            const int j = (cq * sched.grid + sched.cta) * sched.run + cr;
+            cr += 2;
+            while (cr >= sched.run) { cr -= sched.run; ++cq; }
+            return j;
+        };
+        int jA = 0, jB = 0;
+        auto fetch_ent = [&](int j, uint32_t& ent, int& row0, int& h) {
             TileInfo ti = load_tile(p.ix, j);
             row0 = ti.row0; h = ti.h;
             ent = 0xFFFFFFFFu;
             if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);
         };
         auto fetch_stats = [&](uint32_t ent, int h, int row0, float& lse_, float& delta_, int& c_lo, int& c_hi) {
-            lse_ = 0.f; delta_ = 0.f; c_lo = 0; c_hi = 0;    // padding rows: nothing visible
+            // padding rows: their Q and dO rows are zero, so they add nothing to dK / dV whatever P is, and their dQ
+            // rows are never read: they count as fully visible with lse = delta = 0 (finite values everywhere)
+            lse_ = 0.f; delta_ = 0.f; c_lo = 0; c_hi = key_lim;
             if (ent != 0xFFFFFFFFu) {
                 const int tok_ = (int)(ent >> kSlotBits);
                 const int64_t idx = (int64_t)(h * s.G + g) * s.N + tok_;
                 lse_ = __ldg(p.lse + idx);
-                delta_ = __ldg(p.delta + idx);
+                delta_ = __ldg(p.delta + idx) * p.scale;
                 visible_cols(p.bd, tok_, row0, key_lim, c_lo, c_hi);
             }
         };
         if (sb < nloc) {
-            fetch_ent(sb, entA, row0A, hA);
+            jA = cursor_next();
+            fetch_ent(jA, entA, row0A, hA);
             fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
         }
-        if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B, hB);
+        if (sb + 2 < nloc) {
+            jB = cursor_next();
+            fetch_ent(jB, entB, row0B, hB);
+        }
         BT_DECL;
         for (int k = sb; k < nloc && ok; k += 2) {
-            const int j = sched.tile(k);
-            const uint32_t ent = entA;
-            const float lse_r = lseA, delta_r = deltaA;
+            const int j = jA;
+            const float lse_r = lseA, delta_s = deltaA;
             const int c_lo = cloA, c_hi = chiA;
             // rotate the prefetch registers
-            entA = entB; row0A = row0B; hA = hB;
+            entA = entB; row0A = row0B; hA = hB; jA = jB;
             if (k + 2 < nloc) fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
-            if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B, hB);
+            if (k + 4 < nloc) {
+                jB = cursor_next();
+                fetch_ent(jB, entB, row0B, hB);
+            }
             BT_TOC(0);
             ok = mbar_wait(&sdp_full[sb], (k >> 1) & 1, status) && ok;
             BT_TOC(1);
             tc_fence_after();
             uint32_t pp[KT / 2], dd[KT / 2];
+            // most tiles are fully visible to all their rows (only a token's own block is cut by causality)
+            const bool all_visible = __all_sync(0xffffffffu, c_lo == 0 && c_hi == KT);
 #pragma unroll
             for (int c0 = 0; c0 < KT; c0 += 32) {
                 uint32_t sv[32], dv[32];
                 tmem_ld32(tbase + lane_off + cS + sb * 128 + c0, sv);
                 tmem_ld32(tbase + lane_off + cDP + sb * 128 + c0, dv);
                 tmem_ld_wait();
+                if (all_visible) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
-                    float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
-                    float d0 = p0 * (__uint_as_float(dv[i]) - delta_r) * p.scale;
-                    float d1 = p1 * (__uint_as_float(dv[i + 1]) - delta_r) * p.scale;
-                    pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
-                    dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r));
+                        const float p1 = ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r));
+                        const float d0 = p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s);
+                        const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s);
+                        pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                        dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                        const float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                        const float d0 = p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s);
+                        const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s);
+                        pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                        dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                    }
                 }
             }
             tc_fence_before();
@@ -518,7 +583,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 }
                 __syncwarp();
             } else {
-                const bool row_valid = ent != 0xFFFFFFFFu;
+                const bool row_valid = true;   // padding rows are written too (never read)
                 uint4* dst = reinterpret_cast<uint4*>(p.dq_part + ((int64_t)j * kTileRows + r) * D);
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
