@@ -623,7 +623,7 @@ static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const Sel
     p.lse = a.lse; p.delta = a.delta;
     p.s = s; p.ix = ix;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
-    p.run = a.run > 0 ? a.run : 8;
+    p.run = a.run > 0 ? a.run : 32;    // longer runs: fewer flushes of the dK / dV accumulators per block
     p.bd = a.bd;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     auto kern = sel_bwd_pipe<ET>;
