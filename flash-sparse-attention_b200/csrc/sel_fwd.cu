@@ -354,12 +354,17 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
         // own tiles ahead, the visible-column bounds (which may need the token's row limits) one ahead
         const bool row_exists = g < s.G;
         uint32_t entA = 0xFFFFFFFFu, entB = 0xFFFFFFFFu;
-        int row0A = 0, row0B = 0, cloA = 0, chiA = BK;
-        auto fetch_ent = [&](int k, uint32_t& ent, int& row0) {
+        int row0A = 0, row0B = 0, cloA = 0, chiA = BK, hA = 0, hB = 0;
+        auto fetch_ent = [&](int k, uint32_t& ent, int& row0, int& h) {
             const int j = sched.tile(k);
-            row0 = load_tile(p.ix, j).row0;
+            const TileInfo ti = load_tile(p.ix, j);
+            row0 = ti.row0; h = ti.h;
             ent = 0xFFFFFFFFu;
             if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e);
+        };
+        // statistics go to ml[(head, token, slot)]: the merge kernel reads a token's T pairs as one contiguous line
+        auto ml_index = [&](uint32_t ent, int h) {
+            return ((int64_t)(h * s.G + g) * s.N + (int64_t)(ent >> kSlotBits)) * s.T + (int)(ent & ((1u << kSlotBits) - 1));
         };
         auto fetch_bounds = [&](uint32_t ent, int row0, int& c_lo, int& c_hi) {
             c_lo = 0; c_hi = BK;   // padding rows: anything finite
@@ -368,6 +373,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
         bool have_prev = false, prev_valid = false;
         int prev_j = 0, prev_u = 0;
         float prev_m = 0.f, prev_l = 0.f;
+        int64_t prev_mli = 0;
         // O / l -> staging -> TMA store, for the tile (prev_j) whose softmax ran one iteration ago
         auto epilogue = [&]() {
             T_TIC;
@@ -398,7 +404,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             }
             tc_fence_before();
             mbar_arrive(&o_empty[sb]);
-            if (prev_valid) p.ml[(int64_t)prev_j * kTileRows + r] = make_float2(prev_m, prev_l);
+            if (prev_valid) p.ml[prev_mli] = make_float2(prev_m, prev_l);
             fence_async_smem();
             __syncwarp();
 #ifdef FSA_TIMING
@@ -414,10 +420,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             if (quarter == 2 && lane == 0) TR(3, prev_u * 2 + sb, 3);
         };
         if (sb < nloc) {
-            fetch_ent(sb, entA, row0A);
+            fetch_ent(sb, entA, row0A, hA);
             fetch_bounds(entA, row0A, cloA, chiA);
         }
-        if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B);
+        if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B, hB);
         for (int k = sb; k < nloc && ok; k += 2) {
             const int j = sched.tile(k);
             const int u = k >> 1;                     // use count of this group's O buffer
@@ -425,10 +431,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             const uint32_t tS = tS0 + sbuf * BK;
             const bool row_valid = entA != 0xFFFFFFFFu;
             const int c_lo = cloA, c_hi = chiA;            // visible key columns of this row
-            entA = entB; row0A = row0B;
+            const int64_t mli = row_valid ? ml_index(entA, hA) : 0;
+            entA = entB; row0A = row0B; hA = hB;
             T_TIC;
             if (k + 2 < nloc) fetch_bounds(entA, row0A, cloA, chiA);
-            if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B);
+            if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B, hB);
             T_TOC(0);
             ok = mbar_wait(&s_full[sbuf], (k / C::NS) & 1, status) && ok;
             T_TOC(1);
@@ -518,7 +525,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             // to finish, so the wait below is normally free
             if (have_prev) epilogue();
             have_prev = true;
-            prev_j = j; prev_u = u; prev_m = m; prev_l = l; prev_valid = row_valid;
+            prev_j = j; prev_u = u; prev_m = m; prev_l = l; prev_valid = row_valid; prev_mli = mli;
         }
         if (have_prev && ok) epilogue();
         if (lane == 0) bulk_wait0();
@@ -672,7 +679,11 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> 
         tc_fence_after();
         {
             const int64_t grow = (int64_t)item * kTileRows + r;
-            if (row_valid) p.ml[grow] = make_float2(m, l);
+            if (row_valid) {
+                const uint32_t ent = s_ent[r - (r / s.TPT) * s.TPT];
+                p.ml[((int64_t)(w.h * s.G + r / s.TPT) * s.N + (int64_t)(ent >> kSlotBits)) * s.T + (int)(ent & ((1u << kSlotBits) - 1))] =
+                    make_float2(m, l);
+            }
             uint4* dst = reinterpret_cast<uint4*>(p.opart + grow * D);
 #pragma unroll 2
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -711,6 +722,7 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
     const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);
     const int h = hq / s.G, g = hq - h * s.G;
     const int* prow = pos + ((int64_t)h * s.N + n) * s.T;
+    const float2* mlrow = ml + ((int64_t)hq * s.N + n) * s.T;      // this row's statistics, one pair per slot
     constexpr int V = D / 32;   // elements per lane
     float acc[V];
 #pragma unroll
@@ -730,7 +742,7 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
             u[j] = prj >= 0 ? ld_row_vec<V, ET>(opart + prj * D + lane * V) : make_uint4(0u, 0u, 0u, 0u);
         }
         if (pr >= 0) {
-            float2 v = ml[pr];
+            float2 v = mlrow[lane];
             m0 = v.x; l0 = v.y;
         }
         M = m0;
@@ -750,7 +762,7 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
             int ps = __ldg(prow + lane);
             if (ps >= 0) {
                 pr0 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
-                float2 v = ml[pr0];
+                float2 v = mlrow[lane];
                 m0 = v.x; l0 = v.y;
             }
         }
@@ -758,7 +770,7 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
             int ps = __ldg(prow + lane + 32);
             if (ps >= 0) {
                 pr1 = (int64_t)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
-                float2 v = ml[pr1];
+                float2 v = mlrow[lane + 32];
                 m1 = v.x; l1 = v.y;
             }
         }
@@ -860,7 +872,7 @@ static cudaError_t launch_sel_fwd(const SelFwdArgs& a, const SelShape& s, const 
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(1, stream);
-        static const int mode = [] { const char* v = getenv("FSA_FWD_REDUCE_MODE"); return v && *v ? atoi(v) : 0; }();
+        static const int mode = [] { const char* v = getenv("FSA_FWD_REDUCE_MODE"); return v && *v ? atoi(v) : 2; }();
         if (mode == 2)
             sel_fwd_reduce<D, ET, 2><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
         else if (mode == 1)
