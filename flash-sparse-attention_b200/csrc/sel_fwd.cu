@@ -57,9 +57,12 @@ struct SelFwdCfg {
 };
 
 // warps: 0..3 gather loaders | 4 issues S = Q K^T | 5 issues O = P V | 6..9 softmax group 0 | 10..13 softmax group 1
-// (any four consecutive warps cover the four TMEM lane quarters, warp % 4)
-constexpr int kFwdThreads = 448;
+// (any four consecutive warps cover the four TMEM lane quarters, warp % 4) | 14 prepares the tokens of the tile rows up
+// to four tiles ahead | 15 loads the K/V blocks by TMA.  The gather warps issue no global load of their own: a plain
+// load issued behind a burst of async copies waits for the burst.
+constexpr int kFwdThreads = 512;
 constexpr int kFwdLoaders = 128;
+constexpr int kFwdRing = 4;
 
 // Optional cycle accounting per role (debug builds only): FSA_TIMING defines a global table
 // [gridDim.x][32] of accumulated clock64() deltas.
@@ -100,9 +103,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
     uint8_t* sKV = sQ + C::NQ * C::kQ;
     uint8_t* sOS = sKV + C::NKV * C::kKV;
     uint8_t* tail = sOS + 2 * C::kOS;
-    long long (*s_off)[kTileRows] = reinterpret_cast<long long (*)[kTileRows]>(tail);   // [2][128] element offset of every
-                                                                                        // tile row in q (-1: padding)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * kTileRows * 8);
+    int (*s_tok)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail);   // [4][128] token of every tile row (-1: padding)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail + kFwdRing * kTileRows * 4);
     uint64_t* q_full = bars;                 // [NQ]
     uint64_t* q_empty = q_full + C::NQ;      // [NQ]
     uint64_t* kv_full = q_empty + C::NQ;     // [NKV]
@@ -112,10 +114,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
     uint64_t* p_full = s_empty + C::NS;      // [NS]
     uint64_t* o_full = p_full + C::NS;       // [2]
     uint64_t* o_empty = o_full + 2;          // [2]
-    uint64_t* meta_full = o_empty + 2;       // [NQ] "new block" flag of the tile in Q stage i is valid
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(meta_full + C::NQ);
-    int* s_nb = reinterpret_cast<int*>(meta_full + C::NQ) + 2;   // [NQ]
-    static_assert(2 * kTileRows * 8 + (3 * C::NQ + 2 * C::NKV + 3 * C::NS + 4) * 8 + 8 + 4 * C::NQ <= C::kTail, "tail budget");
+    uint64_t* off_full = o_empty + 2;        // [4] ring of prepared tiles: tokens, kv head, new-block flag are valid
+    uint64_t* off_empty = off_full + kFwdRing;   // [4] ... have been read by the gather warps and the S issuer
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(off_empty + kFwdRing);
+    int* s_h = reinterpret_cast<int*>(off_empty + kFwdRing) + 2;   // [4] kv head of the prepared tile
+    int* s_nb = s_h + kFwdRing;                                    // [4] 1: the tile starts a new K/V block
+    static_assert(kFwdRing * kTileRows * 4 + (2 * C::NQ + 2 * C::NKV + 3 * C::NS + 4 + 2 * kFwdRing) * 8 + 8 + 8 * kFwdRing <= C::kTail,
+                  "tail budget");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const SelShape& s = p.s;
@@ -126,7 +131,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
     }
 
     if (tid == 0) {
-        for (int i = 0; i < C::NQ; ++i) { mbar_init(&q_full[i], kFwdLoaders); mbar_init(&q_empty[i], 1); mbar_init(&meta_full[i], 1); }
+        for (int i = 0; i < C::NQ; ++i) { mbar_init(&q_full[i], kFwdLoaders); mbar_init(&q_empty[i], 1); }
+        for (int i = 0; i < kFwdRing; ++i) { mbar_init(&off_full[i], 1); mbar_init(&off_empty[i], kFwdLoaders / 32 + 1); }
         for (int i = 0; i < C::NKV; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
         for (int i = 0; i < C::NS; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 1); mbar_init(&p_full[i], 128); }
         for (int i = 0; i < 2; ++i) { mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 128); }
@@ -145,89 +151,48 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
     const int nloc = sched.nloc;
 
     if (warp < 4) {
-        // ------------------------------------------------------------------ loaders (128 threads)
-        // Thread t looks up the token of tile row t, and copies 16-byte chunk (t % CPR) of the rows
-        // t / CPR, t / CPR + RSTEP, ... (a half-warp covers one 256-byte row).
+        // ------------------------------------------------------------------ gather warps (128 threads)
+        // Thread t copies 16-byte chunk (t % CPR) of the rows t / CPR, t / CPR + RSTEP, ... (a half-warp covers one
+        // 256-byte row).  Tokens come from the prepared ring; the head part of a row offset is a thread constant.
         T_DECL;
         const int t = tid;
         bool ok = true;
-        int kvn = -1;
-        // row t of every tile: head of the group and entry slot are thread constants
-        const int g0 = t / s.TPT, e0 = t - g0 * s.TPT;
-        const bool row_exists = g0 < s.G;
-        // Tile records and entries are addressed by the tile index alone, so they are fetched two
-        // tiles ahead of their use.
-        TileInfo m1{0, 0, 0, -1}, m2{0, 0, 0, -1};
-        uint32_t ent1 = 0xFFFFFFFFu, ent2 = 0xFFFFFFFFu;
-        auto fetch = [&](int k, TileInfo& ti, uint32_t& ent) {
-            const int j = sched.tile(k);
-            ti = load_tile(p.ix, j);
-            ent = 0xFFFFFFFFu;
-            if (row_exists) ent = __ldg(p.ix.entries + (int64_t)j * s.TPT + e0);
-        };
-        if (nloc > 0) fetch(0, m1, ent1);
-        if (nloc > 1) fetch(1, m2, ent2);
-        int prev_hg = -1;
-        // copy schedule of this thread: chunk c of rows rbase, rbase + RSTEP, ...
         constexpr int CPR = D / 8;                         // 16-byte chunks per row
         constexpr int RSTEP = kFwdLoaders / CPR;           // rows advanced per iteration
+        constexpr int NIT = kTileRows / RSTEP;
         const int cchunk = t % CPR, rbase = t / CPR;
         const uint32_t slab_off = (uint32_t)(cchunk >> 3) * (kTileRows * 128);
+        int gq[NIT];                                       // (head-in-group * head stride) / 8 of this thread's rows
+#pragma unroll
+        for (int it = 0; it < NIT; ++it) gq[it] = (int)((((rbase + it * RSTEP) / s.TPT) * q_sh) >> 3);
+        const int qsn8 = (int)(q_sn >> 3);
+        const ET* qc = q + cchunk * 8;
         for (int k = 0; k < nloc && ok; ++k) {
-            const int qs = k % C::NQ;
-            const TileInfo cur = m1;
-            const uint32_t c_ent = ent1;
-            const int c_h = cur.h, c_row0 = cur.row0;
-            const bool c_nb = cur.hg != prev_hg;
-            prev_hg = cur.hg;
-            m1 = m2; ent1 = ent2;
+            const int qs = k % C::NQ, slot = k % kFwdRing;
             T_TIC;
-            if (k + 2 < nloc) fetch(k + 2, m2, ent2);
-            T_TOC(0);
-            // the Q stage (and its flag slot) is free once the S MMA of the tile that used it is done
+            // the Q stage is free once the S MMA of the tile that used it is done
             ok = mbar_wait(&q_empty[qs], ((k / C::NQ) & 1) ^ 1, status) && ok;
             T_TOC(1);
             if (t == 0) TR(0, k, 0);
-            if (t == 0) {
-                // tell the MMA thread whether this tile starts a new K/V block (it walks no index itself)
-                s_nb[qs] = c_nb ? 1 : 0;
-                mbar_arrive(&meta_full[qs]);
-            }
-            if (c_nb) {
-                ++kvn;
-                if (t == 0) {
-                    const int ks = kvn % C::NKV;
-                    ok = mbar_wait(&kv_empty[ks], ((kvn / C::NKV) & 1) ^ 1, status) && ok;
-                    mbar_expect_tx(&kv_full[ks], (uint32_t)C::kKV);
-                    uint8_t* dK = sKV + ks * C::kKV;
-                    uint8_t* dV = dK + BK * D * 2;
+            ok = mbar_wait(&off_full[slot], (k / kFwdRing) & 1, status) && ok;
+            const int hq0 = (int)(((long long)s_h[slot] * s.G * q_sh) >> 3);
+            int tok[NIT];
 #pragma unroll
-                    for (int b = 0; b < D / 64; ++b) {
-                        tma_load_2d(smem_u32(dK + b * BK * 128), &kmap, c_h * D + b * 64, c_row0, &kv_full[ks]);
-                        tma_load_2d(smem_u32(dV + b * BK * 128), &vmap, c_h * D + b * 64, c_row0, &kv_full[ks]);
-                    }
-                }
-            }
-            s_off[k & 1][t] = c_ent != 0xFFFFFFFFu ? (long long)(c_ent >> kSlotBits) * q_sn + (long long)(c_h * s.G + g0) * q_sh : -1ll;
+            for (int it = 0; it < NIT; ++it) tok[it] = s_tok[slot][rbase + it * RSTEP];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&off_empty[slot]);
             T_TOC(2);
-            named_bar_sync(1, kFwdLoaders);
-            {
-                const uint32_t dstq = smem_u32(sQ + qs * C::kQ) + slab_off;
-                const long long* offs = s_off[k & 1];
+            const uint32_t dstq = smem_u32(sQ + qs * C::kQ) + slab_off;
 #ifdef FSA_TIMING
-                if (!(p.dbg & 1))
+            if (!(p.dbg & 1))
 #endif
-                {
-                    // all row offsets first (the copies are asm statements the loads cannot move across)
-                    long long off[kTileRows / RSTEP];
+            {
 #pragma unroll
-                    for (int it = 0; it < kTileRows / RSTEP; ++it) off[it] = offs[rbase + it * RSTEP];
-#pragma unroll
-                    for (int it = 0; it < kTileRows / RSTEP; ++it) {
-                        const int r = rbase + it * RSTEP;
-                        const bool valid = off[it] >= 0;
-                        cp_async16(dstq + sw128_chunk_off(r, cchunk & 7), q + (valid ? off[it] : 0) + cchunk * 8, valid);
-                    }
+                for (int it = 0; it < NIT; ++it) {
+                    const int r = rbase + it * RSTEP;
+                    const bool valid = tok[it] >= 0;
+                    const int tk = valid ? tok[it] : 0;
+                    cp_async16(dstq + sw128_chunk_off(r, cchunk & 7), qc + ((long long)(tk * qsn8 + hq0 + gq[it]) << 3), valid);
                 }
             }
             // arrives on q_full when this thread's copies have landed; nobody waits here, so the
@@ -237,6 +202,74 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             if (t == 0) TR(0, k, 1);
         }
         if (t == 0) T_DUMP(0, 5);
+    } else if (warp == 14) {
+        // ------------------------------------------------------------------ tile preparation (tokens of the rows)
+        // lane l owns rows l, l + 32, l + 64, l + 96; records and entries are fetched three tiles ahead
+        bool ok = true;
+        int gg[4], ee[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = lane + 32 * i;
+            gg[i] = r / s.TPT;
+            ee[i] = r - gg[i] * s.TPT;
+        }
+        struct Pre { int h, hg; uint32_t e[4]; };
+        auto fetch = [&](int k, Pre& m) {
+            const int j = sched.tile(k);
+            const TileInfo ti = load_tile(p.ix, j);
+            m.h = ti.h; m.hg = ti.hg;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m.e[i] = gg[i] < s.G ? __ldg(p.ix.entries + (int64_t)j * s.TPT + ee[i]) : 0xFFFFFFFFu;
+        };
+        Pre m1{0, -1, {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}}, m2 = m1, m3 = m1;
+        if (nloc > 0) fetch(0, m1);
+        if (nloc > 1) fetch(1, m2);
+        if (nloc > 2) fetch(2, m3);
+        int prev_hg = -1;
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int slot = k % kFwdRing;
+            const Pre cur = m1;
+            m1 = m2; m2 = m3;
+            if (k + 3 < nloc) fetch(k + 3, m3);
+            ok = mbar_wait(&off_empty[slot], ((k / kFwdRing) & 1) ^ 1, status) && ok;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s_tok[slot][lane + 32 * i] = cur.e[i] != 0xFFFFFFFFu ? (int)(cur.e[i] >> kSlotBits) : -1;
+            if (lane == 0) {
+                s_h[slot] = cur.h;
+                s_nb[slot] = cur.hg != prev_hg ? 1 : 0;
+            }
+            prev_hg = cur.hg;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&off_full[slot]);
+        }
+    } else if (warp == 15) {
+        // ------------------------------------------------------------------ K/V blocks by TMA
+        bool ok = true;
+        int kvn = -1, prev_hg = -1;
+        TileInfo t1{0, 0, 0, -1}, t2 = t1;
+        if (nloc > 0) t1 = load_tile(p.ix, sched.tile(0));
+        if (nloc > 1) t2 = load_tile(p.ix, sched.tile(1));
+        for (int k = 0; k < nloc && ok; ++k) {
+            const TileInfo cur = t1;
+            t1 = t2;
+            if (k + 2 < nloc) t2 = load_tile(p.ix, sched.tile(k + 2));
+            if (cur.hg == prev_hg) continue;
+            prev_hg = cur.hg;
+            ++kvn;
+            if (lane == 0) {
+                const int ks = kvn % C::NKV;
+                ok = mbar_wait(&kv_empty[ks], ((kvn / C::NKV) & 1) ^ 1, status) && ok;
+                mbar_expect_tx(&kv_full[ks], (uint32_t)C::kKV);
+                uint8_t* dK = sKV + ks * C::kKV;
+                uint8_t* dV = dK + BK * D * 2;
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b) {
+                    tma_load_2d(smem_u32(dK + b * BK * 128), &kmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
+                    tma_load_2d(smem_u32(dV + b * BK * 128), &vmap, cur.h * D + b * 64, cur.row0, &kv_full[ks]);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
     } else if (warp == 4) {
         // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
         // The whole warp walks the loop (uniform control flow); one elected lane issues.  S and P V
@@ -254,8 +287,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             const int qs = k % C::NQ, sbuf = k % C::NS;
             T_TIC;
             // "does this tile start a new K/V block": published by the loader with the Q stage
-            ok = mbar_wait(&meta_full[qs], (k / C::NQ) & 1, status) && ok;
-            if (s_nb[qs] != 0) {
+            ok = mbar_wait(&off_full[k % kFwdRing], (k / kFwdRing) & 1, status) && ok;
+            const int new_block = s_nb[k % kFwdRing];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&off_empty[k % kFwdRing]);
+            if (new_block != 0) {
                 ++kvn;
                 ok = mbar_wait(&kv_full[kvn % C::NKV], (kvn / C::NKV) & 1, status) && ok;
             }
