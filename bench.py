@@ -31,7 +31,7 @@ import torch  # noqa: E402
 
 # DRAM bytes (read + write) per launch of the main kernels from one ncu capture of the small case (one 16384-token
 # sequence; profiles/sel_attn_kernels_small_case_ncu.md); traffic grows with the token count, so cfg1 is 4 x that.
-NCU_TRAFFIC_SMALL = {"sel_bwd_main": 178.6e6 + 538.6e6, "sel_fwd_main": 76.4e6 + 494.9e6}
+NCU_TRAFFIC_SMALL = {"sel_bwd_main": 290.8e6 + 572.2e6, "sel_fwd_main": 79.3e6 + 496.9e6}
 # the compressed pass of the decode step at batch 8 (profiles/decode_kernels_small_case_ncu.md); grows with the batch
 NCU_TRAFFIC_DECODE_B8 = 268.5e6 + 6.7e6
 
