@@ -195,8 +195,8 @@ def run_decode(args, rank, world, local_rank):
     NCCL all-gather."""
     import torch.distributed as dist
 
-    from fsa_preview.module import FlashSparseAttentionDecodeKernel, GraphedStep
-    from fsa_preview.ops.decode import CudaDecodeOps, nsa_decode_attention, shard_plan
+    from fsa_preview.module import FlashSparseAttentionDecodeKernel, GraphedShardedAttention, GraphedStep
+    from fsa_preview.ops.decode import CudaDecodeOps, DecodeStepPlan, nsa_decode_attention, shard_plan
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
@@ -236,10 +236,15 @@ def run_decode(args, rank, world, local_rank):
                                                cache.cmp_row0, max_len=max_len, shard=shard, **nsa)
         return gate_mix(mod.gate(qd.view(B, -1)), oc, os_.contiguous(), ow.contiguous())
 
-    # N > 1: the step holds two NCCL all-gathers; capturing them in a graph stalled here, so the sharded step is launched eagerly
-    use_graph = world == 1 and not args.no_graph
+    # N > 1: the step holds two NCCL all-gathers; capturing them in a graph stalled here, so the sharded step is three
+    # graphs (its collective-free parts) with the two all-gathers launched in between
+    use_graph = not args.no_graph
     step = eager_step
-    if use_graph:
+    if use_graph and world > 1:
+        plan = DecodeStepPlan(max_len=max_len, shard=shard, **nsa)
+        step = GraphedShardedAttention(plan, qd, cache, lambda oc, os_, ow: gate_mix(mod.gate(qd.view(B, -1)), oc, os_.contiguous(),
+                                                                                      ow.contiguous()))
+    elif use_graph:
         # the attention step at a fixed cache length, captured once and replayed
         with torch.no_grad():
             for _ in range(3):
@@ -293,7 +298,7 @@ def run_decode(args, rank, world, local_rank):
         ms_cmp = timed(g_cmp.replay, args.steps)
 
         # end to end: host q / k_new / v_new in, output row out, through the module's step (append + attention + gate mix)
-        gstep = GraphedStep(mod.step, cache, [qd, knh.to(dev), vnh.to(dev)]) if use_graph else None
+        gstep = GraphedStep(mod.step, cache, [qd, knh.to(dev), vnh.to(dev)]) if use_graph and world == 1 else None
 
         def e2e_step():
             if gstep is not None:

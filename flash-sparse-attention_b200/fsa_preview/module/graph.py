@@ -46,3 +46,46 @@ class GraphedStep:
         self.graph.replay()
         self.cache.host_len = [L + 1 for L in self.cache.host_len]
         return self.static_out
+
+
+class GraphedShardedAttention:
+    """The KV-sequence-sharded decode attention as three CUDA graphs around its two all-gathers.
+
+    A collective captured inside a graph stalled on this system, and launched kernel by kernel the sharded step is
+    bound by host launch cost; so the step's three collective-free parts (``DecodeStepPlan.part1/2/3``) are captured
+    separately and the two NCCL all-gathers of one packed buffer each stay ordinary launches between the replays:
+    five launches per step instead of about forty."""
+
+    def __init__(self, plan, q: torch.Tensor, cache: DecodeCache, finish: Callable[..., torch.Tensor], warmup: int = 2):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, plan.shard.group
+        args1 = (q, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.cmp_row0)
+        args2 = (q, cache.k, cache.v, cache.seq_len, cache.seq_row0)
+        world = plan.shard.world
+        with torch.no_grad():
+            for _ in range(warmup):                          # eager: sizes the buffers, sets kernel attributes
+                f1 = plan.part1(*args1)
+                g1 = torch.empty(world * f1.numel(), dtype=f1.dtype, device=f1.device)
+                dist.all_gather_into_tensor(g1, f1, group=self.group)
+                f2 = plan.part2(*args2, g1)
+                g2 = torch.empty(world * f2.numel(), dtype=f2.dtype, device=f2.device)
+                dist.all_gather_into_tensor(g2, f2, group=self.group)
+                finish(*plan.part3(q, g2)[:3])
+            torch.cuda.synchronize()
+            self.g1, self.g2 = g1, g2
+            self.graph1, self.graph2, self.graph3 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph1, capture_error_mode="thread_local"):
+                self.f1 = plan.part1(*args1)
+            with torch.cuda.graph(self.graph2, capture_error_mode="thread_local"):
+                self.f2 = plan.part2(*args2, self.g1)
+            with torch.cuda.graph(self.graph3, capture_error_mode="thread_local"):
+                self.out = finish(*plan.part3(q, self.g2)[:3])
+
+    def __call__(self) -> torch.Tensor:
+        self.graph1.replay()
+        self.dist.all_gather_into_tensor(self.g1, self.f1, group=self.group)
+        self.graph2.replay()
+        self.dist.all_gather_into_tensor(self.g2, self.f2, group=self.group)
+        self.graph3.replay()
+        return self.out

@@ -127,20 +127,26 @@ def shard_plan(max_len: int, kernel_size: int, kernel_stride: int, rank: int, wo
     return Shard(rank * per, (rank + 1) * per, rank * cper, (rank + 1) * cper, rank, world, group)
 
 
-def _gather(shard: Shard, *tensors: torch.Tensor):
-    """All-gather several fp32 tensors from every rank of the shard's group with ONE collective (they are packed
-    into one flat buffer): returns, per input, a view ``[world, *t.shape]``."""
-    import torch.distributed as dist
+def _pack(*tensors: torch.Tensor) -> torch.Tensor:
+    return torch.cat([t.reshape(-1) for t in tensors])
 
-    flat = torch.cat([t.reshape(-1) for t in tensors])
-    out = torch.empty((shard.world * flat.numel(),), dtype=flat.dtype, device=flat.device)
-    dist.all_gather_into_tensor(out, flat, group=shard.group)
-    out = out.view(shard.world, flat.numel())
+
+def _unpack(gathered: torch.Tensor, world: int, *like: torch.Tensor):
+    """``gathered [world * n]`` (every rank's packed buffer) -> per tensor a view ``[world, *shape]``."""
+    out = gathered.view(world, -1)
     views, off = [], 0
-    for t in tensors:
-        views.append(out[:, off : off + t.numel()].reshape(shard.world, *t.shape))
+    for t in like:
+        views.append(out[:, off : off + t.numel()].reshape(world, *t.shape))
         off += t.numel()
     return views
+
+
+def _all_gather(flat: torch.Tensor, shard: Shard) -> torch.Tensor:
+    import torch.distributed as dist
+
+    out = torch.empty((shard.world * flat.numel(),), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(out, flat, group=shard.group)
+    return out
 
 
 def _merge_gathered(ops, o_all, lse_all, out_dtype):
@@ -151,6 +157,75 @@ def _merge_gathered(ops, o_all, lse_all, out_dtype):
     m = lse_all.permute(*range(1, nd - 1), 0)
     ml = torch.stack([m, torch.isfinite(m).to(torch.float32)], dim=-1).contiguous()
     return ops.lse_merge(o_part, ml, out_dtype)
+
+
+class DecodeStepPlan:
+    """The decode step cut at its two exchanges.  One GPU: ``part1`` -> ``part2`` -> ``part3`` back to back.  KV sequence
+    sharded: after ``part1`` and after ``part2`` every rank all-gathers one packed fp32 buffer (``self.flat1`` /
+    ``self.flat2``) and hands the gathered buffer to the next part.  Each part is free of host synchronisation and of
+    collectives, so it can be captured in a CUDA graph of its own while the two collectives stay ordinary launches."""
+
+    def __init__(self, *, kernel_size, kernel_stride, block_size, topk, init_blocks, local_blocks, window_size, max_len,
+                 sm_scale=None, shard: Optional[Shard] = None, ops=None, cmp_chunk: int = 512):
+        self.ks, self.stride, self.bs, self.topk = kernel_size, kernel_stride, block_size, topk
+        self.init_blocks, self.local_blocks, self.window, self.max_len = init_blocks, local_blocks, window_size, max_len
+        self.sm_scale, self.shard, self.ops, self.cmp_chunk = sm_scale, shard or Shard(), ops or CudaDecodeOps(), cmp_chunk
+        s = self.shard
+        max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
+        cmp_local = max(min(max_cmp, s.cmp_hi) - s.cmp_lo, 1)
+        self.nchunk = -(-cmp_local // cmp_chunk)
+        self.ld = cmp_chunk * self.nchunk
+        self.max_blocks = -(-max_len // block_size)
+        self.npieces = -(-(window_size + 1) // block_size)
+        self.rpp = 4 if topk % 4 == 0 else (2 if topk % 2 == 0 else 1)   # a partial never mixes selected blocks and window pieces
+
+    # compressed branch on this GPU's compressed rows
+    def part1(self, q, cmp_k, cmp_v, seq_len, cmp_row0):
+        ops, s = self.ops, self.shard
+        Hk = cmp_k.shape[1]
+        scale = self.sm_scale if self.sm_scale is not None else q.shape[-1] ** -0.5
+        # compressed token c is visible when its window ends at or before t (c*stride + ks - 1 <= t)
+        self.num_cmp, lo_c, hi_c = ops.cmp_ranges(seq_len, cmp_row0, Hk, self.ks, self.stride, s.cmp_lo, s.cmp_hi)
+        o_part, ml, self.scores = ops.attn_partial(q, cmp_k, cmp_v, lo_c, hi_c, self.cmp_chunk, self.nchunk, scale, want_scores=True)
+        if s.world == 1:
+            self.o_cmp, self.lse_cmp = ops.lse_merge(o_part, ml, q.dtype)
+            return None
+        self.o_loc, self.lse_loc = ops.lse_merge(o_part, ml, torch.float32)
+        self.flat1 = _pack(self.o_loc, self.lse_loc, self.scores)
+        return self.flat1
+
+    # top-k of the decoded row, selected blocks + sliding window on this GPU's rows
+    def part2(self, q, k, v, seq_len, seq_row0, gathered1=None):
+        ops, s = self.ops, self.shard
+        Hk = k.shape[1]
+        scale = self.sm_scale if self.sm_scale is not None else q.shape[-1] ** -0.5
+        if s.world == 1:
+            scores, shard_len, shard_stride = self.scores, self.ld, 0
+        else:
+            o_all, lse_all, scores = _unpack(gathered1, s.world, self.o_loc, self.lse_loc, self.scores)   # scores stay shard-major
+            self.o_cmp, self.lse_cmp = _merge_gathered(ops, o_all, lse_all, q.dtype)
+            shard_len, shard_stride = s.cmp_hi - s.cmp_lo, scores.stride(0)
+        self.topk_idx = ops.select_topk(scores, self.ld, shard_len, shard_stride, self.lse_cmp, seq_len, self.num_cmp, Hk, self.ks,
+                                        self.stride, self.bs, self.init_blocks, self.local_blocks, self.topk, self.max_blocks)
+        lo, hi = ops.ranges(self.topk_idx, seq_len, seq_row0, Hk, self.topk, self.bs, self.window, self.bs, self.npieces,
+                            s.tok_lo, s.tok_hi)
+        o_part, ml, _ = ops.attn_partial(q, k, v, lo, hi, self.bs, 1, scale, rpp=self.rpp)
+        first = torch.float32 if s.world > 1 else q.dtype
+        self.o_sel, self.lse_sel = ops.lse_merge(o_part, ml, first, 0, self.topk // self.rpp)
+        self.o_win, self.lse_win = ops.lse_merge(o_part, ml, first, self.topk // self.rpp, -(-self.npieces // self.rpp))
+        if s.world == 1:
+            return None
+        self.o_both, self.lse_both = torch.stack([self.o_sel, self.o_win]), torch.stack([self.lse_sel, self.lse_win])
+        self.flat2 = _pack(self.o_both, self.lse_both)
+        return self.flat2
+
+    def part3(self, q, gathered2=None):
+        s = self.shard
+        if s.world > 1:
+            o_all, lse_all = _unpack(gathered2, s.world, self.o_both, self.lse_both)      # [W, 2, B, Hq, (D)]
+            both, lse_both = _merge_gathered(self.ops, o_all, lse_all, q.dtype)
+            self.o_sel, self.o_win, self.lse_sel, self.lse_win = both[0], both[1], lse_both[0], lse_both[1]
+        return self.o_cmp, self.o_sel, self.o_win, self.lse_cmp, self.lse_sel, self.lse_win, self.topk_idx
 
 
 def nsa_decode_attention(
@@ -167,42 +242,11 @@ def nsa_decode_attention(
     """The three NSA branches for ONE new token per sequence; the token is the last of its sequence and gets
     what the prefill path gives that row.  Returns (o_cmp, o_sel, o_win [B,Hq,D], lse_cmp, lse_sel, lse_win
     [B,Hq] log2 units, topk_idx [B,Hk,T]).  ``max_len`` (host int) bounds every sequence length."""
-    ops = ops or CudaDecodeOps()
-    shard = shard or Shard()
-    B, Hq, D = q.shape
-    Hk = k.shape[1]
-    if sm_scale is None:
-        sm_scale = D ** -0.5
-    # ---- compressed branch: compressed token c is visible when its window ends at or before t (c*stride + ks - 1 <= t)
-    num_cmp, lo_c, hi_c = ops.cmp_ranges(seq_len, cmp_row0, Hk, kernel_size, kernel_stride, shard.cmp_lo, shard.cmp_hi)
-    max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
-    cmp_local = max(min(max_cmp, shard.cmp_hi) - shard.cmp_lo, 1)
-    nchunk = -(-cmp_local // cmp_chunk)
-    o_part, ml, scores = ops.attn_partial(q, cmp_k, cmp_v, lo_c, hi_c, cmp_chunk, nchunk, sm_scale, want_scores=True)
-    ld = cmp_chunk * nchunk
-    if shard.world == 1:
-        o_cmp, lse_cmp = ops.lse_merge(o_part, ml, q.dtype)
-        shard_len, shard_stride = ld, 0
-    else:
-        o_loc, lse_loc = ops.lse_merge(o_part, ml, torch.float32)
-        o_all, lse_all, scores = _gather(shard, o_loc, lse_loc, scores)     # scores [W, B, Hk, ld] stay shard-major
-        o_cmp, lse_cmp = _merge_gathered(ops, o_all, lse_all, q.dtype)
-        shard_len, shard_stride = shard.cmp_hi - shard.cmp_lo, scores.stride(0)
-    # ---- top-k blocks of the decoded token
-    max_blocks = -(-max_len // block_size)
-    topk_idx = ops.select_topk(scores, ld, shard_len, shard_stride, lse_cmp, seq_len, num_cmp, Hk, kernel_size, kernel_stride,
-                               block_size, init_blocks, local_blocks, topk, max_blocks)
-    # ---- selected blocks + sliding window in one launch (ranges 0..T-1 and T..)
-    piece = block_size
-    npieces = -(-(window_size + 1) // piece)
-    lo, hi = ops.ranges(topk_idx, seq_len, seq_row0, Hk, topk, block_size, window_size, piece, npieces, shard.tok_lo, shard.tok_hi)
-    rpp = 4 if topk % 4 == 0 else (2 if topk % 2 == 0 else 1)     # a partial never mixes selected blocks and window pieces
-    o_part, ml, _ = ops.attn_partial(q, k, v, lo, hi, piece, 1, sm_scale, rpp=rpp)
-    first = torch.float32 if shard.world > 1 else q.dtype
-    o_sel, lse_sel = ops.lse_merge(o_part, ml, first, 0, topk // rpp)
-    o_win, lse_win = ops.lse_merge(o_part, ml, first, topk // rpp, -(-npieces // rpp))
-    if shard.world > 1:
-        o_all, lse_all = _gather(shard, torch.stack([o_sel, o_win]), torch.stack([lse_sel, lse_win]))   # [W, 2, B, Hq, (D)]
-        both, lse_both = _merge_gathered(ops, o_all, lse_all, q.dtype)
-        o_sel, o_win, lse_sel, lse_win = both[0], both[1], lse_both[0], lse_both[1]
-    return o_cmp, o_sel, o_win, lse_cmp, lse_sel, lse_win, topk_idx
+    plan = DecodeStepPlan(kernel_size=kernel_size, kernel_stride=kernel_stride, block_size=block_size, topk=topk,
+                          init_blocks=init_blocks, local_blocks=local_blocks, window_size=window_size, max_len=max_len,
+                          sm_scale=sm_scale, shard=shard, ops=ops, cmp_chunk=cmp_chunk)
+    flat1 = plan.part1(q, cmp_k, cmp_v, seq_len, cmp_row0)
+    g1 = _all_gather(flat1, plan.shard) if flat1 is not None else None
+    flat2 = plan.part2(q, k, v, seq_len, seq_row0, g1)
+    g2 = _all_gather(flat2, plan.shard) if flat2 is not None else None
+    return plan.part3(q, g2)
