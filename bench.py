@@ -469,8 +469,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="cfg1", choices=["cfg1", "small"],
-                    help="small = one 16384-token sequence of cfg1 (a quarter of it), for profiler captures")
+    ap.add_argument("--case", default="cfg1", choices=["cfg1", "small", "cfg2"],
+                    help="small = one 16384-token sequence of cfg1 (a quarter of it), for profiler captures; "
+                         "cfg2 = one 65536-token sequence, 4 KV heads, --group / --head-dim (the GQA sweep)")
+    ap.add_argument("--group", type=int, default=2, help="cfg2: GQA group size (1..16)")
+    ap.add_argument("--head-dim", type=int, default=128, help="cfg2: 128 or 256")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="decode workload: launch the step's kernels one by one")
     args = ap.parse_args()
@@ -508,6 +511,8 @@ def main():
     seqlens, Hk, G, d, bs, T = (CFG[k] for k in ("seqlens", "Hk", "G", "d", "bs", "T"))
     if args.case == "small":
         seqlens = seqlens[:1]
+    if args.case == "cfg2":
+        seqlens, G, d = [65536], args.group, args.head_dim
     N = sum(seqlens)
     scale = d ** -0.5
     # each rank owns one 4-KV-head shard with its own seed
@@ -614,13 +619,14 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded N(0,1) q/k/v/dO, seeded causal block ids)",
-            "config": {"workload": workload_name() if args.case == "cfg1" else "small: 1x16384 tokens of cfg1", "parallelism": f"kv-head shards x{world}, no collective",
+            "config": {"workload": workload_name() if args.case == "cfg1" else ("small: 1x16384 tokens of cfg1" if args.case == "small" else
+                                    f"cfg2: 1x65536 tokens, 4 KV heads, G={G}, d={d}, B_K=64, T=16, fwd+bwd"), "parallelism": f"kv-head shards x{world}, no collective",
                        "l2": "inputs and partial buffers exceed L2 (q 134 MB, partials > 4 GB per step)",
                        "useful_flops_per_step": flops_step, "tokens_per_s": world * N / (ms_step * 1e-3)},
             "kernels": kern,
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (achieved / peak_tf if achieved else None),
-                         "traffic": NCU_TRAFFIC_SMALL[dom] * (4 if args.case == "cfg1" else 1),
+                         "traffic": (NCU_TRAFFIC_SMALL[dom] * (4 if args.case == "cfg1" else 1)) if args.case != "cfg2" else None,
                          "traffic_source": "ncu capture of the small case scaled by the token count", "peak_source": peak_src},
             "cpu_baseline": cpu,
             "e2e": {"value": world * flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,

@@ -172,7 +172,8 @@ class DecodeStepPlan:
         self.sm_scale, self.shard, self.ops, self.cmp_chunk = sm_scale, shard or Shard(), ops or CudaDecodeOps(), cmp_chunk
         s = self.shard
         max_cmp = (max_len - kernel_size) // kernel_stride + 1 if max_len >= kernel_size else 0
-        cmp_local = max(min(max_cmp, s.cmp_hi) - s.cmp_lo, 1)
+        # every rank must size its score rows alike (they are all-gathered): the shard WIDTH, not what this rank holds of it
+        cmp_local = max(min(max_cmp, s.cmp_hi - s.cmp_lo), 1)
         self.nchunk = -(-cmp_local // cmp_chunk)
         self.ld = cmp_chunk * self.nchunk
         self.max_blocks = -(-max_len // block_size)

@@ -174,7 +174,8 @@ def _rank_main(rank, world, port, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        seqlens, steps, max_len = [37, 5, 64, 18], 6, 96
+        # max_len chosen so that the two ranks hold different numbers of 8-token score chunks (12 and 7 compressed tokens)
+        seqlens, steps, max_len = [37, 5, 64, 18], 6, 160
         q, k, v, wk, wv, pe = _make_problem(5, seqlens, 4, 2, 16, steps)
         shard = shard_plan(max_len, CFG["kernel_size"], CFG["kernel_stride"], rank, world, group=None, align=16)
         outs = _run_steps(shard, seqlens, steps, q, k, v, wk, wv, pe, max_len)
