@@ -3,7 +3,7 @@
 
 The attention itself runs on the sm_100a range-attention kernels; the selection scores are the
 raw products of the first query head of each GQA group with the compressed keys (one batched
-library GEMM per sequence, fp32 out) fed to the fused exp / block-score / top-k kernel.
+library GEMM per sequence, 16-bit operands, fp32 accumulation and output) fed to the fused exp / block-score / top-k kernel.
 """
 from __future__ import annotations
 
@@ -38,11 +38,16 @@ def select_topk_blocks(q, ck, lse, kernel_size, kernel_stride, block_size, topk,
         for Lq, Lk in zip(seqlens_q, seqlens_k):
             if Lq > 0:
                 q0 = q[qs : qs + Lq, ::G].transpose(0, 1)                 # [Hk, Lq, d] first head of each group
-                kk = ck[ks : ks + Lk].permute(1, 2, 0)                    # [Hk, d, Lk]
                 ld = max((Lk + 3) // 4 * 4, 4)
-                qk = torch.empty((Hk, Lq, ld), dtype=torch.float32, device=q.device)
                 if Lk > 0:
-                    qk[:, :, :Lk] = torch.bmm(q0.float(), kk.float())
+                    kk = ck[ks : ks + Lk]
+                    if ld != Lk:
+                        kk = torch.nn.functional.pad(kk, (0, 0, 0, 0, 0, ld - Lk))   # zero rows: the row stride stays 16-byte aligned
+                    # 16-bit operands, fp32 accumulation and fp32 output on the tensor cores (the products are exact;
+                    # the reference's score kernel does the same with tl.dot)
+                    qk = torch.bmm(q0, kk.permute(1, 2, 0), out_dtype=torch.float32)   # [Hk, Lq, ld]
+                else:
+                    qk = torch.zeros((Hk, Lq, ld), dtype=torch.float32, device=q.device)
                 rc = L.fsa_select_topk_seq(_lib.ptr(qk), ld, _lib.ptr(lse), N, qs, Lq, Lk, Hk, G, float(sm_scale), kernel_size,
                                            kernel_stride, block_size, init_blocks, local_blocks, max_blocks, t_out, _lib.ptr(out),
                                            _lib.current_stream(q.device))
