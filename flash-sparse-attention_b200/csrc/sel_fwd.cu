@@ -21,6 +21,8 @@
 // <= T partial rows through the `pos` map and merges them:  M = max m_s,
 // w_s = exp2(m_s - M),  o = sum w_s O_s / sum w_s l_s,  lse = M + log2 sum w_s l_s  (log2 units;
 // O_s is the unnormalised partial, l_s its row sum).
+#include <type_traits>
+
 #include "sel_launch.cuh"
 #include <cstdlib>
 
@@ -765,31 +767,35 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
     float L, M;
     if (MODE == 2 && s.T <= 16) {
-        // Up to 16 slots: the row loads depend only on the positions, so they are issued together with the loads of
-        // the statistics (one round trip less, 16 rows in flight per warp); weights are applied afterwards.
+        // Up to 16 slots (with 32 rows in flight the kernel measured slower: registers, occupancy): the row loads depend only on the positions, so they are issued together with
+        // the load of the statistics (one round trip less, all rows in flight per warp); weights are applied afterwards.
         int ps = lane < s.T ? __ldg(prow + lane) : -1;
         long long pr = -1;
         float m0 = -INFINITY, l0 = 0.f;
-        if (ps >= 0) pr = (long long)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
-        uint4 u[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const long long prj = __shfl_sync(0xffffffffu, pr, j);
-            u[j] = prj >= 0 ? ld_row_vec<V, ET>(opart + prj * D + lane * V) : make_uint4(0u, 0u, 0u, 0u);
-        }
-        if (pr >= 0) {
+        if (ps >= 0) {
+            pr = (long long)(ps / s.TPT) * kTileRows + g * s.TPT + ps % s.TPT;
             float2 v = mlrow[lane];
             m0 = v.x; l0 = v.y;
         }
-        M = m0;
+        auto body = [&](auto nt_tag) {
+            constexpr int NT = decltype(nt_tag)::value;
+            uint4 u[NT];
 #pragma unroll
-        for (int o_ = 16; o_; o_ >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o_));
-        const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
-        L = w0 * l0;
+            for (int j = 0; j < NT; ++j) {
+                const long long prj = __shfl_sync(0xffffffffu, pr, j);
+                u[j] = prj >= 0 ? ld_row_vec<V, ET>(opart + prj * D + lane * V) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            M = m0;
 #pragma unroll
-        for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
+            for (int o_ = 16; o_; o_ >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o_));
+            const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
+            L = w0 * l0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) fma_row_vec<V, ET>(acc, u[j], __shfl_sync(0xffffffffu, w0, j));
+            for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) fma_row_vec<V, ET>(acc, u[j], __shfl_sync(0xffffffffu, w0, j));
+        };
+        body(std::integral_constant<int, 16>{});
     } else {
         // lane handles slots lane and lane + 32: partial row index and statistics
         int64_t pr0 = -1, pr1 = -1;

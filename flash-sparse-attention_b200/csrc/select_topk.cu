@@ -50,16 +50,31 @@ __global__ void __launch_bounds__(128) select_topk_kernel(const TopkParams p) {
     int nvis = t >= p.ks - 1 ? (t - (p.ks - 1)) / p.stride + 1 : 0;
     nvis = min(nvis, p.ncmp);
     const float* row = p.qk + ((int64_t)h * p.L + t) * p.ld;
-    for (int c = lane; c < p.ncmp; c += 32) ps[c] = c < nvis ? exp2f(fmaf(row[c], p.scale_log2, -lse)) : 0.f;
-    __syncwarp();
     const int bq = t / p.BK;                 // the token's own block
     const int nb = min(bq + 1, p.max_blocks);   // causal candidates
     const int bstride = p.BK / p.stride, pad = p.ks / p.stride - 1;
+    // probabilities of the compressed keys the candidate blocks can touch; eight loads in flight per lane, none past
+    // the visible keys
+    const int cmax = min(p.ncmp, nb * bstride + p.nw);
+    for (int c0 = 0; c0 < cmax; c0 += 256) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * 32 + lane;
+            v[j] = c < nvis ? row[c] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * 32 + lane;
+            if (c < cmax) ps[c] = c < nvis ? exp2f(fmaf(v[j], p.scale_log2, -lse)) : 0.f;
+        }
+    }
+    __syncwarp();
     for (int b = lane; b < nb; b += 32) {
         float s = 0.f;
         for (int o = 0; o < p.nw; ++o) {
             int c = b * bstride - pad + o;
-            float v = (c >= 0 && c < p.ncmp) ? ps[c] : 0.f;
+            float v = (c >= 0 && c < cmax) ? ps[c] : 0.f;
             s += v * p.w[o];
         }
         if (b < p.init_blocks || (bq >= b && bq < b + p.local_blocks)) s = INFINITY;
