@@ -337,24 +337,45 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
     if (warp == 0) tmem_dealloc(tbase, C::kCols);
 }
 
-// delta[hq, n] = sum_d o[n, hq, d] * do[n, hq, d]; one warp per (n, hq)
+// delta[hq, n] = sum_d o[n, hq, d] * do[n, hq, d].  D / 8 threads per row (16 bytes each), four rows per thread
+// in flight; a CTA of 256 threads covers 4 * 256 / (D / 8) rows.
 template <typename ET>
 __global__ void __launch_bounds__(256) sel_bwd_delta(const ET* __restrict__ o, int64_t o_sn, int64_t o_sh,
                                                      const ET* __restrict__ d_o, int64_t do_sn, int64_t do_sh,
                                                      int64_t N, int Hq, int D, float* __restrict__ delta) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= N * Hq) return;
-    const int64_t n = row / Hq;
-    const int hq = (int)(row % Hq);
-    const ET* po = o + n * o_sn + (int64_t)hq * o_sh;
-    const ET* pd = d_o + n * do_sn + (int64_t)hq * do_sh;
-    float acc = 0.f;
-    for (int c = lane * 8; c < D; c += 256) {
-        uint4 a = *reinterpret_cast<const uint4*>(po + c);
-        uint4 b = *reinterpret_cast<const uint4*>(pd + c);
-        const uint32_t* ua = &a.x;
-        const uint32_t* ub = &b.x;
+    const int tpr = D >> 3;                                  // threads per row: 8, 16 or 32
+    const int rpc = 256 / tpr;                               // rows per pass of the CTA
+    const int part = threadIdx.x % tpr, rloc = threadIdx.x / tpr;
+    const int64_t rows = N * Hq;
+    const int64_t row0 = (int64_t)blockIdx.x * (4 * rpc) + rloc;
+    // (token, head) of this thread's four rows: one division, then increments (a 64-bit division per row costs more
+    // than the row's loads)
+    int64_t nn[4];
+    int hh[4];
+    {
+        int64_t n = row0 / Hq;
+        int hq = (int)(row0 - n * Hq);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            nn[j] = n; hh[j] = hq;
+            hq += rpc;
+            while (hq >= Hq) { hq -= Hq; ++n; }
+        }
+    }
+    uint4 a[4], b[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        a[j] = b[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (row0 + (int64_t)j * rpc < rows) {
+            a[j] = *reinterpret_cast<const uint4*>(o + nn[j] * o_sn + (int64_t)hh[j] * o_sh + part * 8);
+            b[j] = *reinterpret_cast<const uint4*>(d_o + nn[j] * do_sn + (int64_t)hh[j] * do_sh + part * 8);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t* ua = &a[j].x;
+        const uint32_t* ub = &b[j].x;
+        float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float2 x = ElemTraits<ET>::unpack2(ua[i]);
@@ -362,10 +383,9 @@ __global__ void __launch_bounds__(256) sel_bwd_delta(const ET* __restrict__ o, i
             acc = fmaf(x.x, y.x, acc);
             acc = fmaf(x.y, y.y, acc);
         }
+        for (int o_ = tpr >> 1; o_; o_ >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o_);
+        if (part == 0 && row0 + (int64_t)j * rpc < rows) delta[(int64_t)hh[j] * N + nn[j]] = acc;
     }
-#pragma unroll
-    for (int o_ = 16; o_; o_ >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o_);
-    if (lane == 0) delta[(int64_t)hq * N + n] = acc;
 }
 
 // dq[n, hq, :] = sum over usable slots (and sub-tiles) of the partial rows, looked up through
@@ -376,7 +396,10 @@ __global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const ET* __restrict__ 
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= s.N * s.Hq) return;
-    const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);
+    // 32-bit division when the row index allows it (a 64-bit one costs about as much as the rest of the prologue)
+    const bool small = s.N * s.Hq <= 0x7fffffffll;
+    const int n = small ? (int)((unsigned)row / (unsigned)s.Hq) : (int)(row / s.Hq);
+    const int hq = (int)(row - (int64_t)n * s.Hq);
     const int h = hq / s.G, g = hq - h * s.G;
     const int* prow = pos + ((int64_t)h * s.N + n) * s.T;
     long long pr0 = -1, pr1 = -1;    // partial row of slot lane / lane + 32 (sub-tile 0)
@@ -449,7 +472,8 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     cudaError_t e = cudaMemsetAsync(a.dk_acc, 0, kv_elems * 4 * 2, stream);   // dk_acc and dv_acc are adjacent
     if (e != cudaSuccess) return e;
     if (rows > 0) {
-        unsigned grid = (unsigned)((rows + 7) / 8);
+        const int64_t rows_per_cta = 4 * (256 / (D / 8));
+        unsigned grid = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
         sel_bwd_delta<ET><<<grid, 256, 0, stream>>>((const ET*)a.o, a.o_sn, a.o_sh, (const ET*)a.d_o, a.do_sn, a.do_sh,
                                                     s.N, s.Hq, D, a.delta);
     }

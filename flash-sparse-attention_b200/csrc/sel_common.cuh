@@ -134,6 +134,39 @@ __device__ __forceinline__ int entry_block(const int* __restrict__ cu, const Sel
     return ck / BK + b + id;
 }
 
+// The same, with everything that depends only on the token looked up once (one binary search per token instead of
+// one per slot).
+struct TokenCtx {
+    int c, ck, kb, lo, hi;    // sequence start (q rows), K/V start, global id of block 0, visible range (range mode)
+};
+__device__ __forceinline__ TokenCtx token_ctx(const int* __restrict__ cu, const SelBounds& bd, int B, int BK, int n) {
+    TokenCtx t;
+    const int b = find_seq(cu, B, n);
+    t.c = __ldg(cu + b);
+    t.ck = bd.cu_k ? __ldg(bd.cu_k + b) : t.c;
+    t.kb = t.ck / BK + b;
+    t.lo = t.ck; t.hi = -1;
+    if (bd.kv_hi) {
+        t.hi = __ldg(bd.kv_hi + n);
+        if (bd.kv_lo) t.lo = __ldg(bd.kv_lo + n);
+    }
+    return t;
+}
+__device__ __forceinline__ int entry_block_ctx(const TokenCtx& t, const SelBounds& bd, int BK, int n, int sl, int id_list,
+                                               int* row0_out) {
+    int id;
+    if (bd.kv_hi) {
+        if (t.hi < t.lo) return -1;
+        id = (t.lo - t.ck) / BK + sl;
+        if (id > (t.hi - t.ck) / BK) return -1;
+    } else {
+        id = id_list;
+        if (id < 0 || id > (n - t.c) / BK) return -1;
+    }
+    *row0_out = t.ck + id * BK;
+    return t.kb + id;
+}
+
 // Visible key columns [c_lo, c_hi) of a tile row whose block starts at K/V row `row0` and holds
 // `klim` keys: list mode is causal (rows <= tok); range mode uses the per-token bounds.
 __device__ __forceinline__ void visible_cols(const SelBounds& bd, int tok, int row0, int klim, int& c_lo, int& c_hi) {

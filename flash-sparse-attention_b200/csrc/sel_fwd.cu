@@ -757,7 +757,8 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // n * Hq + hq
     if (row >= s.N * s.Hq) return;
-    const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);
+    const int n = (int)(row / s.Hq), hq = (int)(row % s.Hq);   // (a 32-bit division here measured 50 % SLOWER end to end:
+                                                               // the kernel is sensitive to how its warps' loads interleave)
     const int h = hq / s.G, g = hq - h * s.G;
     const int* prow = pos + ((int64_t)h * s.N + n) * s.T;
     const float2* mlrow = ml + ((int64_t)hq * s.N + n) * s.T;      // this row's statistics, one pair per slot

@@ -14,14 +14,18 @@ __global__ void __launch_bounds__(256) sel_index_pass(const int* __restrict__ to
     int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = (int64_t)s.Hk * s.N;
     bool active = gid < total;
-    int h = active ? (int)(gid / s.N) : 0;
-    int n = active ? (int)(gid % s.N) : 0;
+    const bool small = total <= 0x7fffffffll;
+    int h = active ? (small ? (int)((unsigned)gid / (unsigned)s.N) : (int)(gid / s.N)) : 0;
+    int n = active ? (int)(gid - (int64_t)h * s.N) : 0;
     const int* row = topk_idx + ((int64_t)h * s.N + n) * s.T;
     unsigned lane = threadIdx.x & 31;
     unsigned lt = (1u << lane) - 1;
+    TokenCtx tc{0, 0, 0, 0, -1};
+    if (active) tc = token_ctx(cu, bd, s.B, s.BK, n);
+    const bool list = bd.kv_hi == nullptr;
     for (int sl = 0; sl < s.T; ++sl) {
         int r0 = 0;
-        int gb = active ? entry_block(cu, bd, s.B, s.BK, n, sl, row, &r0) : -1;
+        int gb = active ? entry_block_ctx(tc, bd, s.BK, n, sl, list ? __ldg(row + sl) : 0, &r0) : -1;
         int key = gb < 0 ? -1 : h * s.NBmax + gb;
         unsigned m = __match_any_sync(0xffffffffu, key);
         if (key >= 0) {
