@@ -68,6 +68,18 @@ def _rank_main(rank, world, port, ret):
                 assert float(err.max()) <= 2e-2 * scale and float(err.mean()) <= 1e-3 * scale, (s, i, float(err.max()), float(err.mean()))
                 fin = torch.isfinite(ref[3 + i])
                 torch.testing.assert_close(got[3 + i].cpu()[fin], ref[3 + i][fin], rtol=1e-4, atol=1e-4)
+        # the step as three CUDA graphs around its two all-gathers gives the same outputs as the launch-by-launch step
+        from fsa_preview.module import GraphedShardedAttention
+        from fsa_preview.ops.decode import DecodeStepPlan
+
+        qd = q[steps - 1].to(dev)
+        plan = DecodeStepPlan(max_len=max_len, shard=shard, **CFG)
+        graphed = GraphedShardedAttention(plan, qd, cache, lambda oc, os_, ow: torch.stack([oc, os_, ow]))
+        for _ in range(2):
+            out = graphed()
+        torch.cuda.synchronize()
+        for i in range(3):
+            assert torch.equal(out[i], got[i]), f"graphed sharded step: branch {i} differs"
         ret[rank] = "ok"
     except Exception:  # noqa: BLE001
         import traceback
