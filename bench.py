@@ -196,7 +196,7 @@ def run_decode(args, rank, world, local_rank):
     import torch.distributed as dist
 
     from fsa_preview.module import FlashSparseAttentionDecodeKernel, GraphedShardedAttention, GraphedStep
-    from fsa_preview.ops.decode import CudaDecodeOps, DecodeStepPlan, nsa_decode_attention, shard_plan
+    from fsa_preview.ops.decode import CudaDecodeOps, DecodeStepPlan, nsa_decode_attention, nsa_decode_mixed, shard_plan
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
@@ -232,6 +232,9 @@ def run_decode(args, rank, world, local_rank):
     from fsa.ops.gate import gate_mix
 
     def eager_step():
+        if world == 1:
+            return nsa_decode_mixed(qd, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0, cache.cmp_row0,
+                                    mod.gate(qd.view(B, -1)), max_len=max_len, **nsa)[0]
         oc, os_, ow, *_ = nsa_decode_attention(qd, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0,
                                                cache.cmp_row0, max_len=max_len, shard=shard, **nsa)
         return gate_mix(mod.gate(qd.view(B, -1)), oc, os_.contiguous(), ow.contiguous())
@@ -349,7 +352,7 @@ def run_decode(args, rank, world, local_rank):
             "e2e": ({"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": (qh.numel() + knh.numel() + vnh.numel()) * 2, "d2h_bytes_per_step": B * Hq * d * 2}
                     if e2e_n else None),
-            "gpu_launches": 9 * args.steps, "cuda_graph": use_graph,
+            "gpu_launches": (7 if world == 1 else 9) * args.steps, "cuda_graph": use_graph,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

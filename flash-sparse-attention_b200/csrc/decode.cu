@@ -546,6 +546,70 @@ __global__ void __launch_bounds__(256) lse_merge_kernel(const float* __restrict_
     if (lane == 0 && lse) lse[row] = L > 0.f ? M + log2f(L) : -INFINITY;
 }
 
+// Last kernel of a one-GPU decode step: merges the selected-block partials [0, ns) and the window partials [ns, ns + nw)
+// of every (sequence, query head) row and mixes the three branches with the sequence's gates, out = g0 o_cmp + g1 o_sel
+// + g2 o_win.  o_sel and o_win are rounded to the output type before the mix, as the separate merge + gate_mix kernels do.
+// One warp per row; a lane owns 4 consecutive columns per 128-column slab.
+template <typename ET>
+__global__ void __launch_bounds__(256) decode_finish_kernel(const float* __restrict__ o_part, const float2* __restrict__ ml, int64_t rows,
+                                                            int ns, int nw, int PS, int D, int Hq, const ET* __restrict__ o_cmp,
+                                                            const ET* __restrict__ gate, ET* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int64_t b = row / Hq;
+    const float g0 = (float)gate[b * 3], g1 = (float)gate[b * 3 + 1], g2 = (float)gate[b * 3 + 2];
+    const float2* mlr = ml + row * PS;
+    const float* src = o_part + row * PS * D;
+    float M[2], inv[2];
+#pragma unroll
+    for (int seg = 0; seg < 2; ++seg) {
+        const int p0 = seg ? ns : 0, pn = seg ? nw : ns;
+        float m = -INFINITY;
+        for (int i = lane; i < pn; i += 32) {
+            float2 v = mlr[p0 + i];
+            if (v.y > 0.f) m = fmaxf(m, v.x);
+        }
+#pragma unroll
+        for (int o_ = 16; o_; o_ >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o_));
+        float L = 0.f;
+        for (int i = lane; i < pn; i += 32) {
+            float2 v = mlr[p0 + i];
+            if (v.y > 0.f) L += exp2f(v.x - m) * v.y;
+        }
+#pragma unroll
+        for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
+        M[seg] = m;
+        inv[seg] = L > 0.f ? 1.f / L : 0.f;
+    }
+    for (int d = lane * 4; d < D; d += 128) {
+        float4 acc[2];
+#pragma unroll
+        for (int seg = 0; seg < 2; ++seg) {
+            const int p0 = seg ? ns : 0, pn = seg ? nw : ns;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < pn; ++i) {
+                const float2 v = mlr[p0 + i];
+                if (v.y > 0.f) {
+                    const float w = exp2f(v.x - M[seg]);
+                    const float4 x = *reinterpret_cast<const float4*>(src + (int64_t)(p0 + i) * D + d);
+                    a.x = fmaf(w, x.x, a.x); a.y = fmaf(w, x.y, a.y); a.z = fmaf(w, x.z, a.z); a.w = fmaf(w, x.w, a.w);
+                }
+            }
+            // round to the output type as the unfused path does
+            const uint32_t lo = ElemTraits<ET>::pack2(a.x * inv[seg], a.y * inv[seg]), hi = ElemTraits<ET>::pack2(a.z * inv[seg], a.w * inv[seg]);
+            const float2 f0 = ElemTraits<ET>::unpack2(lo), f1 = ElemTraits<ET>::unpack2(hi);
+            acc[seg] = make_float4(f0.x, f0.y, f1.x, f1.y);
+        }
+        const uint2 cu_ = *reinterpret_cast<const uint2*>(o_cmp + row * D + d);
+        const float2 c0 = ElemTraits<ET>::unpack2(cu_.x), c1 = ElemTraits<ET>::unpack2(cu_.y);
+        uint2 o;
+        o.x = ElemTraits<ET>::pack2(g0 * c0.x + g1 * acc[0].x + g2 * acc[1].x, g0 * c0.y + g1 * acc[0].y + g2 * acc[1].y);
+        o.y = ElemTraits<ET>::pack2(g0 * c1.x + g1 * acc[0].z + g2 * acc[1].z, g0 * c1.y + g1 * acc[0].w + g2 * acc[1].w);
+        *reinterpret_cast<uint2*>(out + row * D + d) = o;
+    }
+}
+
 // Top-k block ids of the decoded token of every sequence from its compressed-branch logits.
 // Same rule as select_topk_kernel (select_topk.cu) for the single row t = seq_len - 1.
 struct DecodeTopkParams {
@@ -579,11 +643,29 @@ __global__ void __launch_bounds__(256) decode_topk_kernel(const DecodeTopkParams
     const int bq = t / p.BK;
     const int nb = t >= 0 ? min(bq + 1, p.max_blocks) : 0;
     const int bstride = p.BK / p.stride, pad = p.ks / p.stride - 1;
+    // probabilities of the compressed tokens the candidate blocks can touch, staged in shared memory with coalesced
+    // loads (eight in flight per thread); then every block sums its few neighbours
+    float* pv = reinterpret_cast<float*>(sel + 64);
+    const int cmax = min(ncmp, nb * bstride + p.nw);
+    for (int c0 = 0; c0 < cmax; c0 += 2048) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * 256 + tid;
+            v[j] = c < cmax ? row[(int64_t)(c / p.shard_len) * p.shard_stride + c % p.shard_len] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * 256 + tid;
+            if (c < cmax) pv[c] = exp2f(v[j] - lse);
+        }
+    }
+    __syncthreads();
     for (int blk = tid; blk < nb; blk += 256) {
         float s = 0.f;
         for (int o = 0; o < p.nw; ++o) {
             int c = blk * bstride - pad + o;
-            float v = (c >= 0 && c < ncmp) ? exp2f(row[(int64_t)(c / p.shard_len) * p.shard_stride + c % p.shard_len] - lse) : 0.f;
+            float v = (c >= 0 && c < cmax) ? pv[c] : 0.f;
             s += v * p.w[o];
         }
         if (blk < p.init_blocks || (bq >= blk && bq < blk + p.local_blocks)) s = INFINITY;
@@ -798,7 +880,9 @@ extern "C" int fsa_decode_select_topk(const float* scores, int64_t scores_ld, in
     for (int i = 0; i < a; ++i)
         for (int j = 0; j < bb; ++j) p.w[i + j] += 1.f;
     p.out = topk_idx;
-    size_t smem = (size_t)(max_blocks + 64) * sizeof(float);
+    // block scores, winners, probabilities of the compressed tokens those blocks can touch
+    const int max_cmp_touched = max_blocks * (block_size / kernel_stride) + (kernel_size / kernel_stride + block_size / kernel_stride - 1);
+    size_t smem = (size_t)(max_blocks + 64 + max_cmp_touched) * sizeof(float);
     if (smem > 200 * 1024) return FSA_ERR_UNSUPPORTED;
     (void)cudaGetLastError();
     if (smem > 48 * 1024) {
@@ -839,4 +923,26 @@ extern "C" int fsa_decode_cmp_ranges(const int32_t* seq_len, const int32_t* cmp_
 extern "C" int fsa_decode_read_status(int* status_out) {
     if (!status_out) return FSA_ERR_BAD_ARG;
     return cudaMemcpyFromSymbol(status_out, g_decode_status, sizeof(int)) == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
+}
+
+extern "C" int fsa_decode_finish(const float* o_part, const float* ml, int64_t rows, int num_sel_partials, int num_win_partials,
+                                 int part_stride, int head_dim, int num_q_heads, int dtype, const void* o_cmp, const void* gate,
+                                 void* out, void* stream) {
+    if (!o_part || !ml || !o_cmp || !gate || !out || rows < 0 || num_sel_partials < 0 || num_win_partials < 0 || num_q_heads <= 0)
+        return FSA_ERR_BAD_ARG;
+    if (part_stride < num_sel_partials + num_win_partials || head_dim <= 0 || head_dim % 4 || ((uintptr_t)o_part & 15)) return FSA_ERR_BAD_ARG;
+    if (rows == 0) return FSA_OK;
+    (void)cudaGetLastError();
+    unsigned grid = (unsigned)((rows + 7) / 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == FSA_DTYPE_BF16)
+        decode_finish_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(o_part, (const float2*)ml, rows, num_sel_partials, num_win_partials, part_stride,
+                                                                 head_dim, num_q_heads, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)gate,
+                                                                 (__nv_bfloat16*)out);
+    else if (dtype == FSA_DTYPE_FP16)
+        decode_finish_kernel<__half><<<grid, 256, 0, st>>>(o_part, (const float2*)ml, rows, num_sel_partials, num_win_partials, part_stride, head_dim,
+                                                          num_q_heads, (const __half*)o_cmp, (const __half*)gate, (__half*)out);
+    else
+        return FSA_ERR_BAD_ARG;
+    return cudaGetLastError() == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
 }

@@ -83,6 +83,8 @@ SIGNATURES = {
          c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p],
     ),
     "fsa_decode_read_status": (c_int, [c_void_p]),
+    "fsa_decode_finish": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p]),
     "fsa_lse_merge": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fsa_decode_select_topk": (
         c_int,

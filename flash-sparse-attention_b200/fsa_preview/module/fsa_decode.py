@@ -16,7 +16,7 @@ from fsa.ops.gate import gate_mix
 from fsa.ops.linear_compress import compressed_seqlens, linear_compress
 from fsa_preview.cache import DecodeCache
 from fsa_preview.ops.compat import _linear_compress_decode
-from fsa_preview.ops.decode import Shard, nsa_decode_attention
+from fsa_preview.ops.decode import Shard, nsa_decode_attention, nsa_decode_mixed
 
 
 class FlashSparseAttentionDecode(torch.nn.Module):
@@ -92,10 +92,15 @@ class FlashSparseAttentionDecode(torch.nn.Module):
         v_new = self.proj_v(x).view(B, self.num_kv_heads, self.head_dim)
         q = self.rope_at(q, pos)
         cache.append(k_new, self.rope_at(k_new, pos), v_new, self.compress_key, self.compress_value, self.intra_block_pe, self.rope_at)
+        gate = self.gate(x)
+        if cache.shard.world == 1:
+            mixed, idx = nsa_decode_mixed(q, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0,
+                                          cache.cmp_row0, gate, max_len=cache.max_len, **self._nsa())
+            self.last_topk_idx = idx
+            return self.proj_o(mixed.flatten(1))
         oc, os_, ow, *_, idx = nsa_decode_attention(q, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0,
                                                     cache.cmp_row0, max_len=cache.max_len, shard=cache.shard, **self._nsa())
         self.last_topk_idx = idx
-        gate = self.gate(x)
         return self.proj_o(gate_mix(gate, oc, os_.contiguous(), ow.contiguous()).flatten(1))
 
     # ------------------------------------------------------------------ reference signature (one sequence, stateless)

@@ -9,7 +9,7 @@ import torch
 from fsa.ops.gate import gate_mix
 from fsa_preview.cache import DecodeCache
 from fsa_preview.ops.compat import _linear_compress_decode
-from fsa_preview.ops.decode import Shard, nsa_decode_attention
+from fsa_preview.ops.decode import Shard, nsa_decode_attention, nsa_decode_mixed
 
 
 class FlashSparseAttentionDecodeKernel(torch.nn.Module):
@@ -45,10 +45,15 @@ class FlashSparseAttentionDecodeKernel(torch.nn.Module):
         """One token per sequence: ``q [B, Hq, d]``, ``k_new / v_new [B, Hk, d]`` -> ``[B, Hq*d]``; appends to ``cache``."""
         cache.append(k_new, k_new, v_new, self.compress_key, self.compress_value, self.intra_block_pe, None)
         q = q.contiguous()
+        gate = self.gate(q.view(q.shape[0], -1))
+        if cache.shard.world == 1:
+            mixed, idx = nsa_decode_mixed(q, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0,
+                                          cache.cmp_row0, gate, max_len=cache.max_len, **self._nsa())
+            self.last_topk_idx = idx
+            return mixed.flatten(1)
         oc, os_, ow, *_, idx = nsa_decode_attention(q, cache.k, cache.v, cache.cmp_k, cache.cmp_v, cache.seq_len, cache.seq_row0,
                                                     cache.cmp_row0, max_len=cache.max_len, shard=cache.shard, **self._nsa())
         self.last_topk_idx = idx
-        gate = self.gate(q.view(q.shape[0], -1))
         return gate_mix(gate, oc, os_.contiguous(), ow.contiguous()).flatten(1)
 
     @torch.no_grad()

@@ -90,6 +90,21 @@ class CudaDecodeOps:
         _lib.check(rc, "fsa_decode_cmp_ranges")
         return num_cmp, lo, hi
 
+    def finish(self, o_part, ml, num_sel, num_win, o_cmp, gate):
+        """Merge the selected ([0, num_sel)) and window ([num_sel, num_sel + num_win)) partials of ``o_part [B,Hq,P,D]``
+        and mix the three branches with ``gate [B, 3]``: one launch, returns ``[B, Hq, D]`` in o_cmp's dtype."""
+        self._need_cuda(o_part)
+        B, Hq, P, D = o_part.shape
+        assert o_part.is_contiguous() and ml.is_contiguous() and o_cmp.is_contiguous() and num_sel + num_win <= P
+        gate = gate.to(o_cmp.dtype).contiguous()
+        out = torch.empty_like(o_cmp)
+        with torch.cuda.device(o_part.device):
+            rc = _lib.lib().fsa_decode_finish(_lib.ptr(o_part), _lib.ptr(ml), B * Hq, num_sel, num_win, P, D, Hq,
+                                              _lib.DTYPE_CODE[o_cmp.dtype], _lib.ptr(o_cmp), _lib.ptr(gate), _lib.ptr(out),
+                                              _lib.current_stream(o_part.device))
+        _lib.check(rc, "fsa_decode_finish")
+        return out
+
     def ranges(self, topk_idx, seq_len, seq_row0, num_kv_heads, topk, block_size, window, piece, num_pieces, shard_lo, shard_hi):
         self._need_cuda(seq_len)
         B = seq_len.numel()
@@ -196,7 +211,9 @@ class DecodeStepPlan:
         return self.flat1
 
     # top-k of the decoded row, selected blocks + sliding window on this GPU's rows
-    def part2(self, q, k, v, seq_len, seq_row0, gathered1=None):
+    def part2(self, q, k, v, seq_len, seq_row0, gathered1=None, gate=None):
+        """``gate [B, 3]`` (one GPU only): skip the two merges and return the gate-mixed output of the three branches
+        from one fused launch instead (``self.mixed``)."""
         ops, s = self.ops, self.shard
         Hk = k.shape[1]
         scale = self.sm_scale if self.sm_scale is not None else q.shape[-1] ** -0.5
@@ -211,6 +228,9 @@ class DecodeStepPlan:
         lo, hi = ops.ranges(self.topk_idx, seq_len, seq_row0, Hk, self.topk, self.bs, self.window, self.bs, self.npieces,
                             s.tok_lo, s.tok_hi)
         o_part, ml, _ = ops.attn_partial(q, k, v, lo, hi, self.bs, 1, scale, rpp=self.rpp)
+        if gate is not None and s.world == 1:
+            self.mixed = ops.finish(o_part, ml, self.topk // self.rpp, -(-self.npieces // self.rpp), self.o_cmp, gate)
+            return None
         first = torch.float32 if s.world > 1 else q.dtype
         self.o_sel, self.lse_sel = ops.lse_merge(o_part, ml, first, 0, self.topk // self.rpp)
         self.o_win, self.lse_win = ops.lse_merge(o_part, ml, first, self.topk // self.rpp, -(-self.npieces // self.rpp))
@@ -251,3 +271,14 @@ def nsa_decode_attention(
     flat2 = plan.part2(q, k, v, seq_len, seq_row0, g1)
     g2 = _all_gather(flat2, plan.shard) if flat2 is not None else None
     return plan.part3(q, g2)
+
+
+def nsa_decode_mixed(q, k, v, cmp_k, cmp_v, seq_len, seq_row0, cmp_row0, gate, **kw):
+    """One-GPU decode step ending in the gate mix: ``g0 o_cmp + g1 o_sel + g2 o_win`` ``[B, Hq, D]`` and the top-k ids.
+    Same arguments as ``nsa_decode_attention`` plus ``gate [B, 3]`` (after the sigmoid); the selected / window merges
+    and the mix run as one kernel."""
+    plan = DecodeStepPlan(**kw)
+    assert plan.shard.world == 1, "the fused finish is the one-GPU path; sharded steps merge across ranks first"
+    plan.part1(q, cmp_k, cmp_v, seq_len, cmp_row0)
+    plan.part2(q, k, v, seq_len, seq_row0, None, gate=gate)
+    return plan.mixed, plan.topk_idx

@@ -226,6 +226,15 @@ int fsa_decode_read_status(int* status_out);
 int fsa_lse_merge(const float* o_part, const float* ml, int64_t rows, int num_partials, int part_stride, int head_dim,
                   int out_dtype, void* o, float* lse, void* stream);
 
+/* Last kernel of a one-GPU decode step: LSE-merges the selected-block partials [0, num_sel_partials) and the window
+ * partials [num_sel_partials, + num_win_partials) of every row (rows = batch * num_q_heads, partial stride part_stride)
+ * and mixes the three branches with the sequence's gates [batch, 3] (after the sigmoid, activation dtype):
+ * out = g0 o_cmp + g1 o_sel + g2 o_win, all [rows, head_dim] in the activation dtype.  Replaces the two merges and the
+ * gate mix of fsa_preview/module/fsa_decode.py:188-193 by one launch. */
+int fsa_decode_finish(const float* o_part, const float* ml, int64_t rows, int num_sel_partials, int num_win_partials,
+                      int part_stride, int head_dim, int num_q_heads, int dtype, const void* o_cmp, const void* gate, void* out,
+                      void* stream);
+
 /* Top-k block ids for the decoded token of every sequence, from the scores buffer of the compressed branch
  * and its merged lse [B, Hq].  Same scoring, bf16 rounding and tie rule as fsa_select_topk_seq, evaluated at
  * t = seq_len[b] - 1 (the reference evaluates the "local blocks" rule at t = 0,
