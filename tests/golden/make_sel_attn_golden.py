@@ -16,7 +16,9 @@ os.environ["TRITON_INTERPRET"] = "1"
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, os.path.join(ROOT, "flash-sparse-attention_b200"))
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_sel_attn_golden.py <checkout of Relaxed-System-Lab/Flash-Sparse-Attention>")
+ref_root = sys.argv[1]
 sys.path.append(ref_root)
 
 import numpy as np  # noqa: E402
