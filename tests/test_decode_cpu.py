@@ -108,11 +108,12 @@ def _make_problem(seed, seqlens, Hq, Hk, d, steps):
     return q, k, v, wk, wv, pe
 
 
-def _run_steps(shard, seqlens, steps, q, k, v, wk, wv, pe, max_len):
+def _run_steps(shard, seqlens, steps, q, k, v, wk, wv, pe, max_len, always_compress=False):
     """Prefill a cache from the first L_b tokens, then decode ``steps`` tokens; returns the branch outputs per step."""
     ks, st = CFG["kernel_size"], CFG["kernel_stride"]
     B, Hk, d = len(seqlens), k[0].shape[1], k[0].shape[2]
     cache = DecodeCache(B, max_len, Hk, d, ks, st, torch.bfloat16, "cpu", shard)
+    cache.always_compress = always_compress
     kp = torch.cat([x[:L] for x, L in zip(k, seqlens)])
     vp = torch.cat([x[:L] for x, L in zip(v, seqlens)])
     cu = torch.tensor([0] + list(torch.tensor(seqlens).cumsum(0)), dtype=torch.int32)
@@ -160,6 +161,18 @@ def test_cache_and_step_logic_single_rank():
     q, k, v, wk, wv, pe = _make_problem(3, seqlens, 4, 2, 16, steps)
     outs = _run_steps(None, seqlens, steps, q, k, v, wk, wv, pe, max_len=80)
     _compare(outs, _expected(seqlens, steps, q, k, v, wk, wv, pe))
+
+
+def test_masked_compressor_path_matches_conditional_path():
+    """The launch-invariant append (compressor always runs, masked writes: what a captured step uses) leaves the same
+    cache and gives the same outputs as the append that skips the compressor when no window completes."""
+    seqlens, steps = [37, 5, 64], 10
+    q, k, v, wk, wv, pe = _make_problem(8, seqlens, 4, 2, 16, steps)
+    a = _run_steps(None, seqlens, steps, q, k, v, wk, wv, pe, max_len=96)
+    b = _run_steps(None, seqlens, steps, q, k, v, wk, wv, pe, max_len=96, always_compress=True)
+    for x, y in zip(a, b):
+        for i in range(7):
+            assert torch.equal(x[i], y[i])
 
 
 def _free_port():
