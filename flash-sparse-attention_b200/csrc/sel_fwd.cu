@@ -4,8 +4,7 @@
 // fsa/ops/FSA_topk_sparse_attention.py:285-566): KV blocks are the outer loop.  A persistent
 // CTA owns a contiguous range of tiles; a tile is <= 128 rows = (query head of the group,
 // selecting token).  Warp-specialised:
-//   warps 0..3  load: K/V block by tiled TMA (128-byte swizzle, double-buffered); query rows
-//               gathered by token id with 16-byte async copies into a ring of swizzled Q stages
+//   warps 0..3  gather the query rows by token id with 16-byte async copies into a ring of swizzled Q stages
 //               (TMA gather4 was measured at ~70 cycles per 512-byte instruction: too slow);
 //   warp 4      one elected thread issues tcgen05.mma S = Q K^T into one of two TMEM S buffers;
 //   warp 5      one elected thread issues O = P V (P read from TMEM, V MN-major from smem) into one
@@ -13,9 +12,13 @@
 //   warps 6..13 two softmax groups, each owning every other tile: one thread per row, row
 //               max / exp2 / row sum from TMEM, P written back to TMEM over S (16-bit), then the
 //               epilogue: O / l rounded to the input dtype, staged in swizzled smem and written
-//               with TMA tile stores (one per warp and 64-column slab).
-// Partials are stored in TILE ORDER (contiguous 128-row slabs) with their (m, l) statistics;
-// no atomics, no cross-block state.
+//               with TMA tile stores (one per warp and 64-column slab);
+//   warp 14     prepares the tokens of the tile rows up to four tiles ahead (the gather warps then issue
+//               no global load of their own);
+//   warp 15     loads the K/V blocks by tiled TMA (128-byte swizzle, double-buffered).
+// Partial rows are stored in TILE ORDER (contiguous 128-row slabs); their (m, l) statistics go to
+// ml[(query head, token, slot)] so that the merge reads a token's pairs as one line.  No atomics, no
+// cross-block state.
 //
 // Reduce kernel (replaces reduce_kernel, :139-281): one warp per (token, head) looks up the
 // <= T partial rows through the `pos` map and merges them:  M = max m_s,
@@ -37,7 +40,7 @@ struct SelFwdParams {
     SelBounds bd;            // visible K/V rows per token
     int dbg;                 // debug builds only: bit 0 skip Q copies, bit 1 skip partial stores
     ET* opart;               // [max_tiles * 128, D]  unnormalised partial outputs, tile order
-    float2* ml;              // [max_tiles * 128]     (row max in log2 units, row sum)
+    float2* ml;              // [Hq, N, T] (fits in max_tiles * 128 pairs): row max in log2 units, row sum
 };
 
 __host__ __device__ constexpr uint32_t tmem_cols_pow2(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }

@@ -23,7 +23,7 @@ struct SelFwdArgs {
     float sm_scale;
     int run;                  // tiles per scheduling run; 0 = default
     void* opart;              // [max_tiles * 128, D] input dtype
-    float2* ml;               // [max_tiles * 128]
+    float2* ml;               // [Hq, N, T] statistics (capacity max_tiles * 128 pairs)
     void* o;
     int64_t o_sn, o_sh;
     float* lse;
