@@ -396,8 +396,17 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
         const bool row_exists = g < s.G;
         uint32_t entA = 0xFFFFFFFFu, entB = 0xFFFFFFFFu;
         int row0A = 0, row0B = 0, cloA = 0, chiA = BK, hA = 0, hB = 0;
-        auto fetch_ent = [&](int k, uint32_t& ent, int& row0, int& h) {
-            const int j = sched.tile(k);
+        // tile indices of this group's tiles k, k + 2, k + 4 without a division per tile: a cursor (run index, offset
+        // in the run) that advances by two
+        int cq = sb / sched.run, cr = sb % sched.run;
+        auto cursor_next = [&]() {
+            const int j = (cq * sched.grid + sched.cta) * sched.run + cr;
+            cr += 2;
+            while (cr >= sched.run) { cr -= sched.run; ++cq; }
+            return j;
+        };
+        int jA = 0, jB = 0;
+        auto fetch_ent = [&](int j, uint32_t& ent, int& row0, int& h) {
             const TileInfo ti = load_tile(p.ix, j);
             row0 = ti.row0; h = ti.h;
             ent = 0xFFFFFFFFu;
@@ -461,22 +470,29 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             if (quarter == 2 && lane == 0) TR(3, prev_u * 2 + sb, 3);
         };
         if (sb < nloc) {
-            fetch_ent(sb, entA, row0A, hA);
+            jA = cursor_next();
+            fetch_ent(jA, entA, row0A, hA);
             fetch_bounds(entA, row0A, cloA, chiA);
         }
-        if (sb + 2 < nloc) fetch_ent(sb + 2, entB, row0B, hB);
+        if (sb + 2 < nloc) {
+            jB = cursor_next();
+            fetch_ent(jB, entB, row0B, hB);
+        }
         for (int k = sb; k < nloc && ok; k += 2) {
-            const int j = sched.tile(k);
+            const int j = jA;
             const int u = k >> 1;                     // use count of this group's O buffer
             const int sbuf = k % C::NS;
             const uint32_t tS = tS0 + sbuf * BK;
             const bool row_valid = entA != 0xFFFFFFFFu;
             const int c_lo = cloA, c_hi = chiA;            // visible key columns of this row
             const int64_t mli = row_valid ? ml_index(entA, hA) : 0;
-            entA = entB; row0A = row0B; hA = hB;
+            entA = entB; row0A = row0B; hA = hB; jA = jB;
             T_TIC;
             if (k + 2 < nloc) fetch_bounds(entA, row0A, cloA, chiA);
-            if (k + 4 < nloc) fetch_ent(k + 4, entB, row0B, hB);
+            if (k + 4 < nloc) {
+                jB = cursor_next();
+                fetch_ent(jB, entB, row0B, hB);
+            }
             T_TOC(0);
             ok = mbar_wait(&s_full[sbuf], (k / C::NS) & 1, status) && ok;
             T_TOC(1);
