@@ -290,8 +290,8 @@ def run_decode(args, rank, world, local_rank):
         n_loc = max(min(n_cmp, shard.cmp_hi) - shard.cmp_lo, 0)
         lo = cache.cmp_row0.view(B, 1, 1).expand(B, Hk, 1).contiguous()
         hi = (lo + n_loc).contiguous()
-        nchunk = max(-(-n_loc // 512), 1)
-        cmp_pass = lambda: ops.attn_partial(qd, cache.cmp_k, cache.cmp_v, lo, hi, 512, nchunk, d ** -0.5, want_scores=True)  # noqa: E731
+        nchunk = max(-(-n_loc // 1024), 1)
+        cmp_pass = lambda: ops.attn_partial(qd, cache.cmp_k, cache.cmp_v, lo, hi, 1024, nchunk, d ** -0.5, want_scores=True)  # noqa: E731
         for _ in range(3):
             cmp_pass()
         torch.cuda.synchronize()

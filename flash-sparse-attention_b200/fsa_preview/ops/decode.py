@@ -181,7 +181,7 @@ class DecodeStepPlan:
     collectives, so it can be captured in a CUDA graph of its own while the two collectives stay ordinary launches."""
 
     def __init__(self, *, kernel_size, kernel_stride, block_size, topk, init_blocks, local_blocks, window_size, max_len,
-                 sm_scale=None, shard: Optional[Shard] = None, ops=None, cmp_chunk: int = 512):
+                 sm_scale=None, shard: Optional[Shard] = None, ops=None, cmp_chunk: int = 1024):
         self.ks, self.stride, self.bs, self.topk = kernel_size, kernel_stride, block_size, topk
         self.init_blocks, self.local_blocks, self.window, self.max_len = init_blocks, local_blocks, window_size, max_len
         self.sm_scale, self.shard, self.ops, self.cmp_chunk = sm_scale, shard or Shard(), ops or CudaDecodeOps(), cmp_chunk
@@ -260,7 +260,7 @@ def nsa_decode_attention(
     cmp_row0: torch.Tensor,          # [B] int32: compressed-cache row of compressed token shard.cmp_lo
     *, kernel_size: int, kernel_stride: int, block_size: int, topk: int, init_blocks: int, local_blocks: int,
     window_size: int, max_len: int, sm_scale: Optional[float] = None, shard: Optional[Shard] = None, ops=None,
-    cmp_chunk: int = 512,
+    cmp_chunk: int = 1024,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """The three NSA branches for ONE new token per sequence; the token is the last of its sequence and gets
     what the prefill path gives that row.  Returns (o_cmp, o_sel, o_win [B,Hq,D], lse_cmp, lse_sel, lse_win
