@@ -152,6 +152,24 @@ def test_select_topk_and_ranges_bit_exact():
         assert torch.equal(gl.cpu(), rl) and torch.equal(gh.cpu(), rh)
 
 
+@pytest.mark.parametrize("max_len", [400, 40000, 131136, 160000])
+def test_select_topk_long_rows_bit_exact(max_len):
+    """Rows of up to 2500 candidate blocks (the benchmark's cache length and beyond) against the oracle on identical
+    scores."""
+    torch.manual_seed(max_len)
+    B, Hk, G, ks, st, BK, T = 2, 1, 2, 32, 16, 64, 16
+    seq_len = torch.tensor([max_len, max(max_len // 3, 33)], dtype=torch.int32)
+    ncmp = torch.clamp((seq_len - ks) // st + 1, min=0).to(torch.int32)
+    ld = int(ncmp.max()) + 5
+    scores = torch.randn(B, Hk, ld) * 2
+    lse = torch.full((B, Hk * G), 8.0)
+    max_blocks = -(-max_len // BK)
+    ref = OracleDecodeOps().select_topk(scores, ld, ld, 0, lse, seq_len, ncmp, Hk, ks, st, BK, 1, 2, T, max_blocks)
+    got = CudaDecodeOps().select_topk(scores.to(DEV), ld, ld, 0, lse.to(DEV), seq_len.to(DEV), ncmp.to(DEV), Hk, ks, st, BK, 1, 2, T,
+                                      max_blocks)
+    assert torch.equal(got.cpu(), ref)
+
+
 CFG = dict(kernel_size=32, kernel_stride=16, block_size=64, topk=4, init_blocks=1, local_blocks=2, window_size=100)
 
 
