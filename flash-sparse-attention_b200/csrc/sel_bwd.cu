@@ -484,7 +484,10 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.s = s; p.ix = ix; p.nsub = nsub; p.bd = a.bd;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
-    if (D == 128 && s.BK <= kKT && !a.force_simple && a.dqmap) {
+    // the gather warps of the pipelined kernel address rows by 32-bit offsets in units of 8 elements
+    const bool offsets_fit = ((s.N * a.q_sn + (int64_t)s.Hq * a.q_sh) >> 3) < 0x7fffffffll &&
+                             ((s.N * a.do_sn + (int64_t)s.Hq * a.do_sh) >> 3) < 0x7fffffffll;
+    if (D == 128 && s.BK <= kKT && !a.force_simple && a.dqmap && offsets_fit) {
         e = launch_sel_bwd_pipe(ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16, a, s, ix, kmap, vmap, *a.dqmap, num_sms, stream);
         if (e != cudaSuccess) return e;
     } else {

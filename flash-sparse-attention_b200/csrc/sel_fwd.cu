@@ -904,7 +904,9 @@ static cudaError_t launch_sel_fwd(const SelFwdArgs& a, const SelShape& s, const 
 #endif
     cudaError_t e;
     constexpr bool kPipelined = (D <= 128 && BK <= 128);
-    if (kPipelined && a.omap) {
+    // the gather warps of the pipelined kernel address rows by 32-bit offsets in units of 8 elements
+    const bool offsets_fit = ((s.N * a.q_sn + (int64_t)s.Hq * a.q_sh) >> 3) < 0x7fffffffll;
+    if (kPipelined && a.omap && offsets_fit) {
         if constexpr (kPipelined) {
             auto kern = sel_fwd_main<D, BK, ET>;
             constexpr int smem = SelFwdCfg<D, BK>::kBytes;
