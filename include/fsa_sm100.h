@@ -36,12 +36,14 @@ extern "C" {
 #define FSA_DTYPE_BF16 0
 #define FSA_DTYPE_FP16 1
 
-/* Library version and a human-readable string for an error code. */
+/* Library version and a human-readable string for an error code.  No reference counterpart (the reference raises
+ * Python exceptions). */
 int fsa_version(void);
 const char* fsa_error_string(int code);
-/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread.  No reference
+ * counterpart (diagnostics). */
 int fsa_last_cuda_error(void);
-/* Source line inside the library's API file of that failing call (diagnostics). */
+/* Source line inside the library's API file of that failing call.  No reference counterpart (diagnostics). */
 int fsa_last_cuda_error_line(void);
 
 /* Optional kernel timing for benchmarks (off by default; no counterpart in the reference, which
@@ -112,7 +114,9 @@ int fsa_sel_fwd_static(const void* q, const void* k, const void* v, const int32_
                        int64_t v_stride_n, float sm_scale, void* o, int64_t o_stride_n, int64_t o_stride_h, float* lse,
                        void* stream);
 
-/* Size of the transient backward scratch (dQ partials, fp32 dK/dV accumulators, delta). */
+/* Size of the transient backward scratch (dQ partials, fp32 dK/dV accumulators, delta): the reference's dq buffer
+ * [1, nb-1, max_valid, d] (fsa/ops/FSA_topk_sparse_attention.py:1408-1420), its dk / dv [G, N, Hk, d] staging (:1799-1806)
+ * and delta (:1745). */
 int fsa_sel_bwd_scratch_bytes(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int head_dim,
                               int topk, int block_size, int64_t* bytes_out);
 
@@ -219,8 +223,9 @@ int fsa_decode_attn_partial(const void* q, const void* k, const void* v, int64_t
 int fsa_decode_read_status(int* status_out);
 
 /* Log-sum-exp merge of P partials per row: o = sum w_p o_p / sum w_p l_p, w_p = exp2(m_p - max m), lse = max m +
- * log2 sum w_p l_p.  Used inside one GPU (chunks, blocks) and across GPUs (after an all-gather of the partials;
- * the reference has no multi-GPU path).  Row r reads partials o_part[(r * part_stride + p) * head_dim ...] and
+ * log2 sum w_p l_p: the online-softmax merge of the reference's reduce kernel (fsa/ops/FSA_topk_sparse_attention.py:
+ * 139-281) as a stand-alone operator.  Used inside one GPU (chunks, blocks) and across GPUs (after an all-gather of the
+ * partials; the reference has no multi-GPU path).  Row r reads partials o_part[(r * part_stride + p) * head_dim ...] and
  * ml[(r * part_stride + p) * 2 ...], p < num_partials, so a sub-range of a wider partial buffer can be merged in
  * place (offset the pointers).  out_dtype: 0 bf16, 1 fp16, 2 fp32; lse may be null. */
 int fsa_lse_merge(const float* o_part, const float* ml, int64_t rows, int num_partials, int part_stride, int head_dim,
@@ -263,12 +268,14 @@ int fsa_decode_ranges(const int32_t* topk_idx, const int32_t* seq_len, const int
                       int topk, int block_size, int window, int piece, int num_window_pieces, int shard_lo, int shard_hi,
                       int32_t* rng_lo, int32_t* rng_hi, void* stream);
 
-/* Copy the device status word of an index workspace to the host (synchronises `stream`).
+/* Copy the device status word of an index workspace to the host (synchronises `stream`).  No reference counterpart
+ * (the reference's kernels have no bounded waits to report).
  * *status_out: 0 ok, 1 a bounded wait ran out, 2 an out-of-table index was skipped.
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
 int fsa_read_status(const void* index_ws, void* stream, int* status_out);
 
-/* Debug/inspection: copy the block->entries structure built by the forward to host arrays.
+/* Debug/inspection: copy the block->entries structure built by the forward to host arrays (what the reference
+ * keeps as valid_lens / valid_start_indices / the flat token list, fsa/ops/FSA_topk_sparse_attention.py:60-135).
  * With nbmax = total_tokens / block_size + batch + 1 and tpt = (128 / group) & ~3:
  *   counts_host [Hk * nbmax] entries per (kv head, block); row0_host [nbmax] first K/V row of a block;
  *   tile_off_host [Hk * nbmax + 1] first tile of every (kv head, block);
