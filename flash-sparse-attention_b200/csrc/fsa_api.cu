@@ -393,8 +393,17 @@ int fsa_range_attn_bytes(int64_t N, int64_t Nk, int B, int Hq, int Hk, int D, in
     return FSA_OK;
 }
 
+static int sel_static_base(void** out);
+
 int fsa_read_status(const void* index_ws, void* stream_, int* status_out) {
-    if (!index_ws || !status_out) return FSA_ERR_BAD_ARG;
+    if (!status_out) return FSA_ERR_BAD_ARG;
+    if (!index_ws) {
+        // the status word of fsa_sel_fwd_static lives at the start of the library's built-in array
+        void* base = nullptr;
+        int rc = sel_static_base(&base);
+        if (rc) return rc;
+        index_ws = base;
+    }
     cudaStream_t stream = (cudaStream_t)stream_;
     int st = 0;
     cudaError_t e = cudaMemcpyAsync(&st, index_ws, sizeof(int), cudaMemcpyDeviceToHost, stream);
@@ -466,7 +475,8 @@ int fsa_sel_fwd_static(const void* q, const void* k, const void* v, const int32_
     int rc = make_shape(N, B, Hq, Hk, D, T, BK, &s);
     if (rc) return rc;
     if (D == 0) return FSA_ERR_BAD_ARG;
-    // layout inside the static array: [index workspace | forward scratch], each 1024-byte aligned
+    // layout inside the static array: [index workspace | forward scratch]; the array is 256-byte aligned and the
+    // index workspace is rounded up to 1 KiB, so both regions start 256-byte aligned (all the kernels need)
     const int64_t index_bytes = align_up(sel_index_bytes(s), 1024);
     const int64_t scratch_bytes = fwd_scratch_bytes(s);
     if (index_bytes + scratch_bytes > (int64_t)FSA_SEL_STATIC_SCRATCH_BYTES) return FSA_ERR_STATIC_LIMIT;

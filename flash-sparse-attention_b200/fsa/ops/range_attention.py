@@ -94,6 +94,12 @@ def range_attention(q, k, v, cu_q, cu_k, kv_lo, kv_hi, max_blocks, sm_scale=None
     """``o, lse``: token n attends K/V rows ``kv_lo[n]..kv_hi[n]`` (global rows; ``kv_lo`` may be None)."""
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    if k.shape[0] == 0:
+        # no K/V row exists (e.g. every sequence is shorter than the compression window): every query sees
+        # nothing, which the reference defines as o = 0, lse = -inf (nsa_ref/ops/compressed_attention.py:548-553)
+        assert q.is_cuda, "the sm_100a kernels need CUDA tensors (no CPU fallback)"
+        lse = torch.full((q.shape[1], q.shape[0]), float("-inf"), dtype=torch.float32, device=q.device)
+        return q * 0, lse
     return RangeAttention.apply(q, k, v, cu_q, cu_k, kv_lo, kv_hi, int(max_blocks), float(sm_scale))
 
 

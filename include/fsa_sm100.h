@@ -105,6 +105,8 @@ int fsa_sel_fwd(const void* q, const void* k, const void* v, const int32_t* topk
  *     that must start at zero are cleared on `stream` by the call itself, but two calls that may
  *     overlap on the GPU (different streams, no ordering between them) race on the array and must be
  *     serialised by the caller;
+ *   - device-side failures (a bounded wait that ran out) are recorded in a status word inside the array:
+ *     read it with fsa_read_status(NULL, stream, &status), which allocates nothing either;
  *   - there is no workspace to keep for a backward pass: fsa_sel_bwd needs the caller-owned index
  *     workspace of fsa_sel_fwd. */
 #define FSA_SEL_STATIC_SCRATCH_BYTES (64u << 20)
@@ -269,7 +271,8 @@ int fsa_decode_ranges(const int32_t* topk_idx, const int32_t* seq_len, const int
                       int32_t* rng_lo, int32_t* rng_hi, void* stream);
 
 /* Copy the device status word of an index workspace to the host (synchronises `stream`).  No reference counterpart
- * (the reference's kernels have no bounded waits to report).
+ * (the reference's kernels have no bounded waits to report).  index_ws = NULL reads the status word of the built-in
+ * array that fsa_sel_fwd_static works in (on the current device; nothing is allocated).
  * *status_out: 0 ok, 1 a bounded wait ran out, 2 an out-of-table index was skipped.
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
 int fsa_read_status(const void* index_ws, void* stream, int* status_out);

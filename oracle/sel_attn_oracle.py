@@ -162,6 +162,78 @@ def sel_attn_forward_backward(q, k, v, do, topk_idx, block_size, cu_seqlens, sm_
     return o.detach(), lse.detach(), dq, dk, dv
 
 
+def sel_attn_forward_backward_chunked(q, k, v, do, topk_idx, block_size, cu_seqlens, sm_scale=None, token_chunk=512):
+    """The same forward + gradients for problems whose autograd graph would not fit in memory:
+    one graph per chunk of query tokens (rows of the softmax are independent, so dq comes out
+    per chunk and dk / dv are sums over chunks).  Single sequence per call keeps it simple:
+    ``cu_seqlens`` must be ``[0, N]``.  Returns ``(o, lse, dq, dk, dv)`` in fp32."""
+    N, Hq, d = q.shape
+    assert cu_seqlens.tolist() == [0, N], "one sequence per call"
+    kf = k.detach().float()
+    vf = v.detach().float()
+    dk = torch.zeros_like(kf)
+    dv = torch.zeros_like(vf)
+    o_parts, lse_parts, dq_parts = [], [], []
+    for c0 in range(0, N, token_chunk):
+        c1 = min(N, c0 + token_chunk)
+        # keys a chunk can see end at its last token: the prefix [0, c1) is a complete problem for these rows
+        qc = q[c0:c1].detach().float().requires_grad_(True)
+        kc = kf[:c1].clone().requires_grad_(True)
+        vc = vf[:c1].clone().requires_grad_(True)
+        o_c, lse_c = sel_attn_forward_rows(qc, kc, vc, topk_idx[:, :c1], block_size, c0, c1, sm_scale)
+        gq, gk, gv = torch.autograd.grad(o_c, (qc, kc, vc), do[c0:c1].float())
+        o_parts.append(o_c.detach())
+        lse_parts.append(lse_c.detach())
+        dq_parts.append(gq)
+        dk[:c1] += gk
+        dv[:c1] += gv
+    return torch.cat(o_parts, 0), torch.cat(lse_parts, 1), torch.cat(dq_parts, 0), dk, dv
+
+
+def sel_attn_forward_rows(q_rows, kf, vf, topk_idx, block_size, c0, c1, sm_scale):
+    """Rows [c0, c1) of a single sequence: ``q_rows [c1-c0, Hq, d]`` are those rows' queries, ``kf``/``vf`` the
+    sequence's K/V (at least the prefix [0, c1)); same rules as ``sel_attn_forward``.  Returns
+    ``(o [C,Hq,d], lse [Hq,C])``."""
+    Lk, Hk, d = kf.shape
+    Hq = q_rows.shape[1]
+    G = Hq // Hk
+    T = topk_idx.shape[-1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    nb = (Lk + block_size - 1) // block_size
+    pad = nb * block_size - Lk
+    if pad:
+        kf = torch.cat([kf, kf.new_zeros(pad, Hk, d)], 0)
+        vf = torch.cat([vf, vf.new_zeros(pad, Hk, d)], 0)
+    kb = kf.view(nb, block_size, Hk, d)
+    vb = vf.view(nb, block_size, Hk, d)
+    C = c1 - c0
+    t_loc = torch.arange(c0, c1)
+    idx = topk_idx[:, c0:c1].long()
+    lim = (t_loc // block_size).view(1, C, 1)
+    valid = (idx >= 0) & (idx <= lim)
+    use = torch.arange(T).view(1, 1, T) < valid.sum(-1, keepdim=True)
+    blk = idx.clamp(min=0, max=nb - 1)
+    o_heads, lse_heads = [], []
+    for h in range(Hk):
+        kg = kb[blk[h], :, h]
+        vg = vb[blk[h], :, h]
+        qh = q_rows[:, h * G : (h + 1) * G]
+        logits = torch.einsum("cgd,ctjd->cgtj", qh, kg) * (sm_scale * LOG2E)
+        key_pos = blk[h].unsqueeze(-1) * block_size + torch.arange(block_size).view(1, 1, -1)
+        ok = use[h].unsqueeze(-1) & (key_pos <= t_loc.view(C, 1, 1))
+        logits = logits.masked_fill(~ok.unsqueeze(1), float("-inf"))
+        flat = logits.reshape(C, G, T * block_size)
+        m = flat.max(-1, keepdim=True).values
+        m_safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+        p = torch.exp2(flat - m_safe)
+        l = p.sum(-1, keepdim=True)
+        lse_heads.append((m_safe + torch.log2(l)).squeeze(-1))
+        oh = torch.einsum("cgx,cxd->cgd", p, vg.reshape(C, T * block_size, d))
+        o_heads.append(oh / torch.where(l > 0, l, torch.ones_like(l)))
+    return torch.cat(o_heads, 1), torch.cat(lse_heads, 1).transpose(0, 1)
+
+
 def attended_key_count(topk_idx: torch.Tensor, cu_seqlens: torch.Tensor, block_size: int, group: int) -> int:
     """P = number of (query head, token, key) triples actually attended: the figure the
     effective-FLOP count is built on (forward 4*d*P, backward 10*d*P)."""

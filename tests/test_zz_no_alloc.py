@@ -10,6 +10,8 @@ entry point, which works in caller-owned workspaces.  It also checks the size li
 The file sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
 """
+from ctypes import byref, c_int
+
 import pytest
 import torch
 
@@ -22,12 +24,12 @@ from fsa.synthetic import make_cu_seqlens, make_qkv, make_topk_idx
 DEV = "cuda:0"
 
 
-def _static_fwd(q, k, v, idx, bs, cu, scale):
+def _static_fwd(q, k, v, idx, bs, cu, scale, o=None, lse=None):
     L = _lib.lib()
     N, Hq, D = q.shape
     Hk, T, B = k.shape[1], idx.shape[-1], cu.numel() - 1
-    o = torch.empty_like(q)
-    lse = torch.empty(Hq, N, dtype=torch.float32, device=q.device)
+    o = torch.empty_like(q) if o is None else o
+    lse = torch.empty(Hq, N, dtype=torch.float32, device=q.device) if lse is None else lse
     rc = L.fsa_sel_fwd_static(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(idx), _lib.ptr(cu), N, B, Hq, Hk, D, T, bs,
         _lib.DTYPE_CODE[q.dtype], q.stride(0), q.stride(1), k.stride(0), v.stride(0), float(scale),
@@ -43,16 +45,34 @@ def _problem(seqlens, Hk, G, d, bs, T, seed):
     return [x.to(DEV) for x in (q, k, v, idx, cu)]
 
 
+def _static_status():
+    st = c_int(-1)
+    rc = _lib.lib().fsa_read_status(None, _lib.current_stream(torch.device(DEV)), byref(st))
+    return rc, st.value
+
+
 def test_static_forward_matches_workspace_forward_twice():
     with torch.cuda.device(DEV):
-        # a larger problem first, then a smaller, differently shaped one that reuses the same array
-        for seqlens, Hk, G, d, bs, T, seed in (([1500, 548], 2, 2, 128, 64, 8, 21), ([300, 212], 1, 4, 128, 64, 16, 22)):
+        # differently shaped problems back to back in the one shared array: a large one, a small one with another
+        # head layout (its words land where the first left tile records, entries and positions), then the large one
+        # again -- every call must be independent of what the previous one left behind
+        shapes = (([1500, 548], 2, 2, 128, 64, 8, 21), ([300, 212], 1, 4, 128, 64, 16, 22), ([1500, 548], 2, 2, 128, 64, 8, 21))
+        for i, (seqlens, Hk, G, d, bs, T, seed) in enumerate(shapes):
             q, k, v, idx, cu = _problem(seqlens, Hk, G, d, bs, T, seed)
             scale = d ** -0.5
             o_ref, lse_ref, _ = sel_attn_fwd(q, k, v, idx, bs, cu, scale, check_status=True)
-            rc, o, lse = _static_fwd(q, k, v, idx, bs, cu, scale)
-            assert rc == 0, _lib.lib().fsa_error_string(rc)
+            o = torch.empty_like(q)
+            lse = torch.empty(q.shape[1], q.shape[0], dtype=torch.float32, device=q.device)
             torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            rc, o, lse = _static_fwd(q, k, v, idx, bs, cu, scale, o, lse)
+            assert rc == 0, _lib.lib().fsa_error_string(rc)
+            rc, st = _static_status()          # synchronises the stream
+            assert rc == 0 and st == 0, f"device status {st}"
+            if i > 0:
+                # outputs were allocated before the reading and the first call has loaded every kernel: a call that
+                # allocates nothing leaves the device's free memory where it was
+                assert torch.cuda.mem_get_info()[0] == free_before
             assert float((o.float() - o_ref.float()).abs().max()) <= 2e-2
             assert float((lse - lse_ref).abs().max()) <= 1e-4
 
