@@ -48,197 +48,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One CTA = one chunk of one range of one (sequence, kv head); its 4 warps take the chunk's 16-key tiles round-robin.
-// Per tile a warp computes S = Q K^T (rows = the group's heads padded to 16, 8 keys per MMA) straight from 16-byte
-// global loads: the contraction index may be permuted freely, so the 8 consecutive head_dim elements a thread loads
-// of a key row serve as the (k, k+1, k+8, k+9) slots of two MMA k-steps, and Q is held in registers in the same
-// order.  P (rounded to the input type) is re-used in registers as the A operand of O += P V; the B operand pairs two
-// key rows per register, built with byte permutes from four 16-byte loads, and the 8 output columns of MMA i are the
-// head_dim columns {8 n + i}.  Online softmax per warp, warps merged through shared memory at the end.
-// HI: the group has more than 8 heads (rows 8..15 of the tiles are live).
-template <int D, bool HI, typename ET>
-__global__ void __launch_bounds__(128) decode_partial_kernel(const DecodeParams p) {
-    extern __shared__ float dsm[];
-    constexpr int NJ = D / 32;             // 16-byte K loads per key row and thread
-    constexpr int NS = D / 64;             // 64-column steps of the PV product
-    constexpr int NT = NS * 8;             // PV accumulator tiles
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int gid = lane >> 2, tig = lane & 3;
-    const int G = p.Hq / p.Hk;
-    const int c = blockIdx.x % p.nchunk;
-    const int r = (blockIdx.x / p.nchunk) % p.R;
-    const int h = (blockIdx.x / (p.nchunk * p.R)) % p.Hk;
-    const int b = blockIdx.x / (p.nchunk * p.R * p.Hk);
-    const int P = p.R * p.nchunk, pidx = r * p.nchunk + c;
-    const int lo_r = p.rng_lo[((int64_t)b * p.Hk + h) * p.R + r];
-    const int hi_r = p.rng_hi[((int64_t)b * p.Hk + h) * p.R + r];
-    const int lo = lo_r + c * p.chunk;
-    const int hi = min(hi_r, lo + p.chunk);
-    const int64_t pbase = ((int64_t)b * p.Hq + h * G) * P + pidx;     // + g * P
-    if (lo_r < 0 || lo >= hi) {
-        if (tid < G) p.ml[pbase + (int64_t)tid * P] = make_float2(-INFINITY, 0.f);
-        return;
-    }
-    const int n = hi - lo;
-    const ET* kbase = (const ET*)p.k + (int64_t)lo * p.kv_sn + h * D;
-    const ET* vbase = (const ET*)p.v + (int64_t)lo * p.kv_sn + h * D;
-    // Q fragments: row gid (and gid + 8), this thread's 8 elements of every 32-element group
-    uint4 qa[NJ], qb[NJ];
-    {
-        const ET* q = (const ET*)p.q + ((int64_t)b * p.Hq + h * G) * D;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            qa[j] = gid < G ? *reinterpret_cast<const uint4*>(q + gid * D + j * 32 + tig * 8) : make_uint4(0, 0, 0, 0);
-            qb[j] = (HI && gid + 8 < G) ? *reinterpret_cast<const uint4*>(q + (gid + 8) * D + j * 32 + tig * 8) : make_uint4(0, 0, 0, 0);
-        }
-    }
-    float acc[NT][4];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows gid and gid + 8
-    const bool want_scores = p.scores != nullptr && r == 0 && gid == 0;
-    float* srow = want_scores ? p.scores + ((int64_t)b * p.Hk + h) * p.scores_ld + (lo - lo_r) : nullptr;
-
-    for (int k0 = warp * 16; k0 < n; k0 += 64) {
-        // ---- loads of the tile (rows past the end re-read the last row; their logits are masked)
-        uint4 kf[2][NJ], vf[NS][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const int key = min(k0 + nt * 8 + gid, n - 1);
-#pragma unroll
-            for (int j = 0; j < NJ; ++j) kf[nt][j] = *reinterpret_cast<const uint4*>(kbase + (int64_t)key * p.kv_sn + j * 32 + tig * 8);
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-            const int key = min(k0 + tig * 2 + (q4 & 1) + (q4 >> 1) * 8, n - 1);
-#pragma unroll
-            for (int s = 0; s < NS; ++s) vf[s][q4] = *reinterpret_cast<const uint4*>(vbase + (int64_t)key * p.kv_sn + s * 64 + gid * 8);
-        }
-        // ---- S = Q K^T
-        float sc[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-#pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                mma16816<ET>(sc[nt], qa[j].x, qb[j].x, qa[j].y, qb[j].y, kf[nt][j].x, kf[nt][j].y);
-                mma16816<ET>(sc[nt], qa[j].z, qb[j].z, qa[j].w, qb[j].w, kf[nt][j].z, kf[nt][j].w);
-            }
-        }
-        // ---- scale, mask, running max
-        float tmax0 = -INFINITY, tmax1 = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = k0 + nt * 8 + tig * 2 + e;
-                const bool ok = key < n;
-                sc[nt][e] = ok ? sc[nt][e] * p.scale_log2 : -INFINITY;
-                sc[nt][2 + e] = ok ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
-                if (want_scores && ok) srow[key] = sc[nt][e];
-                tmax0 = fmaxf(tmax0, sc[nt][e]);
-                tmax1 = fmaxf(tmax1, sc[nt][2 + e]);
-            }
-        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
-        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
-        if (HI) {
-            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
-            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
-        }
-        const float mn0 = fmaxf(m0, tmax0), mn1 = HI ? fmaxf(m1, tmax1) : m1;      // finite: key k0 of the tile is valid
-        if (__any_sync(0xffffffffu, mn0 > m0 || (HI && mn1 > m1))) {
-            const float a0 = exp2f(m0 - mn0), a1 = HI ? exp2f(m1 - mn1) : 1.f;   // exp2(-inf) = 0 on the first tile
-            l0 *= a0;
-            l1 *= a1;
-#pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                acc[i][0] *= a0; acc[i][1] *= a0;
-                if (HI) { acc[i][2] *= a1; acc[i][3] *= a1; }
-            }
-            m0 = mn0;
-            m1 = mn1;
-        }
-        // ---- P (rounded to the input type; the sums use the rounded values' fp32 originals as the prefill kernels do)
-        uint32_t pa[4];
-        {
-            float e00 = exp2f(sc[0][0] - m0), e01 = exp2f(sc[0][1] - m0), e10 = exp2f(sc[1][0] - m0), e11 = exp2f(sc[1][1] - m0);
-            l0 += e00 + e01 + e10 + e11;
-            pa[0] = ElemTraits<ET>::pack2(e00, e01);
-            pa[2] = ElemTraits<ET>::pack2(e10, e11);
-            if (HI) {
-                float f00 = exp2f(sc[0][2] - m1), f01 = exp2f(sc[0][3] - m1), f10 = exp2f(sc[1][2] - m1), f11 = exp2f(sc[1][3] - m1);
-                l1 += f00 + f01 + f10 + f11;
-                pa[1] = ElemTraits<ET>::pack2(f00, f01);
-                pa[3] = ElemTraits<ET>::pack2(f10, f11);
-            } else {
-                pa[1] = pa[3] = 0u;
-            }
-        }
-        // ---- O += P V
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const uint32_t* r0 = &vf[s][0].x;
-            const uint32_t* r1 = &vf[s][1].x;
-            const uint32_t* r2 = &vf[s][2].x;
-            const uint32_t* r3 = &vf[s][3].x;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                mma16816<ET>(acc[s * 8 + 2 * w], pa[0], pa[1], pa[2], pa[3], __byte_perm(r0[w], r1[w], 0x5410), __byte_perm(r2[w], r3[w], 0x5410));
-                mma16816<ET>(acc[s * 8 + 2 * w + 1], pa[0], pa[1], pa[2], pa[3], __byte_perm(r0[w], r1[w], 0x7632), __byte_perm(r2[w], r3[w], 0x7632));
-            }
-        }
-    }
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    // ---- merge the four warps: so [4][G][D], sm [4][G], sl [4][G]
-    float* so = dsm;
-    float* smm = so + 4 * G * D;
-    float* sll = smm + 4 * G;
-#pragma unroll
-    for (int half = 0; half < (HI ? 2 : 1); ++half) {
-        const int g = gid + half * 8;
-        if (g < G) {
-            float* dst = so + ((size_t)warp * G + g) * D;
-#pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                // tile i = s * 8 + e: columns s * 64 + (tig * 2 + {0, 1}) * 8 + e
-                const int s = i >> 3, e = i & 7;
-                dst[s * 64 + (tig * 2) * 8 + e] = acc[i][half * 2];
-                dst[s * 64 + (tig * 2 + 1) * 8 + e] = acc[i][half * 2 + 1];
-            }
-            if (tig == 0) {
-                smm[warp * G + g] = half ? m1 : m0;
-                sll[warp * G + g] = half ? l1 : l0;
-            }
-        }
-    }
-    __syncthreads();
-    for (int i = tid; i < G * D; i += 128) {
-        const int g = i / D;
-        float M = fmaxf(fmaxf(smm[g], smm[G + g]), fmaxf(smm[2 * G + g], smm[3 * G + g]));
-        float o = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = smm[w * G + g];
-            if (mw > -INFINITY) o += exp2f(mw - M) * so[(size_t)w * G * D + i];
-        }
-        p.o_part[(pbase + (int64_t)g * P) * D + (i - g * D)] = o;
-    }
-    if (tid < G) {
-        const int g = tid;
-        float M = fmaxf(fmaxf(smm[g], smm[G + g]), fmaxf(smm[2 * G + g], smm[3 * G + g]));
-        float L = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = smm[w * G + g];
-            if (mw > -INFINITY) L += exp2f(mw - M) * sll[w * G + g];
-        }
-        p.ml[pbase + (int64_t)g * P] = make_float2(M, L);
-    }
-}
-
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
@@ -755,14 +564,6 @@ __global__ void decode_cmp_ranges_kernel(const int* __restrict__ seq_len, const 
 }
 
 template <int D, bool HI, typename ET>
-static cudaError_t launch_partial(int G, const DecodeParams& p, cudaStream_t stream) {
-    size_t smem = (size_t)(4 * G * D + 8 * G) * sizeof(float);
-    auto kern = decode_partial_kernel<D, HI, ET>;
-    kern<<<(unsigned)((int64_t)p.B * p.Hk * p.R * p.nchunk), 128, smem, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <int D, bool HI, typename ET>
 static cudaError_t launch_partial_tma(DecodeParams p, const CUtensorMap& kmap, const CUtensorMap& vmap, cudaStream_t stream) {
     constexpr int STAGE_BYTES = 2 * (D / 64) * 64 * 128;
     p.nst = min(max((p.chunk + kDecKT - 1) / kDecKT * p.rpp, 1), 3);
@@ -783,8 +584,7 @@ static cudaError_t launch_partial_tma(DecodeParams p, const CUtensorMap& kmap, c
 template <int D, typename ET>
 static cudaError_t dispatch_g(int G, const DecodeParams& p, const CUtensorMap* kmap, const CUtensorMap* vmap, cudaStream_t stream) {
     if (G < 1 || G > 16) return cudaErrorInvalidValue;
-    if (kmap) return G > 8 ? launch_partial_tma<D, true, ET>(p, *kmap, *vmap, stream) : launch_partial_tma<D, false, ET>(p, *kmap, *vmap, stream);
-    return G > 8 ? launch_partial<D, true, ET>(G, p, stream) : launch_partial<D, false, ET>(G, p, stream);
+    return G > 8 ? launch_partial_tma<D, true, ET>(p, *kmap, *vmap, stream) : launch_partial_tma<D, false, ET>(p, *kmap, *vmap, stream);
 }
 
 }  // namespace fsa
@@ -811,23 +611,18 @@ extern "C" int fsa_decode_attn_partial(const void* q, const void* k, const void*
     if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
     if (head_dim != 128 && head_dim != 64) return FSA_ERR_UNSUPPORTED;
     (void)cudaGetLastError();
-    // K/V rows are streamed by TMA (tensor maps over [kv_rows, Hk * D]); FSA_DECODE_LDG=1 selects the kernel that
-    // loads its fragments straight from global memory instead (kept for comparison).
-    static const bool use_ldg = [] { const char* v = getenv("FSA_DECODE_LDG"); return v && *v == '1'; }();
+    // K/V rows are streamed by TMA (tensor maps over [kv_rows, Hk * D])
     CUtensorMap kmap, vmap;
-    const CUtensorMap *km = nullptr, *vm = nullptr;
-    if (use_ldg && ranges_per_partial != 1) return FSA_ERR_UNSUPPORTED;
-    if (!use_ldg) {
-        if (kv_rows <= 0) return FSA_ERR_BAD_ARG;
+    if (kv_rows <= 0) return FSA_ERR_BAD_ARG;
+    {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return FSA_ERR_CUDA;   // binds the context
         int rc = make_tile_map(&kmap, k, dtype, kv_rows, (int64_t)num_kv_heads * head_dim, kv_stride_n, kDecKT);
         if (rc) return rc;
         rc = make_tile_map(&vmap, v, dtype, kv_rows, (int64_t)num_kv_heads * head_dim, kv_stride_n, kDecKT);
         if (rc) return rc;
-        km = &kmap;
-        vm = &vmap;
     }
+    const CUtensorMap *km = &kmap, *vm = &vmap;
     cudaError_t e = cudaErrorInvalidValue;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == FSA_DTYPE_BF16) {

@@ -122,8 +122,20 @@ static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, Se
     s->N = N; s->Nk = Nk; s->B = B; s->Hq = Hq; s->Hk = Hk; s->G = G; s->D = D; s->T = T; s->BK = BK;
     s->NBmax = (int)(Nk / BK) + B + 1;
     s->TPT = (kTileRows / G) & ~3;
+    // chunk of the index build: at least 1024 tokens, at most 256 chunks
+    int64_t C = 1024;
+    while (C * 256 < N) C *= 2;
+    s->C = (int)C;
+    s->NC = (int)((N + C - 1) / C);
+    if (s->NC < 1) s->NC = 1;
+    // tiles per scheduling run of the backward (FSA_SEL_RUN overrides; read once)
+    static const int env_run = env_int("FSA_SEL_RUN", 0);
+    s->RB = env_run > 0 ? env_run : 32;
     if ((int64_t)s->Hk * s->NBmax >= ((int64_t)1 << 30)) return FSA_ERR_UNSUPPORTED;
-    if ((int64_t)s->Hk * N * T + (int64_t)s->Hk * s->NBmax * kTileRows >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
+    if ((int64_t)s->Hk * s->NBmax * s->NC >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
+    if (Hk > 65535) return FSA_ERR_UNSUPPORTED;
+    if (sel_index_warps(*s) == 0) return FSA_ERR_UNSUPPORTED;                             // a sequence of millions of blocks
+    if (sel_max_tiles(*s) * kTileRows >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;  // partial rows are 32-bit
     return FSA_OK;
 }
 
@@ -131,8 +143,14 @@ static int bwd_nsub(int BK) { return BK > 64 ? BK / 64 : 1; }
 static int64_t bwd_dq_part_bytes(const SelShape& s) {
     return align_up(sel_max_tiles(s) * bwd_nsub(s.BK) * kTileRows * (int64_t)s.D * 2, 1024);
 }
+// fp32 dK / dV accumulators (unpipelined kernel) or per-segment slabs (pipelined kernel): the same region
+static int64_t bwd_dkdv_bytes(const SelShape& s) {
+    const int64_t acc = align_up(2 * s.Nk * s.Hk * (int64_t)s.D * 4, 256);
+    const int64_t slabs = align_up(sel_max_segments(s) * 2 * 64 * (int64_t)s.D * 4, 256);
+    return acc > slabs ? acc : slabs;
+}
 static int64_t bwd_scratch_bytes(const SelShape& s) {
-    return align_up(s.N * s.Hq * 4, 1024) + bwd_dq_part_bytes(s) + align_up(2 * s.Nk * s.Hk * (int64_t)s.D * 4, 256);
+    return align_up(s.N * s.Hq * 4, 1024) + bwd_dq_part_bytes(s) + bwd_dkdv_bytes(s);
 }
 
 static int64_t fwd_scratch_bytes(const SelShape& s) {
@@ -232,7 +250,9 @@ static int sel_fwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const vo
     if (scratch_bytes < fwd_scratch_bytes(s)) return FSA_ERR_WORKSPACE;
 
     SelIndex ix = sel_index_carve(index_ws, s);
+    prof_begin(FSA_KERNEL_SEL_INDEX, stream);
     cudaError_t e = sel_build_index(topk_idx, cu_seqlens, bd, s, ix, index_ws, stream);
+    prof_end(FSA_KERNEL_SEL_INDEX, stream);
     if (e != cudaSuccess) return cuda_fail(e);
 
     CUtensorMap kmap, vmap, omap;
@@ -243,7 +263,8 @@ static int sel_fwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const vo
     const int64_t prow = sel_max_tiles(s) * kTileRows;
     SelFwdArgs a;
     a.q = q; a.q_sn = q_sn; a.q_sh = q_sh; a.sm_scale = sm_scale;
-    a.run = env_int("FSA_SEL_RUN", 0);
+    static const int env_run = env_int("FSA_SEL_RUN", 0);
+    a.run = env_run;
     a.opart = scratch;
     a.ml = (float2*)((char*)scratch + align_up(prow * D * 2, 1024));
     a.o = o; a.o_sn = o_sn; a.o_sh = o_sh; a.lse = lse;
@@ -336,8 +357,7 @@ static int sel_bwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const vo
     a.q = q; a.d_o = d_o; a.o = o;
     a.q_sn = q_sn; a.q_sh = q_sh; a.do_sn = do_sn; a.do_sh = do_sh; a.o_sn = o_sn; a.o_sh = o_sh;
     a.lse = lse; a.topk_idx = topk_idx; a.cu = cu_seqlens; a.sm_scale = sm_scale;
-    a.run = env_int("FSA_SEL_RUN", 0);
-    a.force_simple = env_int("FSA_SEL_BWD_SIMPLE", 0);
+    a.run = s.RB;
     char* sp = (char*)scratch;
     a.delta = (float*)sp;   sp += align_up(N * Hq * 4, 1024);
     a.dq_part = (void*)sp;  sp += bwd_dq_part_bytes(s);
@@ -350,6 +370,7 @@ static int sel_bwd_impl(const SelBounds& bd, int64_t Nk, const void* q, const vo
     }
     a.dk_acc = (float*)sp;
     a.dv_acc = a.dk_acc + Nk * Hk * (int64_t)D;
+    a.slabs = (float*)sp;
     a.bd = bd;
     a.dq = dq; a.dk = dk; a.dv = dv;
     cudaError_t e = dispatch_sel_bwd(dtype, a, s, ix, kmap, vmap, sms, stream);
@@ -414,22 +435,31 @@ int fsa_read_status(const void* index_ws, void* stream_, int* status_out) {
     return st == 0 ? FSA_OK : FSA_ERR_DEVICE_STATUS;
 }
 
+int fsa_sel_index_geometry(int64_t N, int B, int Hq, int Hk, int T, int BK, int64_t* max_tiles_out, int* tpt_out,
+                           int* nbmax_out) {
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, 0, T, BK, &s);
+    if (rc) return rc;
+    if (max_tiles_out) *max_tiles_out = sel_max_tiles(s);
+    if (tpt_out) *tpt_out = s.TPT;
+    if (nbmax_out) *nbmax_out = s.NBmax;
+    return FSA_OK;
+}
+
 int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, int T, int BK, void* stream_,
-                       int32_t* counts_host, int32_t* row0_host, int32_t* tile_off_host, uint32_t* entries_host,
-                       int32_t* header_host) {
+                       int32_t* tile_rec_host, uint32_t* entries_host, int32_t* key_tile_host, int32_t* header_host) {
     cudaStream_t stream = (cudaStream_t)stream_;
     SelShape s;
     int rc = make_shape(N, B, Hq, Hk, 0, T, BK, &s);
     if (rc) return rc;
     if (!index_ws) return FSA_ERR_BAD_ARG;
     SelIndex ix = sel_index_carve(const_cast<void*>(index_ws), s);
-    int64_t HG = (int64_t)s.Hk * s.NBmax;
     cudaError_t e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return cuda_fail(e);
-    if (counts_host && (e = cudaMemcpy(counts_host, ix.counts, HG * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
-    if (row0_host && (e = cudaMemcpy(row0_host, ix.row0, (int64_t)s.NBmax * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
-    if (tile_off_host && (e = cudaMemcpy(tile_off_host, ix.tile_off, (HG + 1) * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
-    if (entries_host && (e = cudaMemcpy(entries_host, ix.entries, sel_max_tiles(s) * s.TPT * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    const int64_t mt = sel_max_tiles(s), HG = (int64_t)s.Hk * s.NBmax;
+    if (tile_rec_host && (e = cudaMemcpy(tile_rec_host, ix.tile_rec, mt * 16, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (entries_host && (e = cudaMemcpy(entries_host, ix.entries, mt * s.TPT * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
+    if (key_tile_host && (e = cudaMemcpy(key_tile_host, ix.key_tile, (HG + 1) * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     if (header_host && (e = cudaMemcpy(header_host, ix.header, 64 * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     return FSA_OK;
 }

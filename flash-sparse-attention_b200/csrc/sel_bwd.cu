@@ -145,9 +145,10 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
         {
             int tl = item / p.nsub;
             if (hg < 0 || tl < hg_first || tl >= hg_first + hg_tiles) {
-                hg = load_tile(p.ix, tl).hg;     // items of one hg span [tile_off[hg], tile_off[hg+1]) * nsub
-                hg_first = p.ix.tile_off[hg];
-                hg_tiles = p.ix.tile_off[hg + 1] - hg_first;
+                hg = load_tile(p.ix, tl).hg;     // items of one key span [first tile, first tile + tiles) * nsub
+                const int2 ax = __ldg(p.ix.tile_aux + tl);
+                hg_first = ax.x;
+                hg_tiles = ax.y;
                 sub = -1;
             }
         }
@@ -155,12 +156,10 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
         const int nsub_i = local / hg_tiles;
         const int tile = local - nsub_i * hg_tiles;
         if (nsub_i != sub) { sub = nsub_i; new_kv = true; }
-        const int h = hg / s.NBmax;
-        const int gb = hg - h * s.NBmax;
-        const int row0 = p.ix.row0[gb] + sub * kKT;
-        const int cnt = p.ix.counts[hg];
-        const int e0 = tile * s.TPT;
-        const int ne = min(s.TPT, cnt - e0);
+        const TileInfo ti = load_tile(p.ix, hg_first + tile);
+        const int h = ti.h;
+        const int row0 = ti.row0 + sub * kKT;
+        const int ne = ti.ne;
         const int64_t ebase = (int64_t)(hg_first + tile) * s.TPT;
 
         // ---- stage 1
@@ -171,7 +170,6 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
             have_acc = false;
         }
         if (tid < s.TPT) s_ent[tid] = tid < ne ? p.ix.entries[ebase + tid] : 0xFFFFFFFFu;
-        (void)e0;
         if (new_kv && tid == 0) {
             mbar_expect_tx(&bar_kv, (uint32_t)(2 * kKT * D * 2));
 #pragma unroll
@@ -448,6 +446,47 @@ __global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const ET* __restrict__ 
     }
 }
 
+// dk / dv of one (kv head, block): the sum, in segment order, of the slabs the pipelined kernel wrote for the block's
+// segments, rounded to the output dtype (replaces the `.sum(0)` over the group's copies of the reference,
+// fsa/ops/FSA_topk_sparse_attention.py:1854-1855).  Thread = head-dim index; blocks nobody selected keep the zeros
+// the caller put there.
+template <typename ET>
+__global__ void __launch_bounds__(128) sel_bwd_dkdv_reduce(const float* __restrict__ slabs, SelShape s, SelIndex ix,
+                                                           ET* __restrict__ dk, ET* __restrict__ dv) {
+    constexpr int D = 128, KT = 64;
+    const int hg = blockIdx.x;
+    if (ix.key_cnt[hg] == 0) return;
+    const int h = hg / s.NBmax, gb = hg - h * s.NBmax;
+    const int row0 = ix.row0[gb];
+    const int seg0 = ix.key_seg[hg], nseg = ix.key_seg[hg + 1] - seg0;
+    const int nkeys = min(KT, ix.nrow[gb]);     // rows past the end of the sequence belong to the next sequence's block
+    const int d = threadIdx.x;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+        const float* src = slabs + (int64_t)seg0 * (2 * KT * D) + which * (KT * D) + d;
+        ET* dst = (which == 0 ? dk : dv) + ((int64_t)row0 * s.Hk + h) * D + d;
+#pragma unroll 1
+        for (int k0 = 0; k0 < nkeys; k0 += 8) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int sg = 0; sg < nseg; ++sg) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = k0 + j < nkeys ? src[(int64_t)sg * (2 * KT * D) + (k0 + j) * D] : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += v[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (k0 + j < nkeys) {
+                    if constexpr (ElemTraits<ET>::kIsBF16) dst[(int64_t)(k0 + j) * s.Hk * D] = __float2bfloat16(acc[j]);
+                    else dst[(int64_t)(k0 + j) * s.Hk * D] = __float2half(acc[j]);
+                }
+        }
+    }
+}
+
 // fp32 accumulators -> output dtype
 template <typename ET>
 __global__ void __launch_bounds__(256) sel_bwd_convert(const float* __restrict__ a, const float* __restrict__ b,
@@ -469,7 +508,19 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     const int nsub = s.BK > kKT ? s.BK / kKT : 1;
     const int64_t rows = s.N * s.Hq;
     const int64_t kv_elems = s.Nk * s.Hk * (int64_t)D;
-    cudaError_t e = cudaMemsetAsync(a.dk_acc, 0, kv_elems * 4 * 2, stream);   // dk_acc and dv_acc are adjacent
+    // the gather warps of the pipelined kernel address rows by 32-bit offsets in units of 8 elements
+    const bool offsets_fit = ((s.N * a.q_sn + (int64_t)s.Hq * a.q_sh) >> 3) < 0x7fffffffll &&
+                             ((s.N * a.do_sn + (int64_t)s.Hq * a.do_sh) >> 3) < 0x7fffffffll;
+    const bool pipelined = D == 128 && s.BK <= kKT && a.dqmap && offsets_fit;
+    cudaError_t e;
+    if (pipelined) {
+        // dk / dv rows of blocks that nobody selected stay zero
+        e = cudaMemsetAsync(a.dk, 0, kv_elems * sizeof(ET), stream);
+        if (e != cudaSuccess) return e;
+        e = cudaMemsetAsync(a.dv, 0, kv_elems * sizeof(ET), stream);
+    } else {
+        e = cudaMemsetAsync(a.dk_acc, 0, kv_elems * 4 * 2, stream);   // dk_acc and dv_acc are adjacent
+    }
     if (e != cudaSuccess) return e;
     if (rows > 0) {
         const int64_t rows_per_cta = 4 * (256 / (D / 8));
@@ -484,10 +535,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.s = s; p.ix = ix; p.nsub = nsub; p.bd = a.bd;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
-    // the gather warps of the pipelined kernel address rows by 32-bit offsets in units of 8 elements
-    const bool offsets_fit = ((s.N * a.q_sn + (int64_t)s.Hq * a.q_sh) >> 3) < 0x7fffffffll &&
-                             ((s.N * a.do_sn + (int64_t)s.Hq * a.do_sh) >> 3) < 0x7fffffffll;
-    if (D == 128 && s.BK <= kKT && !a.force_simple && a.dqmap && offsets_fit) {
+    if (pipelined) {
         e = launch_sel_bwd_pipe(ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16, a, s, ix, kmap, vmap, *a.dqmap, num_sms, stream);
         if (e != cudaSuccess) return e;
     } else {
@@ -512,8 +560,13 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
         prof_end(3, stream);
     }
     if (kv_elems > 0) {
-        int64_t n4 = kv_elems / 4;
-        sel_bwd_convert<ET><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(a.dk_acc, a.dv_acc, (ET*)a.dk, (ET*)a.dv, n4);
+        if (pipelined) {
+            if constexpr (D == 128)
+                sel_bwd_dkdv_reduce<ET><<<(unsigned)(s.Hk * s.NBmax), 128, 0, stream>>>(a.slabs, s, ix, (ET*)a.dk, (ET*)a.dv);
+        } else {
+            int64_t n4 = kv_elems / 4;
+            sel_bwd_convert<ET><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(a.dk_acc, a.dv_acc, (ET*)a.dk, (ET*)a.dv, n4);
+        }
     }
     return cudaGetLastError();
 }

@@ -11,9 +11,10 @@
 //   warp 10      prepares, up to four tiles ahead, the token of every tile row (the gather warps then run without
 //                any global load of their own: a plain load issued behind a burst of async copies waits for it);
 //   warp 11      loads the K/V block of every run of tiles by TMA;
-//   warps 12..15 move the finished dK^T / dV^T accumulators of a block from TMEM to registers
-//                (freeing them for the next block at once) and add them to the fp32 global
-//                accumulators (red.add) while the next block computes;
+//   warps 12..15 move the finished dK^T / dV^T accumulators of a segment (the tiles of one block inside one scheduling
+//                run) from TMEM to registers (freeing them for the next segment at once) and store them to the
+//                segment's own fp32 slab while the next segment computes; a second kernel sums the slabs of a block
+//                in segment order, so dK and dV do not depend on the order in which CTAs finish (no atomics);
 //   warps 16..23 two groups, one row per thread, alternate tiles: P / dS to swizzled smem, then the
 //                dQ partial of the tile from TMEM through a swizzled staging area to global memory by TMA
 //                store (input dtype, tile order): the load/store unit is left to the row gathers.
@@ -33,20 +34,12 @@ struct SelBwdPipeParams {
     int run;
     SelBounds bd;      // visible K/V rows per token
     ET* dq_part;       // [max_tiles * 128, D] (written through dqmap)
-    float* dk_acc;     // [N, Hk, D] fp32, zero-initialised
-    float* dv_acc;
+    float* slabs;      // [segments][2 (dK, dV)][64 keys][D] fp32: the partial sums of every segment of tiles
 };
-
-// 1: dQ partials leave through a staging area and TMA stores, K/V single-buffered; 0: dQ partials by plain stores,
-// K/V double-buffered (the staging area and the second K/V stage compete for the same 32 KB).
-#ifndef FSA_BWD_DQ_TMA
-#define FSA_BWD_DQ_TMA 1
-#endif
 
 namespace bwdpipe {
 constexpr int D = 128, KT = 64;
-constexpr bool kDqTma = FSA_BWD_DQ_TMA != 0;
-constexpr int kKVStages = kDqTma ? 1 : 2;
+constexpr int kKVStages = 1;                     // (a second K/V stage and the dQ staging area compete for the same 32 KB)
 constexpr int kThreads = 768, kLoaders = 256;
 constexpr int kWLoad = kLoaders / 32, kWMma1 = kWLoad, kWMma2 = kWLoad + 1, kWFlush = kWLoad + 4, kWGroups = kWLoad + 8;
 // registers per thread of each role (multiples of 8); 32 * sum over warps <= 768 * 80 = the CTA's allocation
@@ -57,7 +50,7 @@ constexpr int kQD = 2 * kTileRows * D * 2;       // Q then dO: 64 KB
 constexpr int kPS = 2 * kTileRows * KT * 2;      // P then dS: 32 KB
 constexpr int kDQ = kTileRows * D * 2;           // dQ staging: 32 KB, 8 KB per TMEM lane quarter
 constexpr int kTail = 2560;
-constexpr int kBytes = kKVStages * kKV + 2 * kQD + kPS + (kDqTma ? kDQ : 0) + kTail;
+constexpr int kBytes = kKVStages * kKV + 2 * kQD + kPS + kDQ + kTail;
 constexpr int cS = 0, cDP = 64;                  // + 128 * buffer
 constexpr int cDQ = 256, cDK = 384, cDV = 448;
 constexpr uint32_t kCols = 512;
@@ -98,7 +91,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     uint8_t* sP = sQD + 2 * kQD;
     uint8_t* sDS = sP + kTileRows * KT * 2;
     uint8_t* sDQ = sP + kPS;
-    uint8_t* tail = sDQ + (kDqTma ? kDQ : 0);
+    uint8_t* tail = sDQ + kDQ;
     int (*s_tok)[kTileRows] = reinterpret_cast<int (*)[kTileRows]>(tail);                // [4][128] token of every tile row, -1 padding
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
     uint64_t* qd_full = bars;            // [2]
@@ -203,9 +196,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         if (t == 0) BT_DUMP(0, 5);
     } else if (warp >= kWFlush && warp < kWFlush + 4) {
         // ------------------------------------------------------------------ accumulator flush
-        // Walks the CTA's tiles to find the block boundaries; for every finished block: wait for its
+        // Walks the CTA's tiles to find the segment boundaries; for every finished segment: wait for its
         // last products, pull dK^T / dV^T (lane = head-dim index, columns = keys) into registers,
-        // release the TMEM accumulators, then add to the fp32 global accumulators.
+        // release the TMEM accumulators, then store them to the segment's slab.
         reg_inc<kRegFlush>();
         const int d_idx = (warp & 3) * 32 + lane;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -214,14 +207,17 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         int k = 0;
         BT_DECL;
         while (k < nloc && ok) {
-            const TileInfo ti = load_tile(p.ix, sched.tile(k));
+            const int j = sched.tile(k);
+            const TileInfo ti = load_tile(p.ix, j);
             int k2 = k + 1;
-            while (k2 < nloc && load_tile(p.ix, sched.tile(k2)).hg == ti.hg) ++k2;   // tiles [k, k2) form the block
+            while (k2 < nloc && (k2 % sched.run) != 0 && load_tile(p.ix, sched.tile(k2)).hg == ti.hg) ++k2;   // tiles [k, k2): one segment
+            // segments of a key are numbered by the scheduling run they fall into
+            const int seg = ti.seg0 + j / sched.run - __ldg(p.ix.tile_aux + j).x / sched.run;
+            float* slab = p.slabs + (int64_t)seg * (2 * KT * D) + d_idx;
             BT_TOC(0);
             ok = mbar_wait(acc_full, nflush & 1, status) && ok;
             BT_TOC(1);
             tc_fence_after();
-            const int nkeys = (int)min((int64_t)key_lim, s.Nk - ti.row0);
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
                 uint32_t v[KT];
@@ -230,15 +226,14 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                     tmem_ld32(tbase + lane_off + (which == 0 ? cDK : cDV) + c0, *reinterpret_cast<uint32_t (*)[32]>(&v[c0]));
                 tmem_ld_wait();
                 if (which == 1) {
-                    // both accumulators are in registers now: the next block may overwrite them
+                    // both accumulators are in registers now: the next segment may overwrite them
                     tc_fence_before();
                     mbar_arrive(acc_empty);
                     ++nflush;
                 }
-                float* dst = (which == 0 ? p.dk_acc : p.dv_acc) + ((int64_t)ti.row0 * s.Hk + ti.h) * D + d_idx;
+                float* dst = slab + which * (KT * D);
 #pragma unroll
-                for (int key = 0; key < KT; ++key)
-                    if (key < nkeys) atomicAdd(dst + (int64_t)key * s.Hk * D, __uint_as_float(v[key]));
+                for (int key = 0; key < KT; ++key) dst[key * D] = __uint_as_float(v[key]);
             }
             k = k2;
             BT_TOC(2);
@@ -318,8 +313,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             const int prev_hg = hg0;
             hg0 = hg1; hg1 = hg2;
             if (k + 2 < nloc) hg2 = load_tile(p.ix, sched.tile(k + 2)).hg;
-            const bool first_of_block = hg0 != prev_hg;
-            const bool last_of_block = (k + 1 >= nloc) || (hg1 != hg0);
+            // a segment ends where the block changes or the scheduling run ends
+            const bool first_of_block = hg0 != prev_hg || (k % sched.run) == 0;
+            const bool last_of_block = (k + 1 >= nloc) || (hg1 != hg0) || ((k + 1) % sched.run) == 0;
             if (first_of_block) { ++kvn; ++blk; }
             BT_TOC(0);
             ok = mbar_wait(pds_full, k & 1, status) && ok;
@@ -395,7 +391,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             for (int i = 0; i < 4; ++i) s_tok[slot][lane + 32 * i] = cur.e[i] != 0xFFFFFFFFu ? (int)(cur.e[i] >> kSlotBits) : -1;
             if (lane == 0) {
                 s_h[slot] = cur.h;
-                s_nb[slot] = cur.hg != prev_hg ? 1 : 0;
+                s_nb[slot] = (cur.hg != prev_hg || (k % sched.run) == 0) ? 1 : 0;
             }
             prev_hg = cur.hg;
             __syncwarp();
@@ -405,14 +401,14 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         // ------------------------------------------------------------------ K/V blocks by TMA
         bool ok = true;
         int kvn = -1, prev_hg = -1;
-        TileInfo t1{0, 0, 0, -1}, t2 = t1;
+        TileInfo t1{0, 0, 0, -1, 0}, t2 = t1;
         if (nloc > 0) t1 = load_tile(p.ix, sched.tile(0));
         if (nloc > 1) t2 = load_tile(p.ix, sched.tile(1));
         for (int k = 0; k < nloc && ok; ++k) {
             const TileInfo cur = t1;
             t1 = t2;
             if (k + 2 < nloc) t2 = load_tile(p.ix, sched.tile(k + 2));
-            if (cur.hg == prev_hg) continue;
+            if (cur.hg == prev_hg && (k % sched.run) != 0) continue;     // (every segment loads its K/V block)
             prev_hg = cur.hg;
             ++kvn;
             if (lane == 0) {
@@ -549,62 +545,38 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             ok = mbar_wait(dq_full, k & 1, status) && ok;
             BT_TOC(5);
             tc_fence_after();
-            if constexpr (kDqTma) {
-                // staging rows of this lane quarter: free once the store of the previous tile (other group) has read them
-                ok = mbar_wait(&stg_free[quarter], (k - 1) & 1, status) && ok;
-                uint8_t* my_stage = sDQ + quarter * (32 * 256);
-    #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tbase + lane_off + cDQ + c0, v);
-                    tmem_ld_wait();
-    #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 u;
-                        u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
-                        u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
-                        u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
-                        u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
-                        const int chunk = (c0 >> 3) + q4;
-                        *reinterpret_cast<uint4*>(my_stage + (chunk >> 3) * (32 * 128) + sw128_chunk_off(lane, chunk & 7)) = u;
-                    }
-                }
-                tc_fence_before();
-                mbar_arrive(dq_empty);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-    #pragma unroll
-                    for (int b = 0; b < D / 64; ++b)
-                        tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
-                    bulk_commit();
-                    bulk_wait_read0();
-                    mbar_arrive(&stg_free[quarter]);
-                }
-                __syncwarp();
-            } else {
-                const bool row_valid = true;   // padding rows are written too (never read)
-                uint4* dst = reinterpret_cast<uint4*>(p.dq_part + ((int64_t)j * kTileRows + r) * D);
+            // staging rows of this lane quarter: free once the store of the previous tile (other group) has read them
+            ok = mbar_wait(&stg_free[quarter], (k - 1) & 1, status) && ok;
+            uint8_t* my_stage = sDQ + quarter * (32 * 256);
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tbase + lane_off + cDQ + c0, v);
-                    tmem_ld_wait();
-                    if (row_valid) {
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tbase + lane_off + cDQ + c0, v);
+                tmem_ld_wait();
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint4 u;
-                            u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
-                            u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
-                            u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
-                            u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
-                            dst[(c0 >> 3) + q4] = u;
-                        }
-                    }
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 u;
+                    u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                    u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                    u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                    u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                    const int chunk = (c0 >> 3) + q4;
+                    *reinterpret_cast<uint4*>(my_stage + (chunk >> 3) * (32 * 128) + sw128_chunk_off(lane, chunk & 7)) = u;
                 }
-                tc_fence_before();
-                mbar_arrive(dq_empty);
             }
+            tc_fence_before();
+            mbar_arrive(dq_empty);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b)
+                    tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
+                bulk_commit();
+                bulk_wait_read0();
+                mbar_arrive(&stg_free[quarter]);
+            }
+            __syncwarp();
             BT_TOC(6);
         }
         if (quarter == 0 && lane == 0) BT_DUMP(32 + sb * 8, 7);
@@ -623,9 +595,9 @@ static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const Sel
     p.lse = a.lse; p.delta = a.delta;
     p.s = s; p.ix = ix;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
-    p.run = a.run > 0 ? a.run : 32;    // longer runs: fewer flushes of the dK / dV accumulators per block
+    p.run = s.RB;                      // (long runs: few segments per block)
     p.bd = a.bd;
-    p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
+    p.dq_part = (ET*)a.dq_part; p.slabs = a.slabs;
     auto kern = sel_bwd_pipe<ET>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwdpipe::kBytes);
     if (e != cudaSuccess) return e;

@@ -6,13 +6,17 @@
 //   entry      one (token, slot) pair: token n selected a KV block in slot s of its top-k list
 //   gb         global KV-block id.  For sequence b starting at row c_b, local block j:
 //                  gb = c_b / BK + b + j      (unique, ascending, < N/BK + B + 1)
-//   hg         kv_head * NBmax + gb, the key of the block->entries CSR
-//   tile       up to TPT = (128 / G) & ~3 consecutive entries of one hg; each entry contributes its G
+//   key        hg = kv_head * NBmax + gb, the key of the block->entries CSR; the entries of a key are in ascending
+//              order of their 32-token group (a deterministic order: no atomics decide it)
+//   chunk      C consecutive query tokens: the unit of work of the index build (one CTA per (kv head, chunk))
+//   tile       up to TPT = (128 / G) & ~3 consecutive entries of one key; each entry contributes its G
 //              query heads, so a tile is <= 128 rows of the MMA.  Rows are head-major inside a tile:
 //              row r = g * TPT + e (head g of the group, e-th entry of the tile), so that four
-//              consecutive rows are four tokens of one head -- one TMA gather4.
-//   pos        for every (kv head, token, slot): tile_off[hg] * TPT + rank of the entry inside its
-//              block, or -1 for an unusable slot.  Partial results live in tile order
+//              consecutive rows are four tokens of one head
+//   segment    the tiles of one key that one CTA of the backward walks in a row (its static schedule deals runs of
+//              RB consecutive tiles): every segment owns one slab of partial dK / dV sums
+//   pos        for every (kv head, token, slot): first tile of the key * TPT + rank of the entry inside its
+//              key, or -1 for an unusable slot.  Partial results live in tile order
 //              (row = (pos / TPT) * 128 + g * TPT + pos % TPT), which the merge kernels look up here.
 #pragma once
 #include <stdint.h>
@@ -37,6 +41,9 @@ struct SelShape {
     int BK;          // KV block size
     int NBmax;       // bound on gb: N / BK + B + 1
     int TPT;         // entries per tile = (128 / G) & ~3
+    int C;           // query tokens per chunk of the index build
+    int NC;          // chunks = ceil(N / C)
+    int RB;          // tiles per scheduling run of the backward kernel (fixes the segments)
 };
 
 // Index workspace (kept by the caller between forward and backward).  All int32.
@@ -51,12 +58,15 @@ struct SelBounds {
 };
 
 struct SelIndex {
-    int* header;     // [64]: [0] status, [1] total tiles
-    int* counts;     // [Hk * NBmax]   entries per hg
-    int* cursor;     // [Hk * NBmax]   fill cursors (scratch)
-    int* row0;       // [NBmax]        first global K/V row of block gb
-    int* tile_off;   // [Hk * NBmax + 1] exclusive scan of ceil(counts / TPT): first tile of every hg
-    int4* tile_rec;  // [max_tiles]   per tile {kv head, first K/V row of the block, entries in the tile, hg}
+    int* header;     // [64]: [0] status, [1] total tiles, [2] total entries, [3] total segments
+    int* chunk_cnt;  // [Hk * NC * NBmax]  entries of (kv head, chunk, block); then their exclusive prefix over the chunks
+    int* key_cnt;    // [Hk * NBmax]       entries per key
+    int* key_tile;   // [Hk * NBmax + 1]   first tile of every key (exclusive scan of ceil(count / TPT))
+    int* key_seg;    // [Hk * NBmax + 1]   first segment of every key
+    int* row0;       // [NBmax]            first global K/V row of block gb
+    int* nrow;       // [NBmax]            K/V rows of block gb (the last block of a sequence may be short)
+    int4* tile_rec;  // [max_tiles]   per tile {first K/V row of the block, entries | kv head << 8, key, first segment of the key}
+    int2* tile_aux;  // [max_tiles]   per tile {first tile of its key, tiles of its key}
     uint32_t* entries;  // [max_tiles * TPT]  packed entries in TILE ORDER: entry e of tile j at j * TPT + e,
                         //                    0xFFFFFFFF where a tile is not full
     int* pos;        // [Hk * N * T]  tile-order position of every (head, token, slot), -1 if unusable
@@ -68,39 +78,46 @@ __host__ __device__ inline int64_t align_up(int64_t x, int64_t a) { return (x + 
 inline int64_t sel_max_tiles(const SelShape& s) {
     return ((int64_t)s.Hk * s.N * s.T + s.TPT - 1) / s.TPT + (int64_t)s.Hk * s.NBmax;
 }
+// upper bound on the number of segments: one per key plus one per scheduling run that cuts a key
+inline int64_t sel_max_segments(const SelShape& s) {
+    return (int64_t)s.Hk * s.NBmax + sel_max_tiles(s) / s.RB + 1;
+}
 
 inline int64_t sel_index_bytes(const SelShape& s) {
-    int64_t HG = (int64_t)s.Hk * s.NBmax;
+    const int64_t HG = (int64_t)s.Hk * s.NBmax;
     int64_t b = 0;
     b += align_up(64 * 4, 256);
-    b += align_up(HG * 4, 256) * 2;
-    b += align_up((int64_t)s.NBmax * 4, 256);
-    b += align_up((HG + 1) * 4, 256);
+    b += align_up(HG * s.NC * 4, 256);
+    b += align_up(HG * 4, 256);
+    b += align_up((HG + 1) * 4, 256) * 2;
+    b += align_up((int64_t)s.NBmax * 4, 256) * 2;
     b += align_up(sel_max_tiles(s) * 16, 256);
+    b += align_up(sel_max_tiles(s) * 8, 256);
     b += align_up(sel_max_tiles(s) * s.TPT * 4, 256);
     b += align_up((int64_t)s.Hk * s.N * s.T * 4, 256);
     return b;
 }
 
 inline SelIndex sel_index_carve(void* ws, const SelShape& s) {
-    int64_t HG = (int64_t)s.Hk * s.NBmax;
+    const int64_t HG = (int64_t)s.Hk * s.NBmax;
     char* p = (char*)ws;
     SelIndex ix;
-    ix.header = (int*)p;   p += align_up(64 * 4, 256);
-    ix.counts = (int*)p;   p += align_up(HG * 4, 256);
-    ix.cursor = (int*)p;   p += align_up(HG * 4, 256);
-    ix.row0 = (int*)p;     p += align_up((int64_t)s.NBmax * 4, 256);
-    ix.tile_off = (int*)p; p += align_up((HG + 1) * 4, 256);
+    ix.header = (int*)p;    p += align_up(64 * 4, 256);
+    ix.chunk_cnt = (int*)p; p += align_up(HG * s.NC * 4, 256);
+    ix.key_cnt = (int*)p;   p += align_up(HG * 4, 256);
+    ix.key_tile = (int*)p;  p += align_up((HG + 1) * 4, 256);
+    ix.key_seg = (int*)p;   p += align_up((HG + 1) * 4, 256);
+    ix.row0 = (int*)p;      p += align_up((int64_t)s.NBmax * 4, 256);
+    ix.nrow = (int*)p;      p += align_up((int64_t)s.NBmax * 4, 256);
     ix.tile_rec = (int4*)p; p += align_up(sel_max_tiles(s) * 16, 256);
+    ix.tile_aux = (int2*)p; p += align_up(sel_max_tiles(s) * 8, 256);
     ix.entries = (uint32_t*)p; p += align_up(sel_max_tiles(s) * s.TPT * 4, 256);
     ix.pos = (int*)p;
     return ix;
 }
-// bytes from the start of the workspace that must be zero before the index build
-inline int64_t sel_index_zero_bytes(const SelShape& s) {
-    int64_t HG = (int64_t)s.Hk * s.NBmax;
-    return align_up(64 * 4, 256) + align_up(HG * 4, 256) * 2;
-}
+// bytes from the start of the workspace that must be zero before the index build (the header: every other word is
+// written before it is read)
+inline int64_t sel_index_zero_bytes(const SelShape&) { return align_up(64 * 4, 256); }
 
 // sequence of token n: largest b with cu[b] <= n
 __device__ __forceinline__ int find_seq(const int* __restrict__ cu, int B, int n) {
@@ -138,12 +155,14 @@ __device__ __forceinline__ int entry_block(const int* __restrict__ cu, const Sel
 // one per slot).
 struct TokenCtx {
     int c, ck, kb, lo, hi;    // sequence start (q rows), K/V start, global id of block 0, visible range (range mode)
+    int ke;                   // K/V end of the sequence
 };
 __device__ __forceinline__ TokenCtx token_ctx(const int* __restrict__ cu, const SelBounds& bd, int B, int BK, int n) {
     TokenCtx t;
     const int b = find_seq(cu, B, n);
     t.c = __ldg(cu + b);
     t.ck = bd.cu_k ? __ldg(bd.cu_k + b) : t.c;
+    t.ke = bd.cu_k ? __ldg(bd.cu_k + b + 1) : __ldg(cu + b + 1);
     t.kb = t.ck / BK + b;
     t.lo = t.ck; t.hi = -1;
     if (bd.kv_hi) {
@@ -207,11 +226,11 @@ struct TileSchedule {
 // One tile of the list, read from its record: no searching, and the address depends only on the
 // tile index, so records and entries can be prefetched any number of tiles ahead.
 struct TileInfo {
-    int h, row0, ne, hg;
+    int h, row0, ne, hg, seg0;   // kv head, first K/V row of the block, entries, key, first segment of the key
 };
 __device__ __forceinline__ TileInfo load_tile(const SelIndex& ix, int tile) {
     int4 r = __ldg(ix.tile_rec + tile);
-    return TileInfo{r.x, r.y, r.z, r.w};
+    return TileInfo{r.y >> 8, r.x, r.y & 255, r.z, r.w};
 }
 
 // Sequential walker used by the unpipelined kernels.

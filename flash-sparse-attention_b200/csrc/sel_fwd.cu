@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
         // ------------------------------------------------------------------ K/V blocks by TMA
         bool ok = true;
         int kvn = -1, prev_hg = -1;
-        TileInfo t1{0, 0, 0, -1}, t2 = t1;
+        TileInfo t1{0, 0, 0, -1, 0}, t2 = t1;
         if (nloc > 0) t1 = load_tile(p.ix, sched.tile(0));
         if (nloc > 1) t2 = load_tile(p.ix, sched.tile(1));
         for (int k = 0; k < nloc && ok; ++k) {
@@ -769,7 +769,7 @@ __global__ void __launch_bounds__(128, 1) sel_fwd_simple(const SelFwdParams<ET> 
 }
 
 // ------------------------------------------------------------------------------------------
-template <int D, typename ET, int MODE>
+template <int D, typename ET>
 __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opart, const float2* __restrict__ ml,
                                                       const int* __restrict__ pos, SelShape s, ET* __restrict__ o,
                                                       int64_t o_sn, int64_t o_sh, float* __restrict__ lse) {
@@ -786,7 +786,7 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
     float L, M;
-    if (MODE == 2 && s.T <= 16) {
+    if (s.T <= 16) {
         // Up to 16 slots (with 32 rows in flight the kernel measured slower: registers, occupancy): the row loads depend only on the positions, so they are issued together with
         // the load of the statistics (one round trip less, all rows in flight per warp); weights are applied afterwards.
         int ps = lane < s.T ? __ldg(prow + lane) : -1;
@@ -844,14 +844,6 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
         L = w0 * l0 + w1 * l1;
 #pragma unroll
         for (int o_ = 16; o_; o_ >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o_);
-        if (MODE == 0) {
-            for (int sl = 0; sl < s.T; ++sl) {
-                const float w = __shfl_sync(0xffffffffu, sl < 32 ? w0 : w1, sl & 31);
-                const long long pr = __shfl_sync(0xffffffffu, (long long)(sl < 32 ? pr0 : pr1), sl & 31);
-                if (w == 0.f) continue;
-                fma_row_vec<V, ET>(acc, ld_row_vec<V, ET>(opart + pr * D + lane * V), w);
-            }
-        } else {
         for (int sl0 = 0; sl0 < s.T; sl0 += 8) {
             uint4 u[8];
             float w[8];
@@ -865,7 +857,6 @@ __global__ void __launch_bounds__(256) sel_fwd_reduce(const ET* __restrict__ opa
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) fma_row_vec<V, ET>(acc, u[j], w[j]);
-        }
         }
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -936,13 +927,7 @@ static cudaError_t launch_sel_fwd(const SelFwdArgs& a, const SelShape& s, const 
     if (rows > 0) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(1, stream);
-        static const int mode = [] { const char* v = getenv("FSA_FWD_REDUCE_MODE"); return v && *v ? atoi(v) : 2; }();
-        if (mode == 2)
-            sel_fwd_reduce<D, ET, 2><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
-        else if (mode == 1)
-            sel_fwd_reduce<D, ET, 1><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
-        else
-            sel_fwd_reduce<D, ET, 0><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
+        sel_fwd_reduce<D, ET><<<grid, 256, 0, stream>>>((const ET*)a.opart, a.ml, ix.pos, s, (ET*)a.o, a.o_sn, a.o_sh, a.lse);
         prof_end(1, stream);
     }
     return cudaGetLastError();

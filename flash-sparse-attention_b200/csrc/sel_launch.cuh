@@ -10,6 +10,9 @@ namespace fsa {
 void prof_begin(int kernel_id, cudaStream_t stream);
 void prof_end(int kernel_id, cudaStream_t stream);
 
+// warps per CTA of the index kernels (their per-warp histograms must fit in shared memory); 0: too many blocks
+int sel_index_warps(const SelShape& s);
+
 cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelBounds& bd, const SelShape& s, const SelIndex& ix,
                             void* ws, cudaStream_t stream);
 
@@ -45,13 +48,13 @@ struct SelBwdArgs {
     const int* cu;
     float sm_scale;
     int run;           // tiles per scheduling run; 0 = default
-    int force_simple;  // diagnostics: use the unpipelined main kernel even where the pipelined one applies
     // scratch
     float* delta;      // [Hq, N]
     void* dq_part;     // [max_tiles * nsub * 128, D] input dtype
     const CUtensorMap* dqmap;   // over dq_part, box {64, 32}: partial stores of the pipelined kernel (null: not built)
-    float* dk_acc;     // [N, Hk, D]; dv_acc follows immediately
+    float* dk_acc;     // [N, Hk, D]; dv_acc follows immediately (unpipelined kernel: fp32 accumulators)
     float* dv_acc;
+    float* slabs;      // [segments][2][64][D] fp32 (pipelined kernel: per-segment partial dK / dV); shares memory with dk_acc
     // outputs (contiguous)
     void *dq, *dk, *dv;
     SelBounds bd;      // visible K/V rows per token (all null: causal rule of selected attention)

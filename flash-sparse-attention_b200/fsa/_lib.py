@@ -98,10 +98,10 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     ),
     "fsa_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
+    "fsa_sel_index_geometry": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int), POINTER(c_int)]),
     "fsa_sel_index_dump": (
         c_int,
-        [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_void_p],
+        [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
 }
 

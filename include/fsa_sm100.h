@@ -55,6 +55,7 @@ int fsa_last_cuda_error_line(void);
 #define FSA_KERNEL_SEL_FWD_REDUCE 1
 #define FSA_KERNEL_SEL_BWD_MAIN 2
 #define FSA_KERNEL_SEL_BWD_DQ_REDUCE 3
+#define FSA_KERNEL_SEL_INDEX 4          /* the index build of a forward (several small kernels) */
 int fsa_profile_enable(int on);
 int fsa_profile_read(int kernel_id, float* ms_sum_out, int* launches_out);
 
@@ -277,17 +278,23 @@ int fsa_decode_ranges(const int32_t* topk_idx, const int32_t* seq_len, const int
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
 int fsa_read_status(const void* index_ws, void* stream, int* status_out);
 
-/* Debug/inspection: copy the block->entries structure built by the forward to host arrays (what the reference
- * keeps as valid_lens / valid_start_indices / the flat token list, fsa/ops/FSA_topk_sparse_attention.py:60-135).
- * With nbmax = total_tokens / block_size + batch + 1 and tpt = (128 / group) & ~3:
- *   counts_host [Hk * nbmax] entries per (kv head, block); row0_host [nbmax] first K/V row of a block;
- *   tile_off_host [Hk * nbmax + 1] first tile of every (kv head, block);
- *   entries_host [(ceil(Hk * total_tokens * topk / tpt) + Hk * nbmax) * tpt] entries in tile order:
- *   the entries of (kv head, block) hg start at tile_off[hg] * tpt; an entry is (token << 6) | slot;
- *   header_host [64]: [0] status, [1] tiles, [2] entries. */
+/* Debug/inspection: geometry of the index workspace for a problem: the upper bound on tiles the workspace is sized
+ * for, the entries per tile tpt = (128 / group) & ~3, and nbmax = total_tokens / block_size + batch + 1, the bound on
+ * global block ids.  No reference counterpart (host arithmetic only). */
+int fsa_sel_index_geometry(int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads, int topk, int block_size,
+                           int64_t* max_tiles_out, int* tpt_out, int* nbmax_out);
+
+/* Debug/inspection: copy the "(kv head, block) -> entries" tile list built by the forward to host arrays (what the
+ * reference keeps as valid_lens / valid_start_indices / the flat token list,
+ * fsa/ops/FSA_topk_sparse_attention.py:60-135).  Sizes from fsa_sel_index_geometry:
+ *   tile_rec_host [4 * max_tiles]: per tile {first K/V row of its block, entries | kv head << 8, key = kv head * nbmax +
+ *   global block id, first dK/dV segment of the key};
+ *   entries_host [max_tiles * tpt]: entry e of tile j at j * tpt + e, (token << 6) | slot, 0xFFFFFFFF padding;
+ *   key_tile_host [Hk * nbmax + 1]: first tile of every key;
+ *   header_host [64]: [0] status, [1] tiles, [2] entries, [3] segments.  Any pointer may be NULL. */
 int fsa_sel_index_dump(const void* index_ws, int64_t total_tokens, int batch, int num_q_heads, int num_kv_heads,
-                       int topk, int block_size, void* stream, int32_t* counts_host, int32_t* row0_host,
-                       int32_t* tile_off_host, uint32_t* entries_host, int32_t* header_host);
+                       int topk, int block_size, void* stream, int32_t* tile_rec_host, uint32_t* entries_host,
+                       int32_t* key_tile_host, int32_t* header_host);
 
 #ifdef __cplusplus
 }

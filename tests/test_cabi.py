@@ -43,7 +43,8 @@ def test_workspace_queries():
     # config 1 of the benchmark: 64K tokens, 4 sequences, 8 q heads, 4 kv heads, T=16, BK=64
     assert L.fsa_sel_index_bytes(65536, 4, 8, 4, 16, 64, byref(n)) == 0
     entries = 4 * 65536 * 16 * 4   # one int per (kv head, token, slot): entry list and position map
-    assert 2 * entries <= n.value < 2 * entries + (4 << 20)
+    # plus room for one ragged tile per (kv head, window, block) key that may exist: O(N * Hk * T) ints all the same
+    assert 2 * entries <= n.value < 5 * entries
     assert L.fsa_sel_fwd_scratch_bytes(65536, 4, 8, 4, 128, 16, 64, byref(n)) == 0
     assert n.value >= 65536 * 8 * 16 * 64 * 2  # at least bf16 partials
     assert L.fsa_sel_bwd_scratch_bytes(65536, 4, 8, 4, 128, 16, 64, byref(n)) == 0

@@ -11,7 +11,7 @@ atol 0.9; test/test_FSA_optimized_sel_attn.py:275-289).
 """
 import glob
 import os
-from ctypes import byref, c_int
+from ctypes import byref, c_int, c_int64
 
 import numpy as np
 import pytest
@@ -121,27 +121,37 @@ def test_public_operator_autograd_and_strided_inputs():
 
 
 def test_index_inversion_is_exact():
-    """The block->entries CSR against a numpy inversion (integer work: bit-exact as sets,
-    and each block's list is a permutation-free cover)."""
-    seqlens, Hk, G, d, bs, T = [513, 64, 1000], 3, 1, 64, 64, 16
+    """The (kv head, block) -> entries tile list against a numpy inversion (integer work: bit-exact).  Every entry
+    appears exactly once, in a tile of its own key; the tiles of a key are consecutive and start where key_tile says;
+    entries of a key are in ascending order of their 32-token group; two builds of the same index are identical
+    word for word (no atomics decide an order)."""
+    seqlens, Hk, G, d, bs, T = [513, 64, 2000], 3, 1, 64, 64, 16
     N = sum(seqlens)
     cu = make_cu_seqlens(seqlens)
     idx = make_topk_idx(seqlens, Hk, T, bs, 9)
     q, k, v = make_qkv(N, Hk * G, Hk, d, 1, with_do=False)
-    _, _, ws = sel_attn_fwd(q.to(DEV), k.to(DEV), v.to(DEV), idx.to(DEV), bs, cu.to(DEV), d ** -0.5, check_status=True)
     L = _lib.lib()
     B = len(seqlens)
-    nbmax = N // bs + B + 1
-    counts = np.zeros(Hk * nbmax, np.int32)
-    row0 = np.zeros(nbmax, np.int32)
-    tile_off = np.zeros(Hk * nbmax + 1, np.int32)
-    tpt = (128 // G) & ~3
-    entries = np.zeros((-(-Hk * N * T // tpt) + Hk * nbmax) * tpt, np.uint32)
-    header = np.zeros(64, np.int32)
-    rc = L.fsa_sel_index_dump(_lib.ptr(ws), N, B, Hk * G, Hk, T, bs, None, counts.ctypes.data, row0.ctypes.data,
-                              tile_off.ctypes.data, entries.ctypes.data, header.ctypes.data)
-    assert rc == 0
-    # numpy inversion
+    mt, tpt, nbmax = c_int64(0), c_int(0), c_int(0)
+    assert L.fsa_sel_index_geometry(N, B, Hk * G, Hk, T, bs, byref(mt), byref(tpt), byref(nbmax)) == 0
+    mt, tpt, nbmax = mt.value, tpt.value, nbmax.value
+    assert tpt == (128 // G) & ~3 and nbmax == N // bs + B + 1
+
+    def dump():
+        _, _, ws = sel_attn_fwd(q.to(DEV), k.to(DEV), v.to(DEV), idx.to(DEV), bs, cu.to(DEV), d ** -0.5, check_status=True)
+        rec = np.zeros((mt, 4), np.int32)
+        entries = np.zeros(mt * tpt, np.uint32)
+        key_tile = np.zeros(Hk * nbmax + 1, np.int32)
+        header = np.zeros(64, np.int32)
+        rc = L.fsa_sel_index_dump(_lib.ptr(ws), N, B, Hk * G, Hk, T, bs, None, rec.ctypes.data, entries.ctypes.data,
+                                  key_tile.ctypes.data, header.ctypes.data)
+        assert rc == 0
+        return rec, entries, key_tile, header
+
+    rec, entries, key_tile, header = dump()
+    ntiles = int(header[1])
+    assert header[0] == 0 and key_tile[-1] == ntiles and (np.diff(key_tile) >= 0).all()
+    # numpy inversion: key -> entries
     exp = {}
     cul = cu.tolist()
     for b in range(B):
@@ -151,20 +161,44 @@ def test_index_inversion_is_exact():
                 for s in range(T):
                     i = int(idx[h, n, s])
                     if 0 <= i <= tl // bs:
-                        gb = cul[b] // bs + b + i
-                        exp.setdefault((h, gb), []).append((n << 6) | s)
-                        assert row0[gb] == cul[b] + i * bs
+                        exp.setdefault((h * nbmax + cul[b] // bs + b + i, cul[b] + i * bs), []).append((n << 6) | s)
+    got = {}
+    for j in range(ntiles):
+        row0, neh, key, seg0 = (int(x) for x in rec[j])
+        ne, h = neh & 255, neh >> 8
+        assert key // nbmax == h and key_tile[key] <= j < key_tile[key + 1]
+        es = entries[j * tpt : j * tpt + ne].tolist()
+        assert all(x != 0xFFFFFFFF for x in es) and all(x == 0xFFFFFFFF for x in entries[j * tpt + ne : (j + 1) * tpt].tolist())
+        got.setdefault((key, row0), []).extend(es)
+    assert set(got) == set(exp)
     total = 0
-    for h in range(Hk):
-        for gb in range(nbmax):
-            want = sorted(exp.get((h, gb), []))
-            c = counts[h * nbmax + gb]
-            assert c == len(want)
-            first = tile_off[h * nbmax + gb] * tpt
-            got = sorted(entries[first : first + c].tolist())
-            assert got == want
-            total += c
-    assert header[0] == 0 and header[2] == total
+    for kk, want in exp.items():
+        assert sorted(got[kk]) == sorted(want)
+        grp = [(e >> 6) // 32 for e in got[kk]]
+        assert grp == sorted(grp)
+        total += len(want)
+    assert header[2] == total
+    rec2, entries2, key_tile2, header2 = dump()
+    assert np.array_equal(rec[:ntiles], rec2[:ntiles]) and np.array_equal(entries[: ntiles * tpt], entries2[: ntiles * tpt])
+    assert np.array_equal(key_tile, key_tile2) and np.array_equal(header[:4], header2[:4])
+
+
+def test_backward_is_bit_reproducible():
+    """dq, dk and dv of two runs on the same inputs are identical bit for bit: the entry order of the index is fixed by
+    the input alone, and the partial dK / dV sums of a block are added in a fixed order (the reference's backward_dkdv,
+    fsa/ops/FSA_topk_sparse_attention.py:1548-1712, is deterministic too)."""
+    seqlens, Hk, G, d, bs, T = [4096, 1500, 6000], 2, 2, 128, 64, 16
+    N = sum(seqlens)
+    q, k, v, do = (x.to(DEV) for x in make_qkv(N, Hk * G, Hk, d, 77))
+    idx = make_topk_idx(seqlens, Hk, T, bs, 78).to(DEV)
+    cu = make_cu_seqlens(seqlens).to(DEV)
+    outs = []
+    for _ in range(3):
+        o, lse, ws = sel_attn_fwd(q, k, v, idx, bs, cu, d ** -0.5, check_status=True)
+        outs.append((o, lse) + sel_attn_bwd(q, k, v, o, lse, do, idx, bs, cu, d ** -0.5, ws, check_status=True))
+    for other in outs[1:]:
+        for a, b, name in zip(outs[0], other, ("o", "lse", "dq", "dk", "dv")):
+            assert torch.equal(a, b), name
 
 
 def test_error_paths_raise():
