@@ -1,18 +1,21 @@
 #!/usr/bin/env python
-"""Benchmark of the selected-attention hot path (forward + backward) on B200.
+"""Benchmark of the selected-attention hot path (forward + backward) on B200, with the NSA layer and the decode step
+measured beside it.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload sel_attn|layer|decode]
 
-Workload (N = 1): BASELINE config 1 -- a varlen batch of 4 x 16384 tokens (64K), 4 KV heads,
-GQA group 2, head_dim 128, block size 64, top-k 16, bf16, seeded synthetic inputs.  A step is one
-forward + backward of the operator.  With N > 1 (one process per GPU, torchrun) every rank owns
-one such 4-KV-head shard of a model with 4*N KV heads: selected attention never mixes KV heads,
-so there is no collective on the path ("weak" scaling).
+Headline (`value`): BASELINE config 1 -- a varlen batch of 4 x 16384 tokens (64K), 4 KV heads, GQA group 2, head_dim
+128, block size 64, top-k 16, bf16, seeded synthetic inputs.  A step is one forward + backward of the operator.  With
+N > 1 (one process per GPU, torchrun) THE SAME problem is split over the ranks: its 16 independent (sequence, kv head)
+pairs are dealt to the GPUs (by kv head up to 4 GPUs, then by sequence), so the total work is fixed ("strong" scaling)
+and there is no collective on the path -- selected attention never mixes kv heads or sequences.
 
-The JSON line carries: the device-resident throughput (`value`, effective TFLOP/s on the useful
-FLOPs 14*d*P), the end-to-end number through the public operator with pinned host buffers
-(`e2e`), the roofline of the dominant kernel, and a CPU baseline (the fp32 oracle timed on the
-host cores on a bounded sample).
+The JSON line carries: the device-resident throughput (`value`, effective TFLOP/s on the useful FLOPs 14*d*P), the
+end-to-end number through the public operator with pinned host buffers (`e2e`), the roofline of the dominant kernel, a
+CPU baseline (the fp32 oracle timed on the host cores), and two sub-records measured in the same process group:
+`layer` (BASELINE config 3, the whole NSA layer forward + backward, head-parallel over the ranks) and `decode`
+(BASELINE config 4, one decode step, KV sequence sharded over the ranks).  `--workload layer|decode` print those
+records as lines of their own.
 """
 from __future__ import annotations
 
@@ -30,9 +33,9 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 # DRAM bytes (read + write) per launch of the main kernels from one ncu capture of the small case (one 16384-token
-# sequence; profiles/sel_attn_kernels_small_case_ncu.md); traffic grows with the token count, so cfg1 is 4 x that.
+# sequence of config 1); traffic grows with the token count, so config 1 is 4 x that.
 NCU_TRAFFIC_SMALL = {"sel_bwd_main": 290.8e6 + 572.2e6, "sel_fwd_main": 79.3e6 + 496.9e6}
-# the compressed pass of the decode step at batch 8 (profiles/decode_kernels_small_case_ncu.md); grows with the batch
+# the compressed pass of the decode step at batch 8, from one ncu capture; grows with the batch
 NCU_TRAFFIC_DECODE_B8 = 268.5e6 + 6.7e6
 
 METRIC = "sel-attn fwd+bwd effective TFLOPS @64K (4x16384 tok, Hk=4, G=2, d=128, B_K=64, T=16)"
@@ -42,12 +45,6 @@ CFG = dict(seqlens=[16384] * 4, Hk=4, G=2, d=128, bs=64, T=16)
 
 def workload_name():
     return "cfg1: varlen 4x16384 tokens, 4 KV heads, G=2, d=128, B_K=64, T=16, fwd+bwd"
-
-
-def attended_pairs(idx_cpu, cu_cpu, bs, G):
-    from oracle.sel_attn_oracle import attended_key_count  # counting helper only (integer work on the indices)
-
-    return attended_key_count(idx_cpu, cu_cpu, bs, G)
 
 
 def analytic_pairs(seqlens, Hk, G, bs, T):
@@ -117,7 +114,7 @@ class ClockSampler:
 
 
 def cpu_baseline_sample(n_tokens, threads, repeats=1):
-    """Time the fp32 oracle (forward + backward) on the first `n_tokens` of one cfg1 sequence."""
+    """Time the fp32 oracle (forward + backward) on the first `n_tokens` of one config-1 sequence."""
     from fsa.synthetic import make_cu_seqlens, make_qkv, make_topk_idx
     from oracle.sel_attn_oracle import sel_attn_forward_backward
 
@@ -137,13 +134,92 @@ def cpu_baseline_sample(n_tokens, threads, repeats=1):
     return flops / best / 1e12, best, flops
 
 
+def cpu_baseline_config0(threads, repeats=3):
+    """The fp32 oracle forward on BASELINE config 0 (1 x 8192 tokens, 4 KV heads, G = 1), best of `repeats`."""
+    from fsa.synthetic import make_cu_seqlens, make_qkv, make_topk_idx
+    from oracle.sel_attn_oracle import sel_attn_forward
+
+    torch.set_num_threads(threads)
+    n, Hk, G, d, bs, T = 8192, 4, 1, 128, 64, 16
+    q, k, v = make_qkv(n, Hk * G, Hk, d, 42, with_do=False)
+    idx = make_topk_idx([n], Hk, T, bs, 42)
+    cu = make_cu_seqlens([n])
+    flops = 4 * d * analytic_pairs([n], Hk, G, bs, T)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        sel_attn_forward(q.float(), k.float(), v.float(), idx, bs, cu, d ** -0.5)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return flops / best / 1e12, best
+
+
+def load_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def tensor_peak(burst):
+    """Measured dense bf16 peak: the burst figure for a kernel timed alone or inside a step of milliseconds, the
+    sustained one for a step that runs for seconds."""
+    peaks = load_peaks()
+    key = "bf16_tflops" if burst else "bf16_tflops_sustained"
+    v = float(peaks.get(key, 0) or 0)
+    if v:
+        return v, f"MEASURED_PEAKS.json {key}"
+    return (1590.0, "fallback (burst cuBLAS bf16 measured earlier on this pool)") if burst else (1400.0, "fallback (sustained cuBLAS bf16 on this pool)")
+
+
+class Dist:
+    """The process group of the run (one rank per GPU) and the timing helpers built on it."""
+
+    def __init__(self, rank, world, local_rank):
+        import torch.distributed as dist
+
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+        self.rank, self.world, self.dist = rank, world, dist
+        torch.cuda.set_device(local_rank)
+        self.dev = torch.device("cuda", local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_ms(self, ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, n):
+        """CUDA-event time of n calls between two barriers, max over the ranks, per call (ms)."""
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        ev0.record()
+        for _ in range(n):
+            fn()
+        ev1.record()
+        self.barrier()
+        return self.max_ms(ev0.elapsed_time(ev1)) / n
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
 def run_reference(args, rank, world):
     """Reference arm: the CPU restatement of the reference's nsa_ref path (the oracle) on the host
     cores.  The reference itself is Triton-only and has no CPU implementation to time."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    n_tok = 1024
+    n_tok = 2048
     for _ in range(max(args.warmup, 0) and 1):
         cpu_baseline_sample(256, threads)
     t_tot, flops_tot = 0.0, 0.0
@@ -155,7 +231,7 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference",
         "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": t_tot / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": t_tot / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic (seeded N(0,1) q/k/v/dO, seeded causal block ids)",
         "config": {"workload": workload_name(), "sample": f"first {n_tok} tokens of one sequence, fwd+bwd per step"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
@@ -189,21 +265,15 @@ def decode_cpu_baseline(threads, cache_len=8192):
     return 1.0 / dt, dt, cache_len
 
 
-def run_decode(args, rank, world, local_rank):
+def run_decode(args, dd, steps, sub=False):
     """One decode step of the three NSA branches + gate mix over a resident KV cache; with N > 1 the KV sequence is
     split over the ranks (same batch, same total cache: strong scaling) and partial outputs are merged by LSE after an
-    NCCL all-gather."""
-    import torch.distributed as dist
-
+    NCCL all-gather.  Returns the record on rank 0 (None elsewhere)."""
     from fsa_preview.module import FlashSparseAttentionDecodeKernel, GraphedShardedAttention, GraphedStep
     from fsa_preview.ops.decode import CudaDecodeOps, DecodeStepPlan, nsa_decode_attention, nsa_decode_mixed, shard_plan
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    rank, world, dev, dist = dd.rank, dd.world, dd.dev, dd.dist
+    barrier, timed = dd.barrier, dd.timed
     c = dict(DECODE_CFG)
     if args.case == "small":
         c.update(batch=8)                   # 4.3 GB of cache: small enough for a profiler capture, larger than L2
@@ -258,30 +328,12 @@ def run_decode(args, rank, world, local_rank):
             eager_step()
         step = graph.replay
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, n):
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        ev0.record()
-        for _ in range(n):
-            fn()
-        ev1.record()
-        barrier()
-        t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / n
-
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
             step()
-        sampler = ClockSampler(local_rank)
+        sampler = ClockSampler(dev.index)
         sampler.start()
-        ms_step = timed(step, args.steps)
+        ms_step = timed(step, steps)
         clocks = sampler.stop()
         # dominant kernel alone: the compressed branch's partial pass (all visible compressed K/V rows of this rank)
         ops = CudaDecodeOps()
@@ -298,7 +350,7 @@ def run_decode(args, rank, world, local_rank):
         g_cmp = torch.cuda.CUDAGraph()                    # replayed, so that the host cost of a launch is not in the figure
         with torch.cuda.graph(g_cmp, capture_error_mode="thread_local"):
             cmp_pass()
-        ms_cmp = timed(g_cmp.replay, args.steps)
+        ms_cmp = timed(g_cmp.replay, steps)
 
         # end to end: host q / k_new / v_new in, output row out, through the module's step (append + attention + gate mix)
         gstep = GraphedStep(mod.step, cache, [qd, knh.to(dev), vnh.to(dev)]) if use_graph and world == 1 else None
@@ -313,22 +365,36 @@ def run_decode(args, rank, world, local_rank):
                 y = mod.step(qh.to(dev, non_blocking=True), knh.to(dev, non_blocking=True), vnh.to(dev, non_blocking=True), cache)
             y_host.copy_(y, non_blocking=True)
 
-        e2e_n = 0 if args.no_e2e else max(1, min(args.steps, margin // 2 - 4))
+        e2e_n = 0 if args.no_e2e else max(1, min(steps, margin // 2 - 4))
         if e2e_n:
             e2e_step()
             e2e_ms = timed(e2e_step, e2e_n)
+    # the two packed all-gathers of the sharded step, alone (same message sizes: o + lse + local score rows, then the
+    # selected and window partials)
+    ag_ms = None
+    if world > 1:
+        max_cmp = (max_len - ks_) // st_ + 1
+        ld = 1024 * -(-max(min(max_cmp, shard.cmp_hi - shard.cmp_lo), 1) // 1024)
+        m1 = torch.empty(B * Hq * (d + 1) + B * Hk * ld, dtype=torch.float32, device=dev)
+        m2 = torch.empty(2 * B * Hq * (d + 1), dtype=torch.float32, device=dev)
+        g1 = torch.empty(world * m1.numel(), dtype=torch.float32, device=dev)
+        g2 = torch.empty(world * m2.numel(), dtype=torch.float32, device=dev)
+
+        def gathers():
+            dist.all_gather_into_tensor(g1, m1)
+            dist.all_gather_into_tensor(g2, m2)
+
+        gathers()
+        ag_ms = timed(gathers, max(steps, 5))
     elem = 2
     T, BK, W = c["topk"], c["block_size"], c["window_size"]
     bytes_cmp = B * Hk * n_cmp * d * elem * 2
     bytes_sel = B * Hk * T * BK * d * elem * 2
     bytes_win = B * Hk * (W + 1) * d * elem * 2
     bytes_step = bytes_cmp + bytes_sel + bytes_win
+    line = None
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
+        peaks = load_peaks()
         peak = float(peaks.get("hbm_gbs", 0) or 0)
         src = "MEASURED_PEAKS.json hbm_gbs"
         if not peak:
@@ -341,13 +407,15 @@ def run_decode(args, rank, world, local_rank):
             cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                    "sample": f"decode oracle, one sequence with a {n}-token cache, one step ({dt:.2f} s); cost grows with the cache length"}
         line = {
-            "metric": DECODE_METRIC, "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "metric": DECODE_METRIC, "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded N(0,1) cache and query)",
             "config": {"workload": f"decode: batch {B} x {Lc}-token cache" + (" (small case)" if args.case == "small" else ""),
                        "parallelism": f"kv-sequence shards x{world}, LSE merge after all-gather" if world > 1 else "one GPU",
                        "l2": "the cache read per step exceeds L2", "algorithmic_bytes_per_step": bytes_step,
                        "step_gbs": bytes_step / world / (ms_step * 1e-3) / 1e9},
+            "tokens_per_s": B / (ms_step * 1e-3), "step_gbs": bytes_step / world / (ms_step * 1e-3) / 1e9,
+            "frac_hbm": bytes_step / world / (ms_step * 1e-3) / 1e9 / peak, "allgather_ms": ag_ms,
             "roofline": {"bound": "hbm", "kernel": "decode_partial_tma (compressed branch)", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_DECODE_B8 * B / 8 / world,
@@ -356,12 +424,12 @@ def run_decode(args, rank, world, local_rank):
             "e2e": ({"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": (qh.numel() + knh.numel() + vnh.numel()) * 2, "d2h_bytes_per_step": B * Hq * d * 2}
                     if e2e_n else None),
-            "gpu_launches": (7 if world == 1 else 9) * args.steps, "cuda_graph": use_graph,
+            "gpu_launches": (7 if world == 1 else 9) * steps, "cuda_graph": use_graph,
             "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    del cache, mod
+    torch.cuda.empty_cache()
+    return line
 
 
 LAYER_CFG = dict(hidden=4096, Hq=32, Hk=8, d=128, kernel_size=32, kernel_stride=16, block_size=64, topk=16, init_blocks=1,
@@ -369,20 +437,65 @@ LAYER_CFG = dict(hidden=4096, Hq=32, Hk=8, d=128, kernel_size=32, kernel_stride=
 LAYER_METRIC = "NSA layer fwd+bwd tokens/s (2x32768 tok, hidden 4096, 32 Q / 8 KV heads, d=128, ks=32/16, B_K=64, T=16, W=512)"
 
 
-def run_layer(args, rank, world, local_rank):
+def layer_useful_flops(c, seqlens):
+    """Algorithmic FLOPs of one forward + backward of the layer: projections (2 * tokens * in * out, x3 for forward,
+    dX and dW), the three attention branches on their attended (query head, token, key) triples (4 * d forward,
+    10 * d backward per triple), the two compressors (x3)."""
+    N = sum(seqlens)
+    hid, Hq, Hk, d = c["hidden"], c["Hq"], c["Hk"], c["d"]
+    ks, st, bs, T, W = c["kernel_size"], c["kernel_stride"], c["block_size"], c["topk"], c["window_size"]
+    proj = 2 * N * hid * (Hq * d + 2 * Hk * d) + 2 * N * (Hq * d) * hid + 2 * N * hid * 3
+    p_cmp = p_sel = p_win = ncmp = 0
+    for L in seqlens:
+        ncmp += (L - ks) // st + 1 if L >= ks else 0
+        for t in range(L):
+            p_cmp += min((t - (ks - 1)) // st + 1, (L - ks) // st + 1) if t >= ks - 1 else 0
+            p_win += min(t, W) + 1
+        for b in range((L + bs - 1) // bs):
+            n_tok = min(bs, L - b * bs)
+            n_t = min(T, b + 1)
+            p_sel += n_tok * (n_t - 1) * bs + n_tok * (n_tok + 1) // 2
+    attn = 14 * d * Hq * (p_cmp + p_sel + p_win)
+    compress = 3 * 2 * (2 * ncmp * Hk * (ks * d) * d)
+    return 3 * proj + attn + compress
+
+
+def layer_cpu_baseline(threads, n_tokens=512):
+    """The layer oracle (forward only) on one short sequence with the layer's dimensions."""
+    from fsa.module.rope import RopeConfig, compute_inv_freq
+    from oracle.nsa_layer_oracle import layer_forward_ref
+
+    c = LAYER_CFG
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(9)
+    Hq, Hk, d, hid = c["Hq"], c["Hk"], c["d"], c["hidden"]
+    params = {
+        "proj_q.weight": torch.randn(Hq * d, hid, generator=g) * 0.02, "proj_k.weight": torch.randn(Hk * d, hid, generator=g) * 0.02,
+        "proj_v.weight": torch.randn(Hk * d, hid, generator=g) * 0.02, "proj_o.weight": torch.randn(hid, Hq * d, generator=g) * 0.02,
+        "compress_key": torch.randn(Hk, c["kernel_size"] * d, d, generator=g) * 0.02,
+        "compress_value": torch.randn(Hk, c["kernel_size"] * d, d, generator=g) * 0.02,
+        "intra_block_pe": torch.randn(Hk, c["kernel_size"], d, generator=g) * 0.02, "gate.0.weight": torch.randn(3, hid, generator=g) * 0.02,
+    }
+    x = torch.randn(n_tokens, hid, generator=g).to(torch.bfloat16)
+    cfg = dict(num_q_heads=Hq, num_kv_heads=Hk, head_dim=d, kernel_size=c["kernel_size"], kernel_stride=c["kernel_stride"],
+               block_size=c["block_size"], topk=c["topk"], init_blocks=c["init_blocks"], local_blocks=c["local_blocks"],
+               window_size=c["window_size"])
+    inv = compute_inv_freq(RopeConfig(max_position_embeddings=131072, head_dim=d, rope_theta=c["rope_theta"]))
+    t0 = time.perf_counter()
+    layer_forward_ref(params, x, [n_tokens], cfg, inv)
+    dt = time.perf_counter() - t0
+    return n_tokens / dt, dt
+
+
+def run_layer(args, dd, steps, sub=False):
     """Forward + backward of the whole FlashSparseAttention layer.  With N > 1 the heads are split over the ranks
     (8/N KV heads and 32/N query heads each: the attention kernels need no collective); the layer output and the
-    gradient of the input are summed over the ranks with one NCCL all-reduce each, as any head-parallel layer does."""
-    import torch.distributed as dist
-
+    gradient of the input are summed over the ranks with one NCCL all-reduce each, as any head-parallel layer does.
+    Returns the record on rank 0 (None elsewhere)."""
     from fsa.module.fsa import FlashSparseAttention, RopeConfig
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    rank, world, dev, dist = dd.rank, dd.world, dd.dev, dd.dist
+    timed = dd.timed
     c = dict(LAYER_CFG)
     if args.case == "small":
         c["seqlens"] = [8192, 8192]
@@ -415,91 +528,81 @@ def run_layer(args, rank, world, local_rank):
         layer.zero_grad(set_to_none=True)
         return y, x.grad
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, n):
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        ev0.record()
-        for _ in range(n):
-            fn()
-        ev1.record()
-        barrier()
-        t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / n
-
     for _ in range(max(args.warmup, 3)):
         step()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(dev.index)
     sampler.start()
-    ms_step = timed(step, args.steps)
+    ms_step = timed(step, steps)
     clocks = sampler.stop()
+
+    # the two all-reduces of a step, alone (layer output and dX, [tokens, hidden] bf16 each)
+    ar_ms = None
+    if world > 1:
+        buf = torch.empty_like(xd)
+
+        def reduces():
+            dist.all_reduce(buf)
+            dist.all_reduce(buf)
+
+        reduces()
+        ar_ms = timed(reduces, 3)
 
     def e2e_step():
         y, gx = step(xh.to(dev, non_blocking=True), dyh.to(dev, non_blocking=True))
         return torch.stack([y.float().norm(), gx.float().norm()]).cpu()
 
-    e2e_n = 0 if args.no_e2e else max(1, min(args.steps, 3))
+    e2e_n = 0 if args.no_e2e else max(1, min(steps, 3))
     if e2e_n:
         e2e_step()
         e2e_ms = timed(e2e_step, e2e_n)
+    line = None
     if rank == 0:
+        flops = layer_useful_flops(c, seqlens)
+        peak, peak_src = tensor_peak(burst=False)       # a step of tens of milliseconds, dozens of them back to back
+        achieved = flops / world / (ms_step * 1e-3) / 1e12
+        cpu = None
+        if not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tps, dt = layer_cpu_baseline(threads)
+            cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                   "sample": f"layer oracle, forward only, one 512-token sequence with the layer's dimensions ({dt:.1f} s)"}
         line = {
-            "metric": LAYER_METRIC, "value": N / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "metric": LAYER_METRIC, "value": N / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded N(0,1) hidden states, N(0,0.02) weights)",
             "config": {"workload": f"layer fwd+bwd: {len(seqlens)}x{seqlens[0]} tokens" + (" (small case)" if args.case == "small" else ""),
                        "parallelism": f"head-parallel x{world}: {c['Hk'] // world} KV heads per GPU, all-reduce of the output and of dX only",
-                       "l2": "activations exceed L2"},
-            "roofline": None, "cpu_baseline": None,
+                       "l2": "activations exceed L2", "useful_flops_per_step": flops},
+            "tokens_per_s": N / (ms_step * 1e-3), "parallelism": f"head-parallel x{world}", "allreduce_ms": ar_ms,
+            "roofline": {"bound": "tensor", "kernel": "whole step (library GEMMs + attention kernels)", "achieved": achieved,
+                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src},
+            "cpu_baseline": cpu,
             "e2e": ({"value": N / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": 2 * xh.numel() * 2, "d2h_bytes_per_step": 8} if e2e_n else None),
             "gpu_launches": None, "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    del layer
+    torch.cuda.empty_cache()
+    return line
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="sel_attn", choices=["sel_attn", "decode", "layer"],
-                    help="sel_attn (default): selected attention fwd+bwd, the headline; decode: one NSA decode step; "
-                         "layer: the whole NSA layer fwd+bwd")
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="cfg1", choices=["cfg1", "small", "cfg2"],
-                    help="small = one 16384-token sequence of cfg1 (a quarter of it), for profiler captures; "
-                         "cfg2 = one 65536-token sequence, 4 KV heads, --group / --head-dim (the GQA sweep)")
-    ap.add_argument("--group", type=int, default=2, help="cfg2: GQA group size (1..16)")
-    ap.add_argument("--head-dim", type=int, default=128, help="cfg2: 128 or 256")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="decode workload: launch the step's kernels one by one")
-    args = ap.parse_args()
+def shard_config1(rank, world, seqlens, Hk):
+    """The (sequence, kv head) pairs of config 1 dealt to the ranks: by kv head while there are heads to deal, then by
+    sequence.  Returns (kv heads of this rank, sequence indices of this rank)."""
+    if world <= Hk:
+        if Hk % world:
+            raise SystemExit(f"--gpus must divide the {Hk} KV heads or be a multiple of them")
+        per = Hk // world
+        return list(range(rank * per, (rank + 1) * per)), list(range(len(seqlens)))
+    if world % Hk or len(seqlens) % (world // Hk):
+        raise SystemExit(f"--gpus {world}: cannot deal {Hk} KV heads x {len(seqlens)} sequences evenly")
+    m = world // Hk
+    per = len(seqlens) // m
+    return [rank // m], list(range((rank % m) * per, (rank % m + 1) * per))
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
-    if args.workload == "decode":
-        run_decode(args, rank, world, local_rank)
-        return
-    if args.workload == "layer":
-        run_layer(args, rank, world, local_rank)
-        return
-
-    import torch.distributed as dist
+def run_sel(args, dd):
+    """The headline: selected attention forward + backward on config 1 (or --case small / cfg2)."""
     from ctypes import byref, c_float, c_int
 
     from fsa import _lib
@@ -507,27 +610,34 @@ def main():
     from fsa.ops.FSA_topk_sparse_attention import sel_attn_bwd, sel_attn_fwd
     from fsa.synthetic import make_cu_seqlens, make_qkv, make_topk_idx
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
+    rank, world, dev, dist = dd.rank, dd.world, dd.dev, dd.dist
+    barrier = dd.barrier
     L = _lib.lib()
     seqlens, Hk, G, d, bs, T = (CFG[k] for k in ("seqlens", "Hk", "G", "d", "bs", "T"))
     if args.case == "small":
         seqlens = seqlens[:1]
     if args.case == "cfg2":
         seqlens, G, d = [65536], args.group, args.head_dim
-    N = sum(seqlens)
     scale = d ** -0.5
-    # each rank owns one 4-KV-head shard with its own seed
-    q, k, v, do = make_qkv(N, Hk * G, Hk, d, 43 + rank)
-    idx = make_topk_idx(seqlens, Hk, T, bs, 43 + rank)
-    cu = make_cu_seqlens(seqlens)
-    P = analytic_pairs(seqlens, Hk, G, bs, T)
-    flops_step = 14 * d * P
+    # the whole problem from one seed on every rank, then this rank's (sequence, kv head) pairs of it
+    N_all = sum(seqlens)
+    q, k, v, do = make_qkv(N_all, Hk * G, Hk, d, 43)
+    idx = make_topk_idx(seqlens, Hk, T, bs, 43)
+    flops_step = 14 * d * analytic_pairs(seqlens, Hk, G, bs, T)          # of the WHOLE problem
+    P_all = analytic_pairs(seqlens, Hk, G, bs, T)
+    if world > 1:
+        heads, seqs = shard_config1(rank, world, seqlens, Hk)
+        starts = [sum(seqlens[:i]) for i in range(len(seqlens))]
+        tok = torch.cat([torch.arange(starts[i], starts[i] + seqlens[i]) for i in seqs])
+        qh = [h * G + g for h in heads for g in range(G)]
+        q, do = q[tok][:, qh].contiguous(), do[tok][:, qh].contiguous()
+        k, v = k[tok][:, heads].contiguous(), v[tok][:, heads].contiguous()
+        idx = idx[heads][:, tok].contiguous()
+        seqlens_r, Hk_r = [seqlens[i] for i in seqs], len(heads)
+    else:
+        seqlens_r, Hk_r = seqlens, Hk
+    P_r = analytic_pairs(seqlens_r, Hk_r, G, bs, T)
+    cu = make_cu_seqlens(seqlens_r)
     host = [x.pin_memory() for x in (q, k, v, do, idx)]
     qd, kd, vd, dod, idxd = (x.to(dev) for x in host)
     cud = cu.to(dev)
@@ -536,16 +646,11 @@ def main():
         o, lse, ws = sel_attn_fwd(qd, kd, vd, idxd, bs, cud, scale)
         return sel_attn_bwd(qd, kd, vd, o, lse, dod, idxd, bs, cud, scale, ws)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(dev.index)
     L.fsa_profile_enable(1)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.start()
@@ -556,21 +661,15 @@ def main():
     ev1.record()
     barrier()
     clocks = sampler.stop()
-    ms_total = ev0.elapsed_time(ev1)
-    # per-kernel durations recorded inside the timed region
+    ms_step = dd.max_ms(ev0.elapsed_time(ev1)) / args.steps
+    # per-kernel durations recorded inside the timed region (library-owned events around each launch, this rank's)
     kern = {}
-    for name, kid in (("sel_fwd_main", 0), ("sel_fwd_reduce", 1), ("sel_bwd_main", 2), ("sel_bwd_dq_reduce", 3)):
+    for name, kid in (("sel_fwd_main", 0), ("sel_fwd_reduce", 1), ("sel_bwd_main", 2), ("sel_bwd_dq_reduce", 3), ("sel_index_build", 4)):
         ms, n = c_float(0), c_int(0)
         _lib.check(L.fsa_profile_read(kid, byref(ms), byref(n)), "fsa_profile_read")
         kern[name] = {"ms_avg": (ms.value / n.value if n.value else None), "launches": n.value}
     L.fsa_profile_enable(0)
-
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    ms_step = ms_max / args.steps
-    value = world * flops_step / (ms_step * 1e-3) / 1e12
+    value = flops_step / (ms_step * 1e-3) / 1e12
 
     # ---- end to end through the public operator, host buffers in, scalar results out.  Every step copies its inputs
     # from pinned host memory and reads its result back; the copies of step i + 1 run on a second stream into a second
@@ -594,11 +693,11 @@ def main():
         b = i % 2
         cur = torch.cuda.current_stream()
         cur.wait_event(copied[b])
-        qh, kh, vh, doh, ih = dev_bufs[b]
-        qh, kh, vh = (x.detach().requires_grad_(True) for x in (qh, kh, vh))
-        o = FSA_topk_sparse_attention(qh, kh, vh, ih, bs, cud, scale)
-        o.backward(doh)
-        res_host[b].copy_(torch.stack([qh.grad.float().norm(), kh.grad.float().norm(), vh.grad.float().norm()]), non_blocking=True)
+        qh_, kh_, vh_, doh_, ih_ = dev_bufs[b]
+        qh_, kh_, vh_ = (x.detach().requires_grad_(True) for x in (qh_, kh_, vh_))
+        o = FSA_topk_sparse_attention(qh_, kh_, vh_, ih_, bs, cud, scale)
+        o.backward(doh_)
+        res_host[b].copy_(torch.stack([qh_.grad.float().norm(), kh_.grad.float().norm(), vh_.grad.float().norm()]), non_blocking=True)
         consumed[b].record(cur)
 
     def e2e_run(n):
@@ -608,68 +707,108 @@ def main():
                 issue_copy(i + 1)
             compute(i)
 
-    if args.no_e2e:
-        e2e_steps = 0
-    else:
+    e2e_ms = None
+    if not args.no_e2e:
         e2e_run(2)
-    barrier()
-    ev0.record()
-    copy_stream.wait_event(ev0)
-    e2e_run(e2e_steps)
-    ev1.record()
-    barrier()
-    e2e_steps = max(e2e_steps, 1)
-    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
-    h2d = sum(x.numel() * x.element_size() for x in host)
+        barrier()
+        ev0.record()
+        copy_stream.wait_event(ev0)
+        e2e_run(e2e_steps)
+        ev1.record()
+        barrier()
+        e2e_ms = dd.max_ms(ev0.elapsed_time(ev1)) / e2e_steps
+    h2d = sum(x.numel() * x.element_size() for x in host) * world       # all ranks' shards: the whole problem
 
+    line = None
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak_tf = float(peaks.get("bf16_tflops_sustained", 0) or 0)
-        peak_src = "MEASURED_PEAKS.json bf16_tflops_sustained (kernel timed inside a long step)"
-        if not peak_tf:
-            peak_tf, peak_src = 1400.0, "fallback (sustained cuBLAS bf16 on this pool)"
-        # dominant kernel: the backward main kernel (10*d*P useful FLOPs per launch)
+        # the timed region is tens of milliseconds at full clocks: the burst figure is the denominator
+        peak_tf, peak_src = tensor_peak(burst=True)
+        # dominant kernel: the backward main kernel (10*d*P useful FLOPs per launch, P of this rank's shard)
         dom = "sel_bwd_main" if (kern["sel_bwd_main"]["ms_avg"] or 0) >= (kern["sel_fwd_main"]["ms_avg"] or 0) else "sel_fwd_main"
-        dom_flops = (10 if dom == "sel_bwd_main" else 4) * d * P
+        dom_flops = (10 if dom == "sel_bwd_main" else 4) * d * P_r
         dom_ms = kern[dom]["ms_avg"]
         achieved = dom_flops / (dom_ms * 1e-3) / 1e12 if dom_ms else None
         cpu = None
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            n_tok = 2048
-            tf, dt, _ = cpu_baseline_sample(n_tok, threads)
+            tf, dt = cpu_baseline_config0(threads)
             cpu = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
-                   "sample": f"fp32 oracle fwd+bwd on the first {n_tok} tokens of one cfg1 sequence ({dt:.1f} s)"}
+                   "sample": f"fp32 oracle FORWARD on config 0 (1x8192 tokens, 4 KV heads, G=1), best of 3 ({dt:.1f} s), on 4*d*P useful FLOPs"}
+        wl = workload_name() if args.case == "cfg1" else ("small: 1x16384 tokens of cfg1" if args.case == "small" else
+                                                          f"cfg2: 1x65536 tokens, 4 KV heads, G={G}, d={d}, B_K=64, T=16, fwd+bwd")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded N(0,1) q/k/v/dO, seeded causal block ids)",
-            "config": {"workload": workload_name() if args.case == "cfg1" else ("small: 1x16384 tokens of cfg1" if args.case == "small" else
-                                    f"cfg2: 1x65536 tokens, 4 KV heads, G={G}, d={d}, B_K=64, T=16, fwd+bwd"), "parallelism": f"kv-head shards x{world}, no collective",
+            "config": {"workload": wl,
+                       "parallelism": (f"the problem's (sequence, kv head) pairs dealt to {world} GPUs "
+                                       f"({Hk_r} kv head(s) x {len(seqlens_r)} sequence(s) each), no collective") if world > 1 else "one GPU",
                        "l2": "inputs and partial buffers exceed L2 (q 134 MB, partials > 4 GB per step)",
-                       "useful_flops_per_step": flops_step, "tokens_per_s": world * N / (ms_step * 1e-3)},
+                       "useful_flops_per_step": flops_step, "tokens_per_s": N_all / (ms_step * 1e-3)},
             "kernels": kern,
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (achieved / peak_tf if achieved else None),
-                         "traffic": (NCU_TRAFFIC_SMALL[dom] * (4 if args.case == "cfg1" else 1)) if args.case != "cfg2" else None,
+                         "traffic": (NCU_TRAFFIC_SMALL[dom] * (4 if args.case == "cfg1" else 1) * P_r / P_all) if args.case != "cfg2" else None,
                          "traffic_source": "ncu capture of the small case scaled by the token count", "peak_source": peak_src},
             "cpu_baseline": cpu,
-            "e2e": {"value": world * flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12,
-                    "overlap": "copies of step i+1 on a second stream while step i computes"},
-            "gpu_launches": 10 * args.steps,
+            "e2e": ({"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12 * world,
+                     "overlap": "copies of step i+1 on a second stream while step i computes"} if e2e_ms else None),
+            "gpu_launches": 13 * args.steps,
             "clocks": clocks,
         }
+    del qd, kd, vd, dod, idxd, dev_bufs, host
+    torch.cuda.empty_cache()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="sel_attn", choices=["sel_attn", "decode", "layer"],
+                    help="sel_attn (default): selected attention fwd+bwd, the headline, with the layer and the decode step as "
+                         "sub-records; decode: one NSA decode step alone; layer: the whole NSA layer fwd+bwd alone")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default="cfg1", choices=["cfg1", "small", "cfg2"],
+                    help="small = one 16384-token sequence of cfg1 (a quarter of it), for profiler captures; "
+                         "cfg2 = one 65536-token sequence, 4 KV heads, --group / --head-dim (the GQA sweep)")
+    ap.add_argument("--group", type=int, default=2, help="cfg2: GQA group size (1..16)")
+    ap.add_argument("--head-dim", type=int, default=128, help="cfg2: 128 or 256")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sub", action="store_true", help="sel_attn workload: skip the layer and decode sub-records")
+    ap.add_argument("--no-graph", action="store_true", help="decode workload: launch the step's kernels one by one")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    dd = Dist(rank, world, local_rank)
+    if args.workload == "decode":
+        line = run_decode(args, dd, args.steps)
+    elif args.workload == "layer":
+        line = run_layer(args, dd, args.steps)
+    else:
+        line = run_sel(args, dd)
+        if not args.no_sub and args.case == "cfg1":
+            # the quantities the reference's headline also names, measured in the same process group
+            sub_l = run_layer(args, dd, max(2, min(args.steps, 5)), sub=True) if LAYER_CFG["Hk"] % world == 0 else None
+            sub_d = run_decode(args, dd, args.steps, sub=True)
+            if rank == 0:
+                keep_l = ("tokens_per_s", "ms_per_step", "n_gpus", "parallelism", "allreduce_ms", "roofline", "cpu_baseline", "e2e", "config")
+                keep_d = ("tokens_per_s", "ms_per_step", "n_gpus", "step_gbs", "frac_hbm", "allgather_ms", "roofline", "cpu_baseline", "e2e",
+                          "config", "cuda_graph")
+                line["layer"] = {k: sub_l[k] for k in keep_l} if sub_l else None
+                line["decode"] = {k: sub_d[k] for k in keep_d} if sub_d else None
+    if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    dd.close()
 
 
 if __name__ == "__main__":

@@ -53,6 +53,23 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, i
     return FSA_OK;
 }
 
+// 3-D map over 16-bit elements: dims {d0 (contiguous), d1, d2}, strides of d1 and d2 in ELEMENTS (multiples of 8; they may
+// overlap), box {64, box1, 1}, 128-byte swizzle.  Coordinates past a dimension read as zero.
+int make_tile_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t d0, int64_t d1, int64_t d2, int64_t stride1,
+                     int64_t stride2, int box1) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return cuda_fail(cudaErrorNotSupported);
+    cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)(d1 > 0 ? d1 : 1), (cuuint64_t)(d2 > 0 ? d2 : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)stride1 * 2, (cuuint64_t)stride2 * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box1, 1};
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = fn(map, dtype == FSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail_at(cudaErrorInvalidValue, -(int)r - 100000);   // driver error code, negated
+    return FSA_OK;
+}
+
 int device_sm_count(int* out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

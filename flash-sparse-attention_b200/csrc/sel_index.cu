@@ -23,8 +23,8 @@ namespace fsa {
 constexpr int kIdxMaxWarps = 16;
 constexpr int kIdxMaxSlots = 16;   // top-k lists up to this length are held in registers
 
-// Count (FILL = false: hw[gb] += entries) or place (FILL = true: hw[gb] is this warp's next position inside the key,
-// relative to the chunk's first) the entries of this warp's share of the chunk [n0, n1).
+// Count (FILL = false: hw[gb] += entries) or place (FILL = true: hw[gb] is this warp's next position in the
+// tile-ordered entry list) the entries of this warp's share of the chunk [n0, n1).
 template <bool FILL>
 __device__ __forceinline__ void chunk_pass(const int* __restrict__ topk_idx, const int* __restrict__ cu, const SelBounds& bd,
                                            const SelShape& s, const SelIndex& ix, int h, int c, int n0, int n1, int* hw, int warp,
@@ -35,8 +35,6 @@ __device__ __forceinline__ void chunk_pass(const int* __restrict__ topk_idx, con
     const bool list = bd.kv_hi == nullptr;
     const bool in_regs = list && s.T <= kIdxMaxSlots && (s.T & 3) == 0 && (reinterpret_cast<uintptr_t>(topk_idx) & 15) == 0;
     const unsigned lt = (1u << lane) - 1;
-    const int* kt = ix.key_tile + (int64_t)h * s.NBmax;
-    const int* cc = ix.chunk_cnt + ((int64_t)h * s.NC + c) * s.NBmax;
     for (int g = g_lo; g < g_hi; ++g) {
         const int n = n0 + g * 32 + lane;
         const bool active = n < n1;
@@ -73,8 +71,6 @@ __device__ __forceinline__ void chunk_pass(const int* __restrict__ topk_idx, con
                 if (!FILL) {
                     if (gb >= 0 && lane == leader) {
                         hw[gb] += __popc(m);
-                        ix.row0[gb] = r0;          // every writer stores the same values
-                        ix.nrow[gb] = min(s.BK, tc.ke - r0);
                     }
                 } else {
                     int base = 0;
@@ -86,7 +82,7 @@ __device__ __forceinline__ void chunk_pass(const int* __restrict__ topk_idx, con
                     if (active) {
                         int ps = -1;
                         if (gb >= 0) {
-                            ps = __ldg(kt + gb) * s.TPT + __ldg(cc + gb) + base + __popc(m & lt);
+                            ps = base + __popc(m & lt);
                             ix.entries[ps] = ((uint32_t)n << kSlotBits) | (uint32_t)sl;
                         }
                         if (in_regs) ids[j] = ps;      // the slot's id is used up: keep its position, written as whole rows below
@@ -118,11 +114,13 @@ __global__ void __launch_bounds__(kIdxMaxWarps * 32) sel_index_chunk(const int* 
     chunk_pass<false>(topk_idx, cu, bd, s, ix, h, c, n0, n1, sm + warp * s.NBmax, warp, nwarps, lane);
     __syncthreads();
     int* cc = ix.chunk_cnt + ((int64_t)h * s.NC + c) * s.NBmax;
+    const int* kt = ix.key_tile + (int64_t)h * s.NBmax;
     for (int gb = tid; gb < s.NBmax; gb += nthreads) {
-        int run = 0;
+        // FILL: first position of the key's entries + the chunk's first position inside the key (steps 2 and 3)
+        int run = FILL ? kt[gb] * s.TPT + cc[gb] : 0;
         for (int i = 0; i < nwarps; ++i) {
             const int v = sm[i * s.NBmax + gb];
-            sm[i * s.NBmax + gb] = run;        // this warp's first position inside the key, relative to the chunk
+            sm[i * s.NBmax + gb] = run;        // this warp's first position inside the key
             run += v;
         }
         if (!FILL) cc[gb] = run;
@@ -133,17 +131,22 @@ __global__ void __launch_bounds__(kIdxMaxWarps * 32) sel_index_chunk(const int* 
     }
 }
 
-// Step 2: per key, exclusive prefix of the chunks' counts and the total.
-__global__ void __launch_bounds__(256) sel_index_keys(SelShape s, SelIndex ix) {
+// Step 2: per key, exclusive prefix of the chunks' counts and the total (thread per key; eight loads in flight).
+__global__ void __launch_bounds__(64) sel_index_keys(SelShape s, SelIndex ix) {
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= s.Hk * s.NBmax) return;
     const int h = k / s.NBmax, gb = k - h * s.NBmax;
     int* p = ix.chunk_cnt + (int64_t)h * s.NC * s.NBmax + gb;
     int run = 0;
-    for (int c = 0; c < s.NC; ++c) {
-        const int v = p[(int64_t)c * s.NBmax];
-        p[(int64_t)c * s.NBmax] = run;
-        run += v;
+    for (int c0 = 0; c0 < s.NC; c0 += 8) {
+        int v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = c0 + j < s.NC ? p[(int64_t)(c0 + j) * s.NBmax] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (c0 + j < s.NC) p[(int64_t)(c0 + j) * s.NBmax] = run;
+            run += v[j];
+        }
     }
     ix.key_cnt[k] = run;
 }
@@ -212,16 +215,28 @@ __global__ void __launch_bounds__(1024) sel_index_scan(SelShape s, SelIndex ix) 
     }
 }
 
-// Step 4: tile records and the padding of the tile-ordered entry list: one warp per key.
-__global__ void __launch_bounds__(256) sel_index_tiles(SelShape s, SelIndex ix) {
+// Step 4: tile records and the padding of the tile-ordered entry list: one warp per key.  The block's first K/V row
+// and its row count follow from the block id: gb = cu_k[b] / BK + b + j for block j of sequence b.
+__global__ void __launch_bounds__(256) sel_index_tiles(const int* __restrict__ cu, SelBounds bd, SelShape s, SelIndex ix) {
     const int lane = threadIdx.x & 31;
     const int hg = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (hg >= s.Hk * s.NBmax) return;
     const int cnt = ix.key_cnt[hg];
     if (cnt == 0) return;
     const int t0 = ix.key_tile[hg], nt = (cnt + s.TPT - 1) / s.TPT;
-    const int h = hg / s.NBmax;
-    const int row0 = ix.row0[hg - h * s.NBmax];
+    const int h = hg / s.NBmax, gb = hg - h * s.NBmax;
+    const int* ck = bd.cu_k ? bd.cu_k : cu;
+    int lo = 0, hi = s.B;   // largest b with cu_k[b] / BK + b <= gb
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(ck + mid) / s.BK + mid <= gb) lo = mid; else hi = mid;
+    }
+    const int k0 = __ldg(ck + lo), k1 = __ldg(ck + lo + 1);
+    const int row0 = k0 + (gb - (k0 / s.BK + lo)) * s.BK;
+    if (lane == 0) {
+        ix.row0[gb] = row0;                     // (the same values from every kv head)
+        ix.nrow[gb] = min(s.BK, k1 - row0);
+    }
     const int seg0 = ix.key_seg[hg];
     for (int t = lane; t < nt; t += 32) {
         ix.tile_rec[t0 + t] = make_int4(row0, min(s.TPT, cnt - t * s.TPT) | (h << 8), hg, seg0);
@@ -258,9 +273,9 @@ cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelBounds&
     const dim3 grid((unsigned)s.NC, (unsigned)s.Hk);
     const int HG = s.Hk * s.NBmax;
     sel_index_chunk<false><<<grid, nw * 32, smem, stream>>>(topk_idx, cu, bd, s, ix);
-    sel_index_keys<<<(unsigned)((HG + 255) / 256), 256, 0, stream>>>(s, ix);
+    sel_index_keys<<<(unsigned)((HG + 63) / 64), 64, 0, stream>>>(s, ix);
     sel_index_scan<<<1, 1024, 0, stream>>>(s, ix);
-    sel_index_tiles<<<(unsigned)((HG + 7) / 8), 256, 0, stream>>>(s, ix);
+    sel_index_tiles<<<(unsigned)((HG + 7) / 8), 256, 0, stream>>>(cu, bd, s, ix);
     sel_index_chunk<true><<<grid, nw * 32, smem, stream>>>(topk_idx, cu, bd, s, ix);
     return cudaGetLastError();
 }

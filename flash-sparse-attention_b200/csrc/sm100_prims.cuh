@@ -128,6 +128,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// 3-D tiled load: box starting at (x = innermost element, y, z).  x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
 // TMA gather4: four rows (y0..y3) of a 2-D tensor, box {cols, 1}, land in four consecutive
 // 128-byte rows of the destination (swizzled like a tiled load).
 __device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const CUtensorMap* map, int x, int y0, int y1, int y2, int y3,

@@ -1,9 +1,10 @@
 """Compressed-branch attention + top-k block selection with the reference's interface
 (``compressed_attention``, nsa_ref/ops/compressed_attention.py:1161-1317).
 
-The attention itself runs on the sm_100a range-attention kernels; the selection scores are the
-raw products of the first query head of each GQA group with the compressed keys (one batched
-library GEMM per sequence, 16-bit operands, fp32 accumulation and output) fed to the fused exp / block-score / top-k kernel.
+The attention itself runs on the sm_100a range-attention kernels.  The selection is one fused kernel
+(``fsa_select_topk_fused``: q.k^T on the tensor cores, probabilities, block scores, top-k, no score tensor in memory);
+shapes outside what that kernel is compiled for take the two-step path (a batched library GEMM per sequence writing the
+raw products in fp32, then ``fsa_select_topk_seq``).
 """
 from __future__ import annotations
 
@@ -15,6 +16,9 @@ import torch
 
 from fsa import _lib
 from fsa.ops.range_attention import compressed_attention_core
+
+
+_FUSED_TAPS = {(2, 2), (2, 4), (2, 8), (1, 4), (4, 4), (4, 8)}     # (kernel_size / stride, block_size / stride) the fused kernel is compiled for
 
 
 def select_topk_blocks(q, ck, lse, kernel_size, kernel_stride, block_size, topk, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
@@ -33,6 +37,19 @@ def select_topk_blocks(q, ck, lse, kernel_size, kernel_stride, block_size, topk,
         seqlens_k = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).tolist()
     out = torch.empty((Hk, N, t_out), dtype=torch.int32, device=q.device)
     lse = lse.contiguous()
+    a, bsr = kernel_size // kernel_stride, block_size // kernel_stride
+    fused_ok = (d in (64, 128) and t_out <= 32 and (a, bsr) in _FUSED_TAPS and kernel_size % kernel_stride == 0
+                and block_size % kernel_stride == 0)
+    if fused_ok:
+        qf = q if (q.stride(2) == 1 and q.stride(1) == d and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0) else q.contiguous()
+        kf = ck if (ck.stride(2) == 1 and ck.stride(1) == d and ck.stride(0) % 8 == 0 and ck.data_ptr() % 16 == 0) else ck.contiguous()
+        with torch.cuda.device(q.device):
+            rc = L.fsa_select_topk_fused(_lib.ptr(qf), qf.stride(0), _lib.ptr(kf) if kf.shape[0] else None, kf.stride(0) if kf.shape[0] else Hk * d,
+                                         _lib.ptr(lse), _lib.ptr(cu_seqlens_q), _lib.ptr(cu_seqlens_k), N, kf.shape[0], cu_seqlens_q.numel() - 1,
+                                         Hq, Hk, d, _lib.DTYPE_CODE[q.dtype], float(sm_scale), kernel_size, kernel_stride, block_size,
+                                         init_blocks, local_blocks, max_blocks, t_out, _lib.ptr(out), None, _lib.current_stream(q.device))
+        _lib.check(rc, "fsa_select_topk_fused")
+        return out
     qs = ks = 0
     with torch.cuda.device(q.device):
         for Lq, Lk in zip(seqlens_q, seqlens_k):

@@ -168,6 +168,35 @@ int fsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* 
                        void* dv, void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes,
                        void* stream);
 
+/* K/V compression forward: y[c, h, :] = sum_k x[s_b + c * stride + k, h, :] @ W[h, k*d:(k+1)*d, :] (+ bias[h, :]) for the
+ * n_b = floor((L_b - kernel_size) / stride) + 1 windows of every sequence (0 when L_b < kernel_size).  Replaces
+ * linear_compress_fwd_kernel (nsa_ref/ops/linear_compress.py:28-131, :334-398) and the bias add of :497-501; the token
+ * windows are read in place through a strided tensor map (no unfolded copy).
+ *   x [N, H, D] (row stride x_stride_n, head stride D), w [H, kernel_size * D, D] contiguous, bias [H, D] or NULL (added
+ *   to the rounded product in the activation dtype, as the reference does), seqlens_host [batch] HOST array of sequence
+ *   lengths, y [sum n_b, H, D] contiguous.  head_dim 64 or 128.  One launch per sequence.
+ *   status: a device int (zeroed by the caller) that receives a non-zero code if a bounded wait ran out, or NULL. */
+int fsa_linear_compress_fwd(const void* x, int64_t x_stride_n, const void* w, const void* bias, const int32_t* seqlens_host,
+                            int batch, int num_heads, int head_dim, int kernel_size, int kernel_stride, int dtype, void* y,
+                            int32_t* status, void* stream);
+
+/* Fused top-k block selection for a varlen batch: q.k^T on the tensor cores, probabilities, block scores and the ids
+ * in one kernel; no score tensor is written to memory.  Replaces _get_attention_score / score_kernel, transform_score /
+ * _transform_score_kernel and the topk + sort + mask tail (nsa_ref/ops/compressed_attention.py:833-1158, :1274-1315;
+ * per-KV-head path) -- the fusion the reference sketches in fsa/ops/fused_score_kernels.py:15-145.
+ *   q [N, Hq, D] (row stride q_stride_n, head stride D; the first head of every GQA group is used), cmp_k [Nc, Hk, D]
+ *   compressed keys (row stride k_stride_n, head stride D), lse [Hq, N] of the compressed branch (log2 units),
+ *   cu_seqlens_q / cu_seqlens_k [B + 1]; topk_idx [Hk, N, topk_out] int32: ascending sequence-local block ids, -1 padded.
+ *   Scores are rounded to bf16 as in the reference; ties go to the lower block index.  topk_out = min(topk, max_blocks)
+ *   <= 32, max_blocks = ceil(max_seqlen / block_size); head_dim 64 or 128; (kernel_size / stride, block_size / stride)
+ *   in {(2,2), (2,4), (2,8), (1,4), (4,4), (4,8)}, else FSA_ERR_UNSUPPORTED (use fsa_select_topk_seq).
+ *   status: a device int (zeroed by the caller) that receives a non-zero code if a bounded wait ran out, or NULL. */
+int fsa_select_topk_fused(const void* q, int64_t q_stride_n, const void* cmp_k, int64_t k_stride_n, const float* lse,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int64_t total_tokens, int64_t total_cmp,
+                          int batch, int num_q_heads, int num_kv_heads, int head_dim, int dtype, float sm_scale,
+                          int kernel_size, int kernel_stride, int block_size, int init_blocks, int local_blocks,
+                          int max_blocks, int topk_out, int32_t* topk_idx, int32_t* status, void* stream);
+
 /* Top-k block selection for one sequence.  Replaces _get_attention_score / score_kernel, transform_score /
  * _transform_score_kernel and the topk + sort + mask tail (nsa_ref/ops/compressed_attention.py:833-1158,
  * :1274-1315; per-KV-head path).

@@ -8,7 +8,8 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from fsa.ops.linear_compress import compressed_seqlens, linear_compress
+from fsa.ops.linear_compress import compressed_seqlens
+from fsa.ops.linear_compress import linear_compress_gemm as linear_compress   # CPU tensors: the library-GEMM formulation
 from fsa_preview.cache import DecodeCache
 from fsa_preview.ops.compat import _linear_compress_decode
 from fsa_preview.ops.decode import Shard, nsa_decode_attention, shard_plan

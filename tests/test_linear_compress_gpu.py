@@ -1,0 +1,64 @@
+"""The K/V compressor on the GPU (fsa_linear_compress_fwd through the operator) against the CPU oracle
+(oracle.nsa_layer_oracle.linear_compress_ref, which restates nsa_ref/ops/linear_compress.py:113-131, :334-346, :495-502).
+
+Tolerance: the kernel accumulates in fp32 and rounds once to the activation dtype (twice with the bias, as the reference
+does); against the fp32 oracle max-abs <= 2e-2 * max(1, |ref|max / 2), mean-abs <= 1e-3 * the same scale."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from fsa.ops.linear_compress import linear_compress, linear_compress_gemm
+from fsa.synthetic import make_cu_seqlens
+from oracle.nsa_layer_oracle import linear_compress_ref
+
+DEV = "cuda:0"
+
+
+def _tol_ok(got, ref, name):
+    err = (got.float().cpu() - ref).abs()
+    scale = max(1.0, float(ref.abs().max()) / 2.0)
+    assert float(err.max()) <= 2e-2 * scale, f"{name}: max-abs {float(err.max()):.3e} (ref max {float(ref.abs().max()):.2f})"
+    assert float(err.mean()) <= 1e-3 * scale, f"{name}: mean-abs {float(err.mean()):.3e}"
+
+
+@pytest.mark.parametrize("seqlens,H,d,ks,st,dtype,with_pe", [
+    ([300, 20, 1000], 2, 128, 32, 16, torch.bfloat16, True),       # a sequence shorter than one window
+    ([2100], 3, 128, 32, 16, torch.bfloat16, False),               # more than one tile of 128 windows
+    ([257, 513], 2, 64, 32, 16, torch.float16, True),
+    ([31], 1, 128, 32, 16, torch.bfloat16, True),                  # no window at all
+    ([700], 2, 128, 64, 32, torch.bfloat16, True),
+])
+def test_forward_backward_matches_oracle(seqlens, H, d, ks, st, dtype, with_pe):
+    N = sum(seqlens)
+    g = torch.Generator().manual_seed(7 + N)
+    # x as the layer produces it: a strided view of a fused projection output
+    fused = torch.randn(N, 2 * H * d, generator=g).to(dtype)
+    w = (torch.randn(H, ks * d, d, generator=g) * 0.02).to(dtype)
+    pe = (torch.randn(H, ks, d, generator=g) * 0.5).to(dtype) if with_pe else None
+    x = fused[:, H * d :].view(N, H, d)
+    cu = make_cu_seqlens(seqlens)
+    xf, wf = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    pf = pe.float().requires_grad_(True) if with_pe else None
+    y_ref, lens = linear_compress_ref(xf, wf, seqlens, ks, st, pf)
+    fc = fused.to(DEV).requires_grad_(True)
+    wc = w.to(DEV).requires_grad_(True)
+    pc = pe.to(DEV).requires_grad_(True) if with_pe else None
+    y, y_cu = linear_compress(fc[:, H * d :].view(N, H, d), wc, cu.to(DEV), ks, st, pc, seqlens)
+    assert y_cu.tolist() == [0] + list(torch.tensor(lens).cumsum(0).tolist())
+    assert y.shape == y_ref.shape
+    if y.numel() == 0:
+        return
+    _tol_ok(y, y_ref.detach(), "y")
+    # the library-GEMM formulation agrees too (same inputs, same rounding points)
+    y2, _ = linear_compress_gemm(x.to(DEV), w.to(DEV), cu.to(DEV), ks, st, pe.to(DEV) if with_pe else None, seqlens)
+    assert float((y.float() - y2.float()).abs().max()) <= 2e-2 * max(1.0, float(y_ref.abs().max()) / 2)
+    dy = torch.randn(y.shape, generator=g).to(dtype)
+    y.backward(dy.to(DEV))
+    y_ref.backward(dy.float())
+    _tol_ok(fc.grad[:, H * d :].reshape(N, H, d), xf.grad, "dx")
+    assert float(fc.grad[:, : H * d].abs().max()) == 0
+    gw = wc.grad.float().cpu()
+    assert float((gw - wf.grad).norm()) <= 2e-2 * float(wf.grad.norm()), "dw"
+    if with_pe:
+        assert float((pc.grad.float().cpu() - pf.grad).norm()) <= 3e-2 * float(pf.grad.norm()), "dpe"

@@ -206,3 +206,74 @@ def test_topk_selection_on_real_valued_scores():
             sc = orc.block_scores_ref(p, tt, ks, st, bs, 1, 2).sort(descending=True).values
             assert sc.numel() > T and float(sc[T - 1] - sc[T]) <= float(sc[T - 1]) * 2 ** -7, (h, tt, sc[T - 2 : T + 2])
     assert bad <= max(1, Hk * L // 500), f"{bad} of {Hk * L} rows differ from the oracle"
+
+
+@pytest.mark.parametrize("seqlens,Hk,G,d,ks,st,bs,T", [
+    ([900], 2, 2, 128, 32, 16, 64, 8),
+    ([300, 20, 700, 129], 1, 4, 128, 32, 16, 64, 16),      # a sequence with no compressed token, ragged tails
+    ([513, 400], 2, 1, 64, 32, 16, 32, 6),                  # 32-key blocks: taps [1, 2, 1]
+    ([2100], 1, 2, 128, 32, 16, 64, 16),                    # more than one tile of 128 compressed keys
+])
+def test_fused_topk_selection_against_oracle(seqlens, Hk, G, d, ks, st, bs, T):
+    """fsa_select_topk_fused (q.k^T inside the kernel) against the oracle fed fp32 products of the same bf16 inputs.
+    The products are exact in fp32 but the tensor core adds them in its own order, so a probability can differ in its
+    last bits and move a block score across a bf16 rounding boundary; rows whose ids differ must be rare and each must
+    be explained by a near-tie at the cut (or inside the selected set's boundary) of at most one bf16 step.  The
+    two-step path (library GEMM + fsa_select_topk_seq) must agree with the fused kernel at the same level."""
+    from fsa.ops import compressed_attention as ca
+
+    N, Hq = sum(seqlens), Hk * G
+    clens = [(L - ks) // st + 1 if L >= ks else 0 for L in seqlens]
+    g = torch.Generator().manual_seed(31 + N)
+    q = torch.randn(N, Hq, d, generator=g).to(torch.bfloat16)
+    ck = torch.randn(sum(clens), Hk, d, generator=g).to(torch.bfloat16)
+    scale = d ** -0.5
+    cu_q, cu_k = make_cu_seqlens(seqlens), make_cu_seqlens(clens)
+    # lse of the visible compressed keys per (first head of the group, token), fp32 on the host
+    lse = torch.full((Hq, N), float("-inf"))
+    qk_all = []
+    for b, (L, n) in enumerate(zip(seqlens, clens)):
+        qs, cs = int(cu_q[b]), int(cu_k[b])
+        per_h = []
+        for h in range(Hk):
+            qk = q[qs : qs + L, h * G].float() @ ck[cs : cs + n, h].float().t() if n else torch.zeros(L, 0)
+            per_h.append(qk)
+            if n:
+                t = torch.arange(L).view(L, 1)
+                c = torch.arange(n).view(1, n)
+                logits = (qk * (scale * 1.4426950408889634)).masked_fill(~(t >= c * st + ks - 1), float("-inf"))
+                lse[h * G, qs : qs + L] = torch.logsumexp(logits * math.log(2.0), -1) / math.log(2.0)
+        qk_all.append(per_h)
+    max_blocks = math.ceil(max(seqlens) / bs)
+    t_out = min(T, max_blocks)
+    args = (q.to(DEV), ck.to(DEV), lse.to(DEV), ks, st, bs, T, cu_q.to(DEV), cu_k.to(DEV), max(seqlens), scale, 1, 2, seqlens, clens)
+    got = ca.select_topk_blocks(*args).cpu()
+    saved = ca._FUSED_TAPS
+    ca._FUSED_TAPS = set()                     # the two-step path
+    try:
+        two_step = ca.select_topk_blocks(*args).cpu()
+    finally:
+        ca._FUSED_TAPS = saved
+    assert got.shape == (Hk, N, t_out)
+    bad = 0
+    for b, (L, n) in enumerate(zip(seqlens, clens)):
+        qs = int(cu_q[b])
+        for h in range(Hk):
+            qk, lse0 = qk_all[b][h], lse[h * G, qs : qs + L]
+            ref = orc.select_topk_ref(qk, lse0, L, n, scale, ks, st, bs, 1, 2, max_blocks, T)
+            rows = (got[h, qs : qs + L] != ref).any(-1).nonzero().flatten().tolist()
+            bad += len(rows)
+            for tt in rows:
+                nvis = min((tt - (ks - 1)) // st + 1, n) if tt >= ks - 1 else 0
+                p = torch.zeros(n)
+                p[:nvis] = torch.exp2(qk[tt, :nvis] * (scale * 1.4426950408889634) - lse0[tt])
+                sc = orc.block_scores_ref(p, tt, ks, st, bs, 1, 2)
+                # every id that differs has a score within one bf16 step of the score at the cut
+                srt = sc.sort(descending=True).values
+                cut = float(srt[min(t_out, sc.numel()) - 1])
+                diff = set(got[h, qs + tt].tolist()) ^ set(ref[tt].tolist())
+                for i in diff:
+                    assert i >= 0 and abs(float(sc[i]) - cut) <= max(cut, 1e-30) * 2 ** -6, (b, h, tt, i, float(sc[i]), cut)
+    assert bad <= max(2, Hk * N // 200), f"{bad} of {Hk * N} rows differ from the oracle"
+    agree = float((got == two_step).all(-1).float().mean())
+    assert agree >= 0.99, f"fused vs two-step rows identical: {agree:.4f}"

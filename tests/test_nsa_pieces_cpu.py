@@ -1,12 +1,13 @@
 """Host-side NSA pieces that need no GPU: rotary frequencies against the transformers golden vector,
-linear_compress (pure library ops) against the loop oracle, the top-k oracle's tie rule."""
+linear_compress_gemm (the library-GEMM formulation of the compressor) against the loop oracle, the top-k oracle's tie rule."""
 import os
 
 import numpy as np
 import torch
 
 from fsa.module.rope import RopeConfig, compute_inv_freq
-from fsa.ops.linear_compress import compressed_seqlens, linear_compress
+from fsa.ops.linear_compress import compressed_seqlens
+from fsa.ops.linear_compress import linear_compress_gemm as linear_compress   # CPU tensors: the library-GEMM formulation (the backward of the kernel path)
 from oracle.nsa_layer_oracle import linear_compress_ref, topk_from_block_scores
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
