@@ -151,7 +151,9 @@ static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, Se
     if ((int64_t)s->Hk * s->NBmax >= ((int64_t)1 << 30)) return FSA_ERR_UNSUPPORTED;
     if ((int64_t)s->Hk * s->NBmax * s->NC >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
     if (Hk > 65535) return FSA_ERR_UNSUPPORTED;
-    if (sel_index_warps(*s) == 0) return FSA_ERR_UNSUPPORTED;                             // a sequence of millions of blocks
+    s->IW = sel_index_warps(*s);
+    if (s->IW == 0) return FSA_ERR_UNSUPPORTED;                                           // a sequence of millions of blocks
+    if ((int64_t)s->Hk * s->NBmax * s->NC * s->IW >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;
     if (sel_max_tiles(*s) * kTileRows >= ((int64_t)1 << 31)) return FSA_ERR_UNSUPPORTED;  // partial rows are 32-bit
     return FSA_OK;
 }

@@ -453,34 +453,36 @@ __global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const ET* __restrict__ 
 template <typename ET>
 __global__ void __launch_bounds__(128) sel_bwd_dkdv_reduce(const float* __restrict__ slabs, SelShape s, SelIndex ix,
                                                            ET* __restrict__ dk, ET* __restrict__ dv) {
-    constexpr int D = 128, KT = 64, KB = 16;     // KB keys per CTA: all their loads of a segment are in flight together
+    constexpr int D = 128, KT = 64, KB = 16;     // KB keys per pass: all their loads of a segment are in flight together
     const int hg = blockIdx.x;
     if (ix.key_cnt[hg] == 0) return;
     const int h = hg / s.NBmax, gb = hg - h * s.NBmax;
     const int row0 = ix.row0[gb];
     const int seg0 = ix.key_seg[hg], nseg = ix.key_seg[hg + 1] - seg0;
     const int nkeys = min(KT, ix.nrow[gb]);     // rows past the end of the sequence belong to the next sequence's block
-    const int which = blockIdx.y & 1, k0 = (blockIdx.y >> 1) * KB;
-    if (k0 >= nkeys) return;
+    const int which = blockIdx.y;
     const int d = threadIdx.x;
-    const float* src = slabs + (int64_t)seg0 * (2 * KT * D) + which * (KT * D) + k0 * D + d;
-    ET* dst = (which == 0 ? dk : dv) + ((int64_t)(row0 + k0) * s.Hk + h) * D + d;
-    float acc[KB];
+#pragma unroll 1
+    for (int k0 = 0; k0 < nkeys; k0 += KB) {
+        const float* src = slabs + (int64_t)seg0 * (2 * KT * D) + which * (KT * D) + k0 * D + d;
+        ET* dst = (which == 0 ? dk : dv) + ((int64_t)(row0 + k0) * s.Hk + h) * D + d;
+        float acc[KB];
 #pragma unroll
-    for (int j = 0; j < KB; ++j) acc[j] = 0.f;
-    for (int sg = 0; sg < nseg; ++sg) {
-        float v[KB];
+        for (int j = 0; j < KB; ++j) acc[j] = 0.f;
+        for (int sg = 0; sg < nseg; ++sg) {
+            float v[KB];
 #pragma unroll
-        for (int j = 0; j < KB; ++j) v[j] = k0 + j < nkeys ? src[(int64_t)sg * (2 * KT * D) + j * D] : 0.f;
+            for (int j = 0; j < KB; ++j) v[j] = k0 + j < nkeys ? src[(int64_t)sg * (2 * KT * D) + j * D] : 0.f;
 #pragma unroll
-        for (int j = 0; j < KB; ++j) acc[j] += v[j];
-    }
-#pragma unroll
-    for (int j = 0; j < KB; ++j)
-        if (k0 + j < nkeys) {
-            if constexpr (ElemTraits<ET>::kIsBF16) dst[(int64_t)j * s.Hk * D] = __float2bfloat16(acc[j]);
-            else dst[(int64_t)j * s.Hk * D] = __float2half(acc[j]);
+            for (int j = 0; j < KB; ++j) acc[j] += v[j];
         }
+#pragma unroll
+        for (int j = 0; j < KB; ++j)
+            if (k0 + j < nkeys) {
+                if constexpr (ElemTraits<ET>::kIsBF16) dst[(int64_t)j * s.Hk * D] = __float2bfloat16(acc[j]);
+                else dst[(int64_t)j * s.Hk * D] = __float2half(acc[j]);
+            }
+    }
 }
 
 // fp32 accumulators -> output dtype
@@ -558,7 +560,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     if (kv_elems > 0) {
         if (pipelined) {
             if constexpr (D == 128)
-                sel_bwd_dkdv_reduce<ET><<<dim3((unsigned)(s.Hk * s.NBmax), 8), 128, 0, stream>>>(a.slabs, s, ix, (ET*)a.dk, (ET*)a.dv);
+                sel_bwd_dkdv_reduce<ET><<<dim3((unsigned)(s.Hk * s.NBmax), 2), 128, 0, stream>>>(a.slabs, s, ix, (ET*)a.dk, (ET*)a.dv);
         } else {
             int64_t n4 = kv_elems / 4;
             sel_bwd_convert<ET><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(a.dk_acc, a.dv_acc, (ET*)a.dk, (ET*)a.dv, n4);

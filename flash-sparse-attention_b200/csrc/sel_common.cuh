@@ -44,6 +44,7 @@ struct SelShape {
     int C;           // query tokens per chunk of the index build
     int NC;          // chunks = ceil(N / C)
     int RB;          // tiles per scheduling run of the backward kernel (fixes the segments)
+    int IW;          // warps per CTA of the index build
 };
 
 // Index workspace (kept by the caller between forward and backward).  All int32.
@@ -60,6 +61,7 @@ struct SelBounds {
 struct SelIndex {
     int* header;     // [64]: [0] status, [1] total tiles, [2] total entries, [3] total segments
     int* chunk_cnt;  // [Hk * NC * NBmax]  entries of (kv head, chunk, block); then their exclusive prefix over the chunks
+    int* warp_off;   // [Hk * NC * IW * NBmax]  first position, inside the chunk's share of the key, of every warp of the count kernel
     int* key_cnt;    // [Hk * NBmax]       entries per key
     int* key_tile;   // [Hk * NBmax + 1]   first tile of every key (exclusive scan of ceil(count / TPT))
     int* key_seg;    // [Hk * NBmax + 1]   first segment of every key
@@ -88,6 +90,7 @@ inline int64_t sel_index_bytes(const SelShape& s) {
     int64_t b = 0;
     b += align_up(64 * 4, 256);
     b += align_up(HG * s.NC * 4, 256);
+    b += align_up(HG * s.NC * s.IW * 4, 256);
     b += align_up(HG * 4, 256);
     b += align_up((HG + 1) * 4, 256) * 2;
     b += align_up((int64_t)s.NBmax * 4, 256) * 2;
@@ -104,6 +107,7 @@ inline SelIndex sel_index_carve(void* ws, const SelShape& s) {
     SelIndex ix;
     ix.header = (int*)p;    p += align_up(64 * 4, 256);
     ix.chunk_cnt = (int*)p; p += align_up(HG * s.NC * 4, 256);
+    ix.warp_off = (int*)p;  p += align_up(HG * s.NC * s.IW * 4, 256);
     ix.key_cnt = (int*)p;   p += align_up(HG * 4, 256);
     ix.key_tile = (int*)p;  p += align_up((HG + 1) * 4, 256);
     ix.key_seg = (int*)p;   p += align_up((HG + 1) * 4, 256);

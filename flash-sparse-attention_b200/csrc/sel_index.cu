@@ -109,23 +109,30 @@ __global__ void __launch_bounds__(kIdxMaxWarps * 32) sel_index_chunk(const int* 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x, nwarps = nthreads >> 5;
     const int c = blockIdx.x, h = blockIdx.y;
     const int n0 = (int)min((int64_t)c * s.C, s.N), n1 = (int)min((int64_t)(c + 1) * s.C, s.N);
-    for (int i = tid; i < nwarps * s.NBmax; i += nthreads) sm[i] = 0;
-    __syncthreads();
-    chunk_pass<false>(topk_idx, cu, bd, s, ix, h, c, n0, n1, sm + warp * s.NBmax, warp, nwarps, lane);
-    __syncthreads();
     int* cc = ix.chunk_cnt + ((int64_t)h * s.NC + c) * s.NBmax;
-    const int* kt = ix.key_tile + (int64_t)h * s.NBmax;
-    for (int gb = tid; gb < s.NBmax; gb += nthreads) {
-        // FILL: first position of the key's entries + the chunk's first position inside the key (steps 2 and 3)
-        int run = FILL ? kt[gb] * s.TPT + cc[gb] : 0;
-        for (int i = 0; i < nwarps; ++i) {
-            const int v = sm[i * s.NBmax + gb];
-            sm[i * s.NBmax + gb] = run;        // this warp's first position inside the key
-            run += v;
+    int* wo = ix.warp_off + ((int64_t)h * s.NC + c) * nwarps * s.NBmax;
+    if (!FILL) {
+        for (int i = tid; i < nwarps * s.NBmax; i += nthreads) sm[i] = 0;
+        __syncthreads();
+        chunk_pass<false>(topk_idx, cu, bd, s, ix, h, c, n0, n1, sm + warp * s.NBmax, warp, nwarps, lane);
+        __syncthreads();
+        for (int gb = tid; gb < s.NBmax; gb += nthreads) {
+            int run = 0;
+            for (int i = 0; i < nwarps; ++i) {
+                const int v = sm[i * s.NBmax + gb];
+                wo[i * s.NBmax + gb] = run;        // this warp's first position inside the key, relative to the chunk
+                run += v;
+            }
+            cc[gb] = run;
         }
-        if (!FILL) cc[gb] = run;
-    }
-    if (FILL) {
+    } else {
+        // every warp's first position in the tile-ordered entry list: first entry of the key (step 3) + the chunk's first
+        // position inside the key (step 2) + the warp's inside the chunk (step 1)
+        const int* kt = ix.key_tile + (int64_t)h * s.NBmax;
+        for (int gb = tid; gb < s.NBmax; gb += nthreads) {
+            const int base = kt[gb] * s.TPT + cc[gb];
+            for (int i = 0; i < nwarps; ++i) sm[i * s.NBmax + gb] = base + wo[i * s.NBmax + gb];
+        }
         __syncthreads();
         chunk_pass<true>(topk_idx, cu, bd, s, ix, h, c, n0, n1, sm + warp * s.NBmax, warp, nwarps, lane);
     }
@@ -263,7 +270,7 @@ cudaError_t sel_build_index(const int* topk_idx, const int* cu, const SelBounds&
     cudaError_t e = cudaMemsetAsync(ws, 0, sel_index_zero_bytes(s), stream);
     if (e != cudaSuccess) return e;
     if ((int64_t)s.Hk * s.N == 0) return cudaSuccess;
-    const int nw = sel_index_warps(s);
+    const int nw = s.IW;
     if (nw == 0) return cudaErrorInvalidValue;
     const int smem = nw * s.NBmax * 4;
     e = cudaFuncSetAttribute(sel_index_chunk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
