@@ -139,9 +139,9 @@ static int make_shape(int64_t N, int B, int Hq, int Hk, int D, int T, int BK, Se
     s->N = N; s->Nk = Nk; s->B = B; s->Hq = Hq; s->Hk = Hk; s->G = G; s->D = D; s->T = T; s->BK = BK;
     s->NBmax = (int)(Nk / BK) + B + 1;
     s->TPT = (kTileRows / G) & ~3;
-    // chunk of the index build: at least 1024 tokens, at most 256 chunks
-    int64_t C = 1024;
-    while (C * 256 < N) C *= 2;
+    // chunk of the index build: at least 512 tokens, at most 512 chunks
+    int64_t C = 512;
+    while (C * 512 < N) C *= 2;
     s->C = (int)C;
     s->NC = (int)((N + C - 1) / C);
     if (s->NC < 1) s->NC = 1;
@@ -481,6 +481,26 @@ int fsa_sel_index_dump(const void* index_ws, int64_t N, int B, int Hq, int Hk, i
     if (key_tile_host && (e = cudaMemcpy(key_tile_host, ix.key_tile, (HG + 1) * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     if (header_host && (e = cudaMemcpy(header_host, ix.header, 64 * 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(e);
     return FSA_OK;
+}
+
+// A bounded wait that runs out, on purpose and harmlessly: one thread waits on an mbarrier that nothing arrives on, gives
+// up after FSA_WAIT_NS like every wait of the library does, records kStatusWaitTimeout in the status word and returns.
+// Lets a test walk the failure path of the status plumbing without hanging or faulting anything.
+static __global__ void wait_timeout_probe_kernel(int* status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+        if (mbar_wait(&bar, 0, status)) atomicMax(status, 99);   // cannot happen: nobody arrives
+    }
+}
+
+int fsa_debug_wait_timeout(void* status_ws, void* stream_) {
+    if (!status_ws || ((uintptr_t)status_ws & 3)) return FSA_ERR_BAD_ARG;
+    (void)cudaGetLastError();
+    wait_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream_>>>((int*)status_ws);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FSA_OK : cuda_fail(e);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -335,42 +335,34 @@ __global__ void __launch_bounds__(128, 1) sel_bwd_main(const SelBwdParams<ET> p,
     if (warp == 0) tmem_dealloc(tbase, C::kCols);
 }
 
-// delta[hq, n] = sum_d o[n, hq, d] * do[n, hq, d].  D / 8 threads per row (16 bytes each), four rows per thread
-// in flight; a CTA of 256 threads covers 4 * 256 / (D / 8) rows.
+// delta[hq, n] = sum_d o[n, hq, d] * do[n, hq, d].  D / 8 threads per row (16 bytes of o and of dO each), two rows per
+// thread in flight, few registers: the kernel is a pure stream and wants every warp slot of the SM.
 template <typename ET>
 __global__ void __launch_bounds__(256) sel_bwd_delta(const ET* __restrict__ o, int64_t o_sn, int64_t o_sh,
                                                      const ET* __restrict__ d_o, int64_t do_sn, int64_t do_sh,
                                                      int64_t N, int Hq, int D, float* __restrict__ delta) {
-    const int tpr = D >> 3;                                  // threads per row: 8, 16 or 32
+    const int tpr = D >> 3;                                  // threads per row: 8, 16 or 32 (a power of two)
     const int rpc = 256 / tpr;                               // rows per pass of the CTA
-    const int part = threadIdx.x % tpr, rloc = threadIdx.x / tpr;
+    const int part = threadIdx.x & (tpr - 1), rloc = threadIdx.x / tpr;
     const int64_t rows = N * Hq;
-    const int64_t row0 = (int64_t)blockIdx.x * (4 * rpc) + rloc;
-    // (token, head) of this thread's four rows: one division, then increments (a 64-bit division per row costs more
-    // than the row's loads)
-    int64_t nn[4];
-    int hh[4];
-    {
-        int64_t n = row0 / Hq;
-        int hq = (int)(row0 - n * Hq);
+    const int64_t row0 = (int64_t)blockIdx.x * (2 * rpc) + rloc;
+    uint4 a[2], b[2];
+    int64_t nn[2];
+    int hh[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            nn[j] = n; hh[j] = hq;
-            hq += rpc;
-            while (hq >= Hq) { hq -= Hq; ++n; }
-        }
-    }
-    uint4 a[4], b[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 2; ++j) {
+        const int64_t r = row0 + (int64_t)j * rpc;
         a[j] = b[j] = make_uint4(0u, 0u, 0u, 0u);
-        if (row0 + (int64_t)j * rpc < rows) {
+        nn[j] = 0; hh[j] = 0;
+        if (r < rows) {
+            nn[j] = r / Hq;
+            hh[j] = (int)(r - nn[j] * Hq);
             a[j] = *reinterpret_cast<const uint4*>(o + nn[j] * o_sn + (int64_t)hh[j] * o_sh + part * 8);
             b[j] = *reinterpret_cast<const uint4*>(d_o + nn[j] * do_sn + (int64_t)hh[j] * do_sh + part * 8);
         }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 2; ++j) {
         const uint32_t* ua = &a[j].x;
         const uint32_t* ub = &b[j].x;
         float acc = 0.f;
@@ -451,37 +443,45 @@ __global__ void __launch_bounds__(256) sel_bwd_dq_reduce(const ET* __restrict__ 
 // fsa/ops/FSA_topk_sparse_attention.py:1854-1855).  Thread = head-dim index; blocks nobody selected keep the zeros
 // the caller put there.
 template <typename ET>
-__global__ void __launch_bounds__(128) sel_bwd_dkdv_reduce(const float* __restrict__ slabs, SelShape s, SelIndex ix,
+__global__ void __launch_bounds__(256) sel_bwd_dkdv_reduce(const float* __restrict__ slabs, SelShape s, SelIndex ix,
                                                            ET* __restrict__ dk, ET* __restrict__ dv) {
-    constexpr int D = 128, KT = 64, KB = 16;     // KB keys per pass: all their loads of a segment are in flight together
+    constexpr int D = 128, KT = 64;
     const int hg = blockIdx.x;
     if (ix.key_cnt[hg] == 0) return;
     const int h = hg / s.NBmax, gb = hg - h * s.NBmax;
     const int row0 = ix.row0[gb];
     const int seg0 = ix.key_seg[hg], nseg = ix.key_seg[hg + 1] - seg0;
     const int nkeys = min(KT, ix.nrow[gb]);     // rows past the end of the sequence belong to the next sequence's block
-    const int which = blockIdx.y;
-    const int d = threadIdx.x;
-#pragma unroll 1
-    for (int k0 = 0; k0 < nkeys; k0 += KB) {
-        const float* src = slabs + (int64_t)seg0 * (2 * KT * D) + which * (KT * D) + k0 * D + d;
-        ET* dst = (which == 0 ? dk : dv) + ((int64_t)(row0 + k0) * s.Hk + h) * D + d;
-        float acc[KB];
+    // a warp per K/V row (32 lanes x 16 bytes = the row's 128 floats); the CTA's 8 warps walk the block's rows of dK, then dV,
+    // four rows in flight per warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float4* base = reinterpret_cast<const float4*>(slabs + (int64_t)seg0 * (2 * KT * D)) + lane;
+    constexpr int kSegStride = 2 * KT * D / 4, kRowStride = D / 4;       // in float4
+    for (int r0 = warp * 4; r0 < 2 * KT; r0 += 32) {
+        float4 acc[4];
 #pragma unroll
-        for (int j = 0; j < KB; ++j) acc[j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int sg = 0; sg < nseg; ++sg) {
-            float v[KB];
+            float4 v[4];
 #pragma unroll
-            for (int j = 0; j < KB; ++j) v[j] = k0 + j < nkeys ? src[(int64_t)sg * (2 * KT * D) + j * D] : 0.f;
+            for (int j = 0; j < 4; ++j) {
+                const int r = r0 + j;                        // row of the slab: which * 64 + key
+                v[j] = (r & (KT - 1)) < nkeys ? __ldcs(base + (int64_t)sg * kSegStride + r * kRowStride) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
-            for (int j = 0; j < KB; ++j) acc[j] += v[j];
+            for (int j = 0; j < 4; ++j) { acc[j].x += v[j].x; acc[j].y += v[j].y; acc[j].z += v[j].z; acc[j].w += v[j].w; }
         }
 #pragma unroll
-        for (int j = 0; j < KB; ++j)
-            if (k0 + j < nkeys) {
-                if constexpr (ElemTraits<ET>::kIsBF16) dst[(int64_t)j * s.Hk * D] = __float2bfloat16(acc[j]);
-                else dst[(int64_t)j * s.Hk * D] = __float2half(acc[j]);
+        for (int j = 0; j < 4; ++j) {
+            const int r = r0 + j, key = r & (KT - 1);
+            if (key < nkeys) {
+                ET* dst = (r < KT ? dk : dv) + ((int64_t)(row0 + key) * s.Hk + h) * D + lane * 4;
+                uint2 w;
+                w.x = ElemTraits<ET>::pack2(acc[j].x, acc[j].y);
+                w.y = ElemTraits<ET>::pack2(acc[j].z, acc[j].w);
+                *reinterpret_cast<uint2*>(dst) = w;
             }
+        }
     }
 }
 
@@ -521,7 +521,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     }
     if (e != cudaSuccess) return e;
     if (rows > 0) {
-        const int64_t rows_per_cta = 4 * (256 / (D / 8));
+        const int64_t rows_per_cta = 2 * (256 / (D / 8));
         unsigned grid = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
         sel_bwd_delta<ET><<<grid, 256, 0, stream>>>((const ET*)a.o, a.o_sn, a.o_sh, (const ET*)a.d_o, a.do_sn, a.do_sh,
                                                     s.N, s.Hq, D, a.delta);
@@ -560,7 +560,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     if (kv_elems > 0) {
         if (pipelined) {
             if constexpr (D == 128)
-                sel_bwd_dkdv_reduce<ET><<<dim3((unsigned)(s.Hk * s.NBmax), 2), 128, 0, stream>>>(a.slabs, s, ix, (ET*)a.dk, (ET*)a.dv);
+                sel_bwd_dkdv_reduce<ET><<<(unsigned)(s.Hk * s.NBmax), 256, 0, stream>>>(a.slabs, s, ix, (ET*)a.dk, (ET*)a.dv);
         } else {
             int64_t n4 = kv_elems / 4;
             sel_bwd_convert<ET><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(a.dk_acc, a.dv_acc, (ET*)a.dk, (ET*)a.dv, n4);

@@ -11,13 +11,15 @@
 //   warp 10      prepares, up to four tiles ahead, the token of every tile row (the gather warps then run without
 //                any global load of their own: a plain load issued behind a burst of async copies waits for it);
 //   warp 11      loads the K/V block of every run of tiles by TMA;
-//   warps 12..15 move the finished dK^T / dV^T accumulators of a segment (the tiles of one block inside one scheduling
-//                run) from TMEM to registers (freeing them for the next segment at once) and store them to the
-//                segment's own fp32 slab while the next segment computes; a second kernel sums the slabs of a block
-//                in segment order, so dK and dV do not depend on the order in which CTAs finish (no atomics);
-//   warps 16..23 two groups, one row per thread, alternate tiles: P / dS to swizzled smem, then the
-//                dQ partial of the tile from TMEM through a swizzled staging area to global memory by TMA
-//                store (input dtype, tile order): the load/store unit is left to the row gathers.
+//   warps 12..15 the accumulator drain, one row / one head-dim index per thread: for every tile the dQ partial from TMEM
+//                through a swizzled staging area to global memory by TMA store (input dtype, tile order: the load/store
+//                unit is left to the row gathers); at the end of a segment (the tiles of one block inside one
+//                scheduling run) the finished dK^T / dV^T accumulators from TMEM to registers (freeing them for the next
+//                segment at once) and on to the segment's own fp32 slab while the next segment computes; a second kernel
+//                sums the slabs of a block in segment order, so dK and dV do not depend on the order in which CTAs
+//                finish (no atomics);
+//   warps 16..23 two groups, one row per thread, alternate tiles: P / dS to swizzled smem and nothing else -- they are the
+//                critical path of a tile (64 exp2 + the dS arithmetic per row between two MMA phases).
 #include "sel_launch.cuh"
 
 namespace fsa {
@@ -107,7 +109,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
     uint64_t* acc_full = bars + 18;
     uint64_t* acc_empty = bars + 19;
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 20);
-    uint64_t* stg_free = bars + 22;      // [4] dQ staging rows of a lane quarter have been read by the TMA store
     uint64_t* off_full = bars + 26;      // [4] ring of prepared tiles: tokens, kv head and new-block flag are valid
     uint64_t* off_empty = bars + 30;     // [4] ... have been read by the eight gather warps and the S/dP issuer
     int* s_h = reinterpret_cast<int*>(bars + 34);    // [4] kv head of the prepared tile
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
         mbar_init(dq_full, 1); mbar_init(dq_empty, 128);
         mbar_init(acc_full, 1); mbar_init(acc_empty, 128);
-        for (int i = 0; i < 4; ++i) { mbar_init(&stg_free[i], 1); mbar_init(&off_full[i], 1); mbar_init(&off_empty[i], kWLoad + 1); }
+        for (int i = 0; i < 4; ++i) { mbar_init(&off_full[i], 1); mbar_init(&off_empty[i], kWLoad + 1); }
         mbar_init_fence();
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
@@ -195,28 +196,74 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         }
         if (t == 0) BT_DUMP(0, 5);
     } else if (warp >= kWFlush && warp < kWFlush + 4) {
-        // ------------------------------------------------------------------ accumulator flush
-        // Walks the CTA's tiles to find the segment boundaries; for every finished segment: wait for its
-        // last products, pull dK^T / dV^T (lane = head-dim index, columns = keys) into registers,
-        // release the TMEM accumulators, then store them to the segment's slab.
+        // ------------------------------------------------------------------ accumulator drain: dQ per tile, dK / dV per segment
+        // Walks the CTA's tiles in order.  Per tile: wait for its dQ product, move it TMEM -> registers -> swizzled staging
+        // (this warp's 32 rows) -> TMA store.  At the last tile of a segment: wait for the segment's last products, pull
+        // dK^T / dV^T (lane = head-dim index, columns = keys) into registers, release the TMEM accumulators, store them to
+        // the segment's slab.
         reg_inc<kRegFlush>();
-        const int d_idx = (warp & 3) * 32 + lane;
-        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const int quarter = warp & 3;
+        const int d_idx = quarter * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        uint8_t* my_stage = sDQ + quarter * (32 * 256);
         bool ok = true;
         int nflush = 0;
-        int k = 0;
         BT_DECL;
-        while (k < nloc && ok) {
+        // key ids of the CTA's tiles, fetched two tiles ahead
+        int hg0 = -1, hg1 = -1, hg2 = -1;
+        if (nloc > 0) hg1 = load_tile(p.ix, sched.tile(0)).hg;
+        if (nloc > 1) hg2 = load_tile(p.ix, sched.tile(1)).hg;
+        int seg_first = 0;                 // local index of the first tile of the running segment
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int prev_hg = hg0;
+            hg0 = hg1; hg1 = hg2;
+            if (k + 2 < nloc) hg2 = load_tile(p.ix, sched.tile(k + 2)).hg;
+            if (hg0 != prev_hg || (k % sched.run) == 0) seg_first = k;
+            const bool last_of_seg = (k + 1 >= nloc) || (hg1 != hg0) || ((k + 1) % sched.run) == 0;
             const int j = sched.tile(k);
-            const TileInfo ti = load_tile(p.ix, j);
-            int k2 = k + 1;
-            while (k2 < nloc && (k2 % sched.run) != 0 && load_tile(p.ix, sched.tile(k2)).hg == ti.hg) ++k2;   // tiles [k, k2): one segment
-            // segments of a key are numbered by the scheduling run they fall into
-            const int seg = ti.seg0 + j / sched.run - __ldg(p.ix.tile_aux + j).x / sched.run;
-            float* slab = p.slabs + (int64_t)seg * (2 * KT * D) + d_idx;
+            // ---- dQ partial of this tile
             BT_TOC(0);
-            ok = mbar_wait(acc_full, nflush & 1, status) && ok;
+            ok = mbar_wait(dq_full, k & 1, status) && ok;
             BT_TOC(1);
+            tc_fence_after();
+            if (lane == 0) bulk_wait_read0();          // the store of the previous tile has read this warp's staging rows
+            __syncwarp();
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tbase + lane_off + cDQ + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 u;
+                    u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+                    u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+                    u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+                    u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+                    const int chunk = (c0 >> 3) + q4;
+                    *reinterpret_cast<uint4*>(my_stage + (chunk >> 3) * (32 * 128) + sw128_chunk_off(lane, chunk & 7)) = u;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(dq_empty);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b)
+                    tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
+                bulk_commit();
+            }
+            BT_TOC(2);
+            if (!last_of_seg) continue;
+            // ---- dK^T / dV^T of the finished segment
+            const int j0 = sched.tile(seg_first);
+            const TileInfo ti = load_tile(p.ix, j0);
+            // segments of a key are numbered by the scheduling run they fall into
+            const int seg = ti.seg0 + j0 / sched.run - __ldg(p.ix.tile_aux + j0).x / sched.run;
+            float* slab = p.slabs + (int64_t)seg * (2 * KT * D) + d_idx;
+            ok = mbar_wait(acc_full, nflush & 1, status) && ok;
+            BT_TOC(3);
             tc_fence_after();
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
@@ -235,10 +282,10 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
 #pragma unroll
                 for (int key = 0; key < KT; ++key) dst[key * D] = __uint_as_float(v[key]);
             }
-            k = k2;
-            BT_TOC(2);
+            BT_TOC(4);
         }
-        if (warp == kWFlush && lane == 0) BT_DUMP(8, 3);
+        if (lane == 0) bulk_wait0();
+        if (warp == kWFlush && lane == 0) BT_DUMP(8, 5);
     } else if (warp < kWFlush) {
       reg_dec<kRegMma>();
       if (warp == kWMma1) {
@@ -320,7 +367,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             BT_TOC(0);
             ok = mbar_wait(pds_full, k & 1, status) && ok;
             BT_TOC(1);
-            ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
             BT_TOC(2);
             ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;     // already complete: acquire only
             ok = mbar_wait(&kv_full[kvn % kKVStages], (kvn / kKVStages) & 1, status) && ok;
@@ -332,11 +378,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             const uint32_t bk = k_mn_lo + (uint32_t)((kvn % kKVStages) * (kKV >> 4));
             const uint32_t aq = qd_mn_lo + (uint32_t)(st * (kQD >> 4));
             const uint32_t ad = aq + (uint32_t)((kTileRows * D * 2) >> 4);
+            // dK^T / dV^T first: they are the last readers of the Q / dO stage, which goes back to the gather warps as
+            // soon as they are done; dQ (which reads dS and K only) follows
             if (leader) {
-#pragma unroll
-                for (int ks = 0; ks < KT / 16; ++ks)
-                    umma_ss(tbase + cDQ, umma_desc_pack(ds_k_lo + ks * 2, hi_1024), umma_desc_pack(bk + ks * (2048 >> 4), hi_1024),
-                            idesc_dq, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < kTileRows / 16; ++ks) {
                     const uint32_t acc = (!first_of_block || ks > 0) ? 1u : 0u;
@@ -345,13 +389,20 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                     umma_ss(tbase + cDV, umma_desc_pack(ad + ks * (2048 >> 4), hi_1024),
                             umma_desc_pack(p_mn_lo + ks * (2048 >> 4), hi_1024), idesc_dk, acc);
                 }
-                umma_commit(pds_empty);
                 umma_commit(&qd_empty[st]);
+                if (last_of_block) umma_commit(acc_full);
+            }
+            __syncwarp();
+            ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
+            tc_fence_after();
+            if (leader) {
+#pragma unroll
+                for (int ks = 0; ks < KT / 16; ++ks)
+                    umma_ss(tbase + cDQ, umma_desc_pack(ds_k_lo + ks * 2, hi_1024), umma_desc_pack(bk + ks * (2048 >> 4), hi_1024),
+                            idesc_dq, ks > 0);
+                umma_commit(pds_empty);
                 umma_commit(dq_full);
-                if (last_of_block) {
-                    umma_commit(&kv_empty[kvn % kKVStages]);
-                    umma_commit(acc_full);
-                }
+                if (last_of_block) umma_commit(&kv_empty[kvn % kKVStages]);
             }
             __syncwarp();
             BT_TOC(5);
@@ -482,7 +533,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         }
         BT_DECL;
         for (int k = sb; k < nloc && ok; k += 2) {
-            const int j = jA;
             const float lse_r = lseA, delta_s = deltaA;
             const int c_lo = cloA, c_hi = chiA;
             // rotate the prefetch registers
@@ -541,42 +591,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             fence_async_smem();
             mbar_arrive(pds_full);
             BT_TOC(4);
-            // ---- dQ partial of this tile
-            ok = mbar_wait(dq_full, k & 1, status) && ok;
-            BT_TOC(5);
-            tc_fence_after();
-            // staging rows of this lane quarter: free once the store of the previous tile (other group) has read them
-            ok = mbar_wait(&stg_free[quarter], (k - 1) & 1, status) && ok;
-            uint8_t* my_stage = sDQ + quarter * (32 * 256);
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tbase + lane_off + cDQ + c0, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint4 u;
-                    u.x = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
-                    u.y = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
-                    u.z = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
-                    u.w = ElemTraits<ET>::pack2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
-                    const int chunk = (c0 >> 3) + q4;
-                    *reinterpret_cast<uint4*>(my_stage + (chunk >> 3) * (32 * 128) + sw128_chunk_off(lane, chunk & 7)) = u;
-                }
-            }
-            tc_fence_before();
-            mbar_arrive(dq_empty);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-#pragma unroll
-                for (int b = 0; b < D / 64; ++b)
-                    tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
-                bulk_commit();
-                bulk_wait_read0();
-                mbar_arrive(&stg_free[quarter]);
-            }
-            __syncwarp();
             BT_TOC(6);
         }
         if (quarter == 0 && lane == 0) BT_DUMP(32 + sb * 8, 7);

@@ -20,7 +20,7 @@
 
 namespace fsa {
 
-constexpr int kIdxMaxWarps = 16;
+constexpr int kIdxMaxWarps = 8;     // (8 warps x 512-token chunks keep four CTAs resident per SM: the kernels are latency-bound)
 constexpr int kIdxMaxSlots = 16;   // top-k lists up to this length are held in registers
 
 // Count (FILL = false: hw[gb] += entries) or place (FILL = true: hw[gb] is this warp's next position in the

@@ -69,6 +69,9 @@ SIGNATURES = {
     ),
     "fsa_linear_compress_fwd": (
         c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fsa_linear_compress_bwd": (
+        c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                c_void_p, c_void_p]),
     "fsa_select_topk_fused": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
@@ -105,6 +108,7 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     ),
     "fsa_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
+    "fsa_debug_wait_timeout": (c_int, [c_void_p, c_void_p]),
     "fsa_sel_index_geometry": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int), POINTER(c_int)]),
     "fsa_sel_index_dump": (
         c_int,

@@ -5,10 +5,11 @@
     compressed length = floor((L - kernel_size) / stride) + 1, or 0 when L < kernel_size   (:334-337)
 
 Forward: ``fsa_linear_compress_fwd``, a tcgen05 GEMM per (128 windows, head) that reads the overlapping token windows in
-place through a strided TMA map and adds the bias in its epilogue (head_dim 64 / 128).  Backward: the same product laid
-out as a batched library GEMM over the unfolded windows, differentiated by autograd -- no fp32 atomics (the reference's
-backward uses tl.atomic_add, :275, :292, and is therefore not bit-reproducible).  Other head sizes use the library GEMM
-in the forward too.  Everything stays on the device; the only host value needed is the list of sequence lengths, which
+place through a strided TMA map and adds the bias in its epilogue (head_dim 64 / 128).  Backward:
+``fsa_linear_compress_bwd``, two tcgen05 GEMM kernels (dx per token phase, dW with the window index as the reduction)
+that write every gradient row once -- no fp32 atomics (the reference's backward uses tl.atomic_add, :275, :292, and is
+therefore not bit-reproducible).  Other head sizes use a batched library GEMM over the unfolded windows, differentiated
+by autograd.  Everything stays on the device; the only host value needed is the list of sequence lengths, which
 the caller may pass to avoid a sync.
 """
 from __future__ import annotations
@@ -41,7 +42,7 @@ def _compress_gemm(x, w, seqlens, ylens, kernel_size, kernel_stride):
 
 class _LinearCompress(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, seqlens, ylens, kernel_size, kernel_stride):
+    def forward(ctx, x, w, bias, cu_seqlens, seqlens, ylens, kernel_size, kernel_stride):
         assert x.is_cuda, "the sm_100a kernels need CUDA tensors (no CPU fallback)"
         N, H, d = x.shape
         xk = x if (x.stride(2) == 1 and x.stride(1) == d and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0) else x.contiguous()
@@ -55,23 +56,28 @@ class _LinearCompress(torch.autograd.Function):
                                                         H, d, kernel_size, kernel_stride, _lib.DTYPE_CODE[x.dtype], _lib.ptr(y), None,
                                                         _lib.current_stream(x.device))
             _lib.check(rc, "fsa_linear_compress_fwd")
-        ctx.save_for_backward(x, w)
+        ctx.save_for_backward(xk, wk, cu_seqlens)
         ctx.meta = (list(seqlens), list(ylens), kernel_size, kernel_stride, bias is not None)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w = ctx.saved_tensors
+        xk, wk, cu = ctx.saved_tensors
         seqlens, ylens, ks, st, has_bias = ctx.meta
-        with torch.enable_grad():
-            xr, wr = x.detach().requires_grad_(True), w.detach().requires_grad_(True)
-            y = _compress_gemm(xr, wr, seqlens, ylens, ks, st)
-        if y.numel():
-            dx, dw = torch.autograd.grad(y, (xr, wr), dy)
-        else:
-            dx, dw = torch.zeros_like(x), torch.zeros_like(w)
+        N, H, d = xk.shape
+        dx = torch.empty((N, H, d), dtype=xk.dtype, device=xk.device) if ctx.needs_input_grad[0] else None
+        dw = torch.empty_like(wk) if ctx.needs_input_grad[1] else None
+        dyk = dy.contiguous()
+        if dx is not None or dw is not None:
+            lens = np.asarray(seqlens, dtype=np.int32)
+            with torch.cuda.device(xk.device):
+                rc = _lib.lib().fsa_linear_compress_bwd(_lib.ptr(xk), xk.stride(0), _lib.ptr(wk), _lib.ptr(dyk) if dyk.numel() else None,
+                                                        _lib.ptr(cu), lens.ctypes.data, len(seqlens), H, d, ks, st,
+                                                        _lib.DTYPE_CODE[xk.dtype], _lib.ptr(dx), _lib.ptr(dw), None,
+                                                        _lib.current_stream(xk.device))
+            _lib.check(rc, "fsa_linear_compress_bwd")
         dbias = dy.sum(0).to(dy.dtype) if has_bias else None
-        return dx, dw, dbias, None, None, None, None
+        return dx, dw, dbias, None, None, None, None, None
 
 
 def linear_compress_gemm(x, w, cu_seqlens, kernel_size, kernel_stride, pe=None, seqlens=None):
@@ -116,7 +122,7 @@ def linear_compress(
         assert pe.dtype == x.dtype and pe.device == x.device
         bias = torch.einsum("hD,hDd->hd", pe.reshape(H, kernel_size * d), w)
     if d in (64, 128):
-        y = _LinearCompress.apply(x, w, bias, seqlens, ylens, kernel_size, kernel_stride)
+        y = _LinearCompress.apply(x, w, bias, cu_seqlens, seqlens, ylens, kernel_size, kernel_stride)
     else:
         y = _compress_gemm(x, w, seqlens, ylens, kernel_size, kernel_stride)
         if bias is not None:

@@ -180,6 +180,19 @@ int fsa_linear_compress_fwd(const void* x, int64_t x_stride_n, const void* w, co
                             int batch, int num_heads, int head_dim, int kernel_size, int kernel_stride, int dtype, void* y,
                             int32_t* status, void* stream);
 
+/* K/V compression backward without atomics: dx and dW of fsa_linear_compress_fwd from dy.  Replaces
+ * linear_compress_bwd_kernel (nsa_ref/ops/linear_compress.py:135-292, launched at :401-470), which scatters both
+ * gradients with fp32 tl.atomic_add (:275, :292); here every dx row and every dW row is written once from an fp32
+ * accumulator, so the result does not depend on scheduling.
+ *   x, w as in the forward; dy [sum n_b, H, D] contiguous; cu_seqlens [batch + 1] DEVICE token offsets and
+ *   seqlens_host [batch] the same lengths on the HOST (dx runs one launch per sequence, dW a single launch over all
+ *   sequences); dx [N, H, D] contiguous or NULL, dw [H, kernel_size * D, D] contiguous or NULL (a NULL gradient is not
+ *   computed).  head_dim 64 or 128, kernel_stride a power of two dividing kernel_size.  The gradient of the bias is
+ *   the column sum of dy and is left to the caller. */
+int fsa_linear_compress_bwd(const void* x, int64_t x_stride_n, const void* w, const void* dy, const int32_t* cu_seqlens,
+                            const int32_t* seqlens_host, int batch, int num_heads, int head_dim, int kernel_size,
+                            int kernel_stride, int dtype, void* dx, void* dw, int32_t* status, void* stream);
+
 /* Fused top-k block selection for a varlen batch: q.k^T on the tensor cores, probabilities, block scores and the ids
  * in one kernel; no score tensor is written to memory.  Replaces _get_attention_score / score_kernel, transform_score /
  * _transform_score_kernel and the topk + sort + mask tail (nsa_ref/ops/compressed_attention.py:833-1158, :1274-1315;
@@ -306,6 +319,12 @@ int fsa_decode_ranges(const int32_t* topk_idx, const int32_t* seq_len, const int
  * *status_out: 0 ok, 1 a bounded wait ran out, 2 an out-of-table index was skipped.
  * Returns FSA_ERR_DEVICE_STATUS when the word is non-zero. */
 int fsa_read_status(const void* index_ws, void* stream, int* status_out);
+
+/* Debug/inspection: launch one thread that waits on a barrier nothing will ever signal.  Like every wait of the library
+ * it gives up after its bound (0.2 s), records status 1 in the int at status_ws (a zeroed device word, e.g. the start of
+ * an index workspace) and returns: fsa_read_status(status_ws, ...) then reports FSA_ERR_DEVICE_STATUS.  Exists so that the
+ * failure path of the status plumbing can be tested without hanging or faulting a GPU.  No reference counterpart. */
+int fsa_debug_wait_timeout(void* status_ws, void* stream);
 
 /* Debug/inspection: geometry of the index workspace for a problem: the upper bound on tiles the workspace is sized
  * for, the entries per tile tpt = (128 / group) & ~3, and nbmax = total_tokens / block_size + batch + 1, the bound on

@@ -1,4 +1,4 @@
-"""The K/V compressor on the GPU (fsa_linear_compress_fwd through the operator) against the CPU oracle
+"""The K/V compressor on the GPU (fsa_linear_compress_fwd / fsa_linear_compress_bwd through the operator) against the CPU oracle
 (oracle.nsa_layer_oracle.linear_compress_ref, which restates nsa_ref/ops/linear_compress.py:113-131, :334-346, :495-502).
 
 Tolerance: the kernel accumulates in fp32 and rounds once to the activation dtype (twice with the bias, as the reference
@@ -28,6 +28,9 @@ def _tol_ok(got, ref, name):
     ([257, 513], 2, 64, 32, 16, torch.float16, True),
     ([31], 1, 128, 32, 16, torch.bfloat16, True),                  # no window at all
     ([700], 2, 128, 64, 32, torch.bfloat16, True),
+    ([1500, 40, 333], 2, 128, 16, 16, torch.bfloat16, False),      # non-overlapping windows: every token in one window
+    ([900, 2300], 1, 64, 64, 16, torch.bfloat16, True),            # every token in four windows
+    ([5000, 4200], 2, 128, 32, 16, torch.float16, False),          # many 128-window tiles in the dW reduction
 ])
 def test_forward_backward_matches_oracle(seqlens, H, d, ks, st, dtype, with_pe):
     N = sum(seqlens)
@@ -62,3 +65,21 @@ def test_forward_backward_matches_oracle(seqlens, H, d, ks, st, dtype, with_pe):
     assert float((gw - wf.grad).norm()) <= 2e-2 * float(wf.grad.norm()), "dw"
     if with_pe:
         assert float((pc.grad.float().cpu() - pf.grad).norm()) <= 3e-2 * float(pf.grad.norm()), "dpe"
+
+
+def test_backward_is_bit_reproducible():
+    """No atomics: two backward passes on the same inputs give the same bits (the reference's do not, :275, :292)."""
+    seqlens, H, d, ks, st = [3000, 777], 2, 128, 32, 16
+    N = sum(seqlens)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(N, H, d, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(H, ks * d, d, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    cu = make_cu_seqlens(seqlens).to(DEV)
+    grads = []
+    for _ in range(2):
+        xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y, _ = linear_compress(xr, wr, cu, ks, st, None, seqlens)
+        gy = torch.Generator().manual_seed(6)
+        y.backward(torch.randn(y.shape, generator=gy).to(torch.bfloat16).to(DEV))
+        grads.append((xr.grad.clone(), wr.grad.clone()))
+    assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1])

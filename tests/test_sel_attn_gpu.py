@@ -201,6 +201,27 @@ def test_backward_is_bit_reproducible():
             assert torch.equal(a, b), name
 
 
+def test_bounded_wait_reports_through_the_status_word():
+    """A wait that runs out records its status and the kernel returns; the host reads it as FSA_ERR_DEVICE_STATUS and
+    the context stays usable (the next forward is correct)."""
+    L = _lib.lib()
+    ws = torch.zeros(64, dtype=torch.int32, device=DEV)
+    stream = _lib.current_stream(torch.device(DEV))
+    with torch.cuda.device(DEV):
+        assert L.fsa_debug_wait_timeout(_lib.ptr(ws), stream) == 0
+        st = c_int(0)
+        rc = L.fsa_read_status(_lib.ptr(ws), stream, byref(st))
+    assert rc == _lib.FSA_ERR_DEVICE_STATUS and st.value == 1
+    with pytest.raises(_lib.FsaError):
+        _lib.check(rc, "status")
+    seqlens, Hk, G, d, bs, T = [300], 1, 2, 128, 64, 4
+    q, k, v = make_qkv(sum(seqlens), Hk * G, Hk, d, 5, with_do=False)
+    idx, cu = make_topk_idx(seqlens, Hk, T, bs, 5), make_cu_seqlens(seqlens)
+    o, lse, _ = sel_attn_fwd(q.to(DEV), k.to(DEV), v.to(DEV), idx.to(DEV), bs, cu.to(DEV), d ** -0.5, check_status=True)
+    o_ref, _ = sel_attn_forward(q, k, v, idx, bs, cu, d ** -0.5)
+    _tol_ok(o, o_ref, "o")
+
+
 def test_error_paths_raise():
     q = torch.zeros(64, 2, 96, dtype=torch.bfloat16, device=DEV)  # head_dim 96 is not compiled
     k = torch.zeros(64, 1, 96, dtype=torch.bfloat16, device=DEV)
