@@ -18,8 +18,9 @@
 //                segment at once) and on to the segment's own fp32 slab while the next segment computes; a second kernel
 //                sums the slabs of a block in segment order, so dK and dV do not depend on the order in which CTAs
 //                finish (no atomics);
-//   warps 16..23 two groups, one row per thread, alternate tiles: P / dS to swizzled smem and nothing else -- they are the
-//                critical path of a tile (64 exp2 + the dS arithmetic per row between two MMA phases).
+//   warps 16..23 two groups, one row per thread, each on half of the 64 key columns of every tile: P / dS to swizzled smem
+//                and nothing else -- they are the critical path of a tile (the exp2 and the dS arithmetic between two
+//                MMA phases), so both groups shorten the same tile instead of alternating tiles.
 #include "sel_launch.cuh"
 
 namespace fsa {
@@ -66,10 +67,16 @@ __device__ unsigned long long g_bwd_timing[512 * 64];
 #define BT_DECL unsigned long long _t0 = clock64(), _acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define BT_TOC(i) do { unsigned long long _t1 = clock64(); _acc[i] += _t1 - _t0; _t0 = _t1; } while (0)
 #define BT_DUMP(base, n) do { for (int _i = 0; _i < (n); ++_i) g_bwd_timing[blockIdx.x * 64 + (base) + _i] = _acc[_i]; } while (0)
+// Event trace of eight consecutive tiles of CTA 0 (absolute clock64() values), [tile][16 events].
+__device__ unsigned long long g_bwd_trace[8 * 16];
+constexpr int kTraceTile0 = 200;
+#define BT_EV(k, ev, who) do { if (blockIdx.x == 0 && (k) >= kTraceTile0 && (k) < kTraceTile0 + 8 && (who)) \
+        g_bwd_trace[((k) - kTraceTile0) * 16 + (ev)] = clock64(); } while (0)
 #else
 #define BT_DECL
 #define BT_TOC(i)
 #define BT_DUMP(base, n)
+#define BT_EV(k, ev, who)
 #endif
 
 template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -125,9 +132,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         for (int i = 0; i < 2; ++i) {
             mbar_init(&qd_full[i], kLoaders); mbar_init(&qd_empty[i], 1);
             mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-            mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 128);
+            mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 256);
         }
-        mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
+        mbar_init(pds_full, 256); mbar_init(pds_empty, 1);
         mbar_init(dq_full, 1); mbar_init(dq_empty, 128);
         mbar_init(acc_full, 1); mbar_init(acc_empty, 128);
         for (int i = 0; i < 4; ++i) { mbar_init(&off_full[i], 1); mbar_init(&off_empty[i], kWLoad + 1); }
@@ -169,8 +176,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         for (int k = 0; k < nloc && ok; ++k) {
             const int st = k & 1, slot = k & 3;
             BT_TOC(0);
-            ok = mbar_wait(&qd_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
-            BT_TOC(1);
             ok = mbar_wait(&off_full[slot], (k >> 2) & 1, status) && ok;
             BT_TOC(2);
             const int hq0 = (int)(((long long)s_h[slot] * s.G * p.q_sh) >> 3), hd0 = (int)(((long long)s_h[slot] * s.G * p.do_sh) >> 3);
@@ -180,6 +185,19 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             __syncwarp();
             if (lane == 0) mbar_arrive(&off_empty[slot]);
             BT_TOC(3);
+            // the stage is still in use by the tile two back: meanwhile ask for the rows to be brought into L2 (one request
+            // per 128-byte line), so that the copies below, which sit on the tile's critical path, do not wait for DRAM
+            if ((cchunk & 7) == 0) {
+#pragma unroll
+                for (int it = 0; it < NIT; ++it) {
+                    if (tok[it] < 0) continue;
+                    prefetch_l2(qc + ((long long)(tok[it] * qsn8 + hq0 + gq[it]) << 3));
+                    prefetch_l2(dc + ((long long)(tok[it] * dsn8 + hd0 + gd[it]) << 3));
+                }
+            }
+            ok = mbar_wait(&qd_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
+            BT_EV(k, 0, t == 0);
+            BT_TOC(1);
             const uint32_t dq_ = smem_u32(sQD + st * kQD) + slab_off;
             const uint32_t dd_ = dq_ + kTileRows * D * 2;
 #pragma unroll
@@ -192,6 +210,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 cp_async16(dd_ + so, dc + ((long long)(tk * dsn8 + hd0 + gd[it]) << 3), valid);
             }
             cp_async_mbar_arrive_noinc(&qd_full[st]);
+            BT_EV(k, 1, t == 0);
             BT_TOC(4);
         }
         if (t == 0) BT_DUMP(0, 5);
@@ -224,6 +243,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             // ---- dQ partial of this tile
             BT_TOC(0);
             ok = mbar_wait(dq_full, k & 1, status) && ok;
+            BT_EV(k, 13, warp == kWFlush && lane == 0);
             BT_TOC(1);
             tc_fence_after();
             if (lane == 0) bulk_wait_read0();          // the store of the previous tile has read this warp's staging rows
@@ -246,6 +266,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             }
             tc_fence_before();
             mbar_arrive(dq_empty);
+            BT_EV(k, 14, warp == kWFlush && lane == 0);
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -312,9 +333,11 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             }
             BT_TOC(2);
             ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;
+            BT_EV(k, 2, lane == 0);
             BT_TOC(3);
             fence_async_smem();
             ok = mbar_wait(&sdp_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
+            BT_EV(k, 3, lane == 0);
             BT_TOC(4);
             tc_fence_after();
             const uint32_t aq = qd_lo + (uint32_t)(st * (kQD >> 4));
@@ -335,6 +358,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 umma_commit(&sdp_full[st]);
             }
             __syncwarp();
+            BT_EV(k, 4, lane == 0);
             BT_TOC(5);
         }
         if (lane == 0) BT_DUMP(16, 6);
@@ -366,6 +390,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             if (first_of_block) { ++kvn; ++blk; }
             BT_TOC(0);
             ok = mbar_wait(pds_full, k & 1, status) && ok;
+            BT_EV(k, 9, lane == 0);
             BT_TOC(1);
             BT_TOC(2);
             ok = mbar_wait(&qd_full[st], (k >> 1) & 1, status) && ok;     // already complete: acquire only
@@ -393,7 +418,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 if (last_of_block) umma_commit(acc_full);
             }
             __syncwarp();
+            BT_EV(k, 10, lane == 0);
             ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
+            BT_EV(k, 11, lane == 0);
             tc_fence_after();
             if (leader) {
 #pragma unroll
@@ -405,6 +432,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 if (last_of_block) umma_commit(&kv_empty[kvn % kKVStages]);
             }
             __syncwarp();
+            BT_EV(k, 12, lane == 0);
             BT_TOC(5);
         }
         if (lane == 0) BT_DUMP(24, 6);
@@ -478,7 +506,9 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         }
       }
     } else {
-        // ------------------------------------------------------------------ P / dS and dQ epilogue
+        // ------------------------------------------------------------------ P / dS
+        // Both groups work on every tile, each on its 32 of the 64 key columns: the P / dS step sits on the tile's
+        // critical path (between the two MMA phases), so its latency counts, not only its throughput.
         reg_inc<kRegGroup>();
         const int sb = (warp - kWGroups) >> 2;
         const int quarter = warp & 3;
@@ -487,23 +517,15 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         const int g = r / s.TPT;
         const int e = r - g * s.TPT;
         const bool row_exists = g < s.G;
+        constexpr int HC = KT / 2;              // columns of this group
+        const int cb = sb * HC;
         bool ok = true;
-        // software pipeline over this group's tiles: entries two tiles ahead, lse / delta one ahead
+        // software pipeline over the tiles: entries two tiles ahead, lse / delta one ahead
         uint32_t entB = 0xFFFFFFFFu;            // entry of tile k + 2
-        uint32_t entA = 0xFFFFFFFFu;            // entry of tile k (after rotation)
+        uint32_t entA = 0xFFFFFFFFu;            // entry of tile k + 1 (after rotation)
         int row0A = 0, row0B = 0, hA = 0, hB = 0;
         float lseA = 0.f, deltaA = 0.f;
         int cloA = 0, chiA = 0;
-        // tile indices of this group's tiles k, k + 2, k + 4 without a division per tile: a cursor (run index, offset
-        // in the run) that advances by two
-        int cq = sb / sched.run, cr = sb % sched.run;
-        auto cursor_next = [&]() {
-            const int j = (cq * sched.grid + sched.cta) * sched.run + cr;
-            cr += 2;
-            while (cr >= sched.run) { cr -= sched.run; ++cq; }
-            return j;
-        };
-        int jA = 0, jB = 0;
         auto fetch_ent = [&](int j, uint32_t& ent, int& row0, int& h) {
             TileInfo ti = load_tile(p.ix, j);
             row0 = ti.row0; h = ti.h;
@@ -522,38 +544,32 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 visible_cols(p.bd, tok_, row0, key_lim, c_lo, c_hi);
             }
         };
-        if (sb < nloc) {
-            jA = cursor_next();
-            fetch_ent(jA, entA, row0A, hA);
+        if (nloc > 0) {
+            fetch_ent(sched.tile(0), entA, row0A, hA);
             fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
         }
-        if (sb + 2 < nloc) {
-            jB = cursor_next();
-            fetch_ent(jB, entB, row0B, hB);
-        }
+        if (nloc > 1) fetch_ent(sched.tile(1), entB, row0B, hB);
         BT_DECL;
-        for (int k = sb; k < nloc && ok; k += 2) {
+        for (int k = 0; k < nloc && ok; ++k) {
+            const int st = k & 1;
             const float lse_r = lseA, delta_s = deltaA;
             const int c_lo = cloA, c_hi = chiA;
             // rotate the prefetch registers
-            entA = entB; row0A = row0B; hA = hB; jA = jB;
-            if (k + 2 < nloc) fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
-            if (k + 4 < nloc) {
-                jB = cursor_next();
-                fetch_ent(jB, entB, row0B, hB);
-            }
+            entA = entB; row0A = row0B; hA = hB;
+            if (k + 1 < nloc) fetch_stats(entA, hA, row0A, lseA, deltaA, cloA, chiA);
+            if (k + 2 < nloc) fetch_ent(sched.tile(k + 2), entB, row0B, hB);
             BT_TOC(0);
-            ok = mbar_wait(&sdp_full[sb], (k >> 1) & 1, status) && ok;
+            ok = mbar_wait(&sdp_full[st], (k >> 1) & 1, status) && ok;
+            BT_EV(k, 5, sb == 0 && quarter == 0 && lane == 0);
             BT_TOC(1);
             tc_fence_after();
-            uint32_t pp[KT / 2], dd[KT / 2];
+            uint32_t pp[HC / 2], dd[HC / 2];
             // most tiles are fully visible to all their rows (only a token's own block is cut by causality)
             const bool all_visible = __all_sync(0xffffffffu, c_lo == 0 && c_hi == KT);
-#pragma unroll
-            for (int c0 = 0; c0 < KT; c0 += 32) {
+            {
                 uint32_t sv[32], dv[32];
-                tmem_ld32(tbase + lane_off + cS + sb * 128 + c0, sv);
-                tmem_ld32(tbase + lane_off + cDP + sb * 128 + c0, dv);
+                tmem_ld32(tbase + lane_off + cS + st * 128 + cb, sv);
+                tmem_ld32(tbase + lane_off + cDP + st * 128 + cb, dv);
                 tmem_ld_wait();
                 if (all_visible) {
 #pragma unroll
@@ -562,34 +578,37 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                         const float p1 = ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r));
                         const float d0 = p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s);
                         const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s);
-                        pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
-                        dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                        pp[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                        dd[i >> 1] = ElemTraits<ET>::pack2(d0, d1);
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
-                        const float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                        const float p0 = (cb + i >= c_lo && cb + i < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                        const float p1 = (cb + i + 1 >= c_lo && cb + i + 1 < c_hi) ? ex2_approx_b(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
                         const float d0 = p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s);
                         const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s);
-                        pp[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0, p1);
-                        dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                        pp[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                        dd[i >> 1] = ElemTraits<ET>::pack2(d0, d1);
                     }
                 }
             }
             tc_fence_before();
-            mbar_arrive(&sdp_empty[sb]);
+            mbar_arrive(&sdp_empty[st]);
+            BT_EV(k, 6, sb == 0 && quarter == 0 && lane == 0);
             BT_TOC(2);
             ok = mbar_wait(pds_empty, (k & 1) ^ 1, status) && ok;
+            BT_EV(k, 7, sb == 0 && quarter == 0 && lane == 0);
             BT_TOC(3);
 #pragma unroll
-            for (int ch = 0; ch < KT / 8; ++ch) {
-                const uint32_t off = sw128_chunk_off(r, ch);
-                *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
-                *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[ch * 4], dd[ch * 4 + 1], dd[ch * 4 + 2], dd[ch * 4 + 3]);
+            for (int c4 = 0; c4 < HC / 8; ++c4) {
+                const uint32_t off = sw128_chunk_off(r, sb * (HC / 8) + c4);
+                *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c4 * 4], pp[c4 * 4 + 1], pp[c4 * 4 + 2], pp[c4 * 4 + 3]);
+                *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[c4 * 4], dd[c4 * 4 + 1], dd[c4 * 4 + 2], dd[c4 * 4 + 3]);
             }
             fence_async_smem();
             mbar_arrive(pds_full);
+            BT_EV(k, 8, sb == 0 && quarter == 0 && lane == 0);
             BT_TOC(4);
             BT_TOC(6);
         }
@@ -625,6 +644,9 @@ static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const Sel
 }  // namespace fsa
 extern "C" int fsa_debug_read_bwd_timing(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, fsa::g_bwd_timing, (size_t)n * sizeof(unsigned long long));
+}
+extern "C" int fsa_debug_read_bwd_trace(unsigned long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, fsa::g_bwd_trace, sizeof(fsa::g_bwd_trace));
 }
 namespace fsa {
 #endif
