@@ -185,16 +185,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             __syncwarp();
             if (lane == 0) mbar_arrive(&off_empty[slot]);
             BT_TOC(3);
-            // the stage is still in use by the tile two back: meanwhile ask for the rows to be brought into L2 (one request
-            // per 128-byte line), so that the copies below, which sit on the tile's critical path, do not wait for DRAM
-            if ((cchunk & 7) == 0) {
-#pragma unroll
-                for (int it = 0; it < NIT; ++it) {
-                    if (tok[it] < 0) continue;
-                    prefetch_l2(qc + ((long long)(tok[it] * qsn8 + hq0 + gq[it]) << 3));
-                    prefetch_l2(dc + ((long long)(tok[it] * dsn8 + hd0 + gd[it]) << 3));
-                }
-            }
             ok = mbar_wait(&qd_empty[st], ((k >> 1) & 1) ^ 1, status) && ok;
             BT_EV(k, 0, t == 0);
             BT_TOC(1);

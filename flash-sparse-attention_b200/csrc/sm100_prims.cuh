@@ -156,11 +156,6 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // all but the newest 0 groups have finished READING their smem source
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Ask for the 128-byte line holding `ptr` to be brought into L2 (no register result, nothing to wait for).
-__device__ __forceinline__ void prefetch_l2(const void* ptr) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
-}
-
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
