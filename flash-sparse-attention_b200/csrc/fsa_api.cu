@@ -70,6 +70,22 @@ int make_tile_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t d0, 
     return FSA_OK;
 }
 
+// The same with a box of box2 entries along the third dimension (box {64, box1, box2}).
+int make_tile_map_3d_box(CUtensorMap* map, const void* base, int dtype, int64_t d0, int64_t d1, int64_t d2, int64_t stride1,
+                         int64_t stride2, int box1, int box2) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return cuda_fail(cudaErrorNotSupported);
+    cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)(d1 > 0 ? d1 : 1), (cuuint64_t)(d2 > 0 ? d2 : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)stride1 * 2, (cuuint64_t)stride2 * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box1, (cuuint32_t)box2};
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = fn(map, dtype == FSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail_at(cudaErrorInvalidValue, -(int)r - 100000);   // driver error code, negated
+    return FSA_OK;
+}
+
 int device_sm_count(int* out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -110,7 +126,7 @@ void prof_end(int id, cudaStream_t stream) {
 // Tensor-map encoding is a driver call and needs the primary context bound to the calling
 // thread; a thread that has only ever been handed device pointers (an autograd worker) may not
 // have one yet.  cudaSetDevice on the current device binds it.
-static int ensure_context() {
+int ensure_context() {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -420,6 +436,26 @@ int fsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* 
     return sel_bwd_impl(SelBounds{cu_seqlens_k, kv_lo, kv_hi}, Nk, q, k, v, o, lse, d_o, nullptr, cu_seqlens_q, N, B, Hq, Hk, D,
                         max_blocks, BK, dtype, q_sn, q_sh, k_sn, v_sn, o_sn, o_sh, do_sn, do_sh, sm_scale, dq, dk, dv, index_ws,
                         index_ws_bytes, scratch, scratch_bytes, stream_);
+}
+
+int fsa_range_attn_index(const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* kv_lo, const int32_t* kv_hi,
+                         int64_t N, int64_t Nk, int B, int Hq, int Hk, int max_blocks, int BK, void* index_ws,
+                         int64_t index_ws_bytes, void* stream_) {
+    if (!kv_hi || !cu_seqlens_k || !cu_seqlens_q) return FSA_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    (void)cudaGetLastError();
+    SelShape s;
+    int rc = make_shape(N, B, Hq, Hk, 0, max_blocks, BK, &s, Nk);
+    if (rc) return rc;
+    if (N == 0) return FSA_OK;
+    if (!index_ws || !aligned16(index_ws)) return FSA_ERR_BAD_ARG;
+    if (index_ws_bytes < sel_index_bytes(s)) return FSA_ERR_WORKSPACE;
+    SelIndex ix = sel_index_carve(index_ws, s);
+    prof_begin(FSA_KERNEL_SEL_INDEX, stream);
+    cudaError_t e = sel_build_index(nullptr, cu_seqlens_q, SelBounds{cu_seqlens_k, kv_lo, kv_hi}, s, ix, index_ws, stream);
+    prof_end(FSA_KERNEL_SEL_INDEX, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return FSA_OK;
 }
 
 int fsa_range_attn_bytes(int64_t N, int64_t Nk, int B, int Hq, int Hk, int D, int max_blocks, int BK, int64_t* index_bytes_out,

@@ -1,0 +1,418 @@
+// Range attention forward, query-tile-major ("dense") kernel for sm_100a: every token attends one contiguous range of
+// K/V rows, as in the compressed branch (replaces the forward of CompressedAttention,
+// nsa_ref/ops/compressed_attention.py:762-829, kernel :33-190) and in the sliding-window branch (replaces the
+// flash_attn_varlen_func call of fsa/module/fsa.py:149-159).
+//
+// One CTA = one tile of <= 128 rows = (query head of a GQA group, TPT consecutive tokens of one sequence) x one KV head.
+// The rows of the tile see neighbouring ranges, so the CTA walks the 64-row K/V tiles from the lowest row any of its rows
+// sees to the highest, keeps the output accumulator in TMEM across them (online softmax) and writes o and lse once: no
+// partial rows, no merge kernel, no index.  Two CTAs share an SM (96 KB of shared memory and 256 TMEM columns each), so
+// the softmax of one overlaps the MMAs of the other.
+//   warp 0      TMA producer: the Q tile once (3-D box: column, token, head -> head-major rows), K and V tiles through two
+//               rings of two stages (K is released by the S product, V by the P V product, so K runs a tile ahead);
+//   warp 1      one elected thread issues S(j+1) = Q K^T before the softmax of tile j is done, then O (+)= P(j) V(j);
+//   warps 2..5  one row per thread: scaled logits from TMEM, per-row range mask, running max / sum, P -> TMEM (input dtype,
+//               over S).  The reference max of a row is only raised when a tile exceeds it by more than 2^8 (the final
+//               o = O / l does not depend on the reference); then the warp waits for the previous P V product and
+//               rescales its 32 accumulator rows in TMEM.  Epilogue: o = O / l through swizzled staging (the Q tile's
+//               memory) and a 3-D TMA store, or plain stores for the last, partial tile of a sequence; lse = m + log2 l.
+#include "../../include/fsa_sm100.h"
+#include <climits>
+
+#include "sel_launch.cuh"
+
+namespace fsa {
+
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int box_rows);
+int make_tile_map_3d_box(CUtensorMap* map, const void* base, int dtype, int64_t d0, int64_t d1, int64_t d2, int64_t stride1,
+                         int64_t stride2, int box1, int box2);
+int ensure_context();
+
+struct RangeDenseParams {
+    const int32_t* cu_q;    // [B + 1]
+    const int32_t* cu_k;    // [B + 1] first K/V row of every sequence
+    const int32_t* kv_lo;   // [N] lowest visible K/V row of every token, or null (the sequence's first row)
+    const int32_t* kv_hi;   // [N] highest visible K/V row, lower than kv_lo when the token sees nothing
+    int64_t N, Nk;
+    int B, Hq, Hk, G, TPT;
+    float scale_log2;
+    void* o;  int64_t o_sn, o_sh;     // [N, Hq, D]
+    float* lse;                       // [Hq, N] log2 units
+    int* status;
+};
+
+constexpr int kRdThreads = 192;
+constexpr int kRdBK = 64;
+constexpr float kRdLazy = 8.0f;       // raise a row's reference max only when exceeded by more than this (log2 units)
+
+__device__ __forceinline__ float rd_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D, typename ET>
+__global__ void __launch_bounds__(kRdThreads, 2) range_fwd_dense(const RangeDenseParams p, const __grid_constant__ CUtensorMap qmap,
+                                                                const __grid_constant__ CUtensorMap kmap,
+                                                                const __grid_constant__ CUtensorMap vmap,
+                                                                const __grid_constant__ CUtensorMap omap) {
+    constexpr int BK = kRdBK;
+    constexpr int kQ = kTileRows * D * 2;            // Q tile, later the output staging
+    constexpr int kKt = BK * D * 2;                  // one K (or V) tile
+    constexpr int KH = D / 64;
+    constexpr uint32_t kCols = (2 * BK + D) <= 128 ? 128 : 256;
+    constexpr int cS = 0, cO = 2 * BK;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + kQ;
+    uint8_t* sV = sK + 2 * kKt;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * kKt);
+    uint64_t* q_full = bars;            // [1]
+    uint64_t* k_full = bars + 1;        // [2]
+    uint64_t* k_empty = bars + 3;       // [2]
+    uint64_t* v_full = bars + 5;        // [2]
+    uint64_t* v_empty = bars + 7;       // [2]
+    uint64_t* s_full = bars + 9;        // [2]
+    uint64_t* p_full = bars + 11;       // [2]
+    uint64_t* pv_done = bars + 13;      // [1]
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 14);
+    int* s_meta = reinterpret_cast<int*>(bars + 15);     // [0] sequence, [1] first token, [2] tokens, [3] first K/V row, [4] K/V tiles
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int* status = p.status;
+    const int h = blockIdx.y;
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128);
+        }
+        mbar_init(pv_done, 1);
+        mbar_init_fence();
+        tma_prefetch_desc(&qmap);
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        tma_prefetch_desc(&omap);
+    }
+    if (warp == 0) {
+        // which tile is this: sequences are cut into tiles of TPT tokens; the heaviest (last) tiles of the list start first
+        int total = 0;
+        for (int b = 0; b < p.B; ++b) total += (__ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b) + p.TPT - 1) / p.TPT;
+        const int want = total - 1 - (int)blockIdx.x;
+        int seq = -1, tok0 = 0, ne = 0;
+        if (want >= 0) {
+            int acc = 0;
+            for (int b = 0; b < p.B; ++b) {
+                const int s0 = __ldg(p.cu_q + b), L = __ldg(p.cu_q + b + 1) - s0;
+                const int nt = (L + p.TPT - 1) / p.TPT;
+                if (want < acc + nt) {
+                    seq = b;
+                    tok0 = s0 + (want - acc) * p.TPT;
+                    ne = min(p.TPT, s0 + L - tok0);
+                    break;
+                }
+                acc += nt;
+            }
+        }
+        // lowest and highest K/V row any token of the tile sees
+        int lo = INT_MAX, hi = -1;
+        if (seq >= 0) {
+            const int k0 = __ldg(p.cu_k + seq);
+            for (int e = lane; e < ne; e += 32) {
+                const int l = p.kv_lo ? __ldg(p.kv_lo + tok0 + e) : k0;
+                const int u = __ldg(p.kv_hi + tok0 + e);
+                if (u >= l) { lo = min(lo, l); hi = max(hi, u); }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+        }
+        if (lane == 0) {
+            lo = max(lo, 0);
+            hi = min(hi, (int)p.Nk - 1);
+            s_meta[0] = seq; s_meta[1] = tok0; s_meta[2] = ne; s_meta[3] = lo;
+            s_meta[4] = hi >= lo ? (hi - lo) / BK + 1 : 0;
+        }
+        tmem_alloc(&tmem_slot, kCols);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = tmem_slot;
+    const int seq = s_meta[0], tok0 = s_meta[1], ne = s_meta[2], row_lo = s_meta[3], nblk = s_meta[4];
+
+    if (seq >= 0) {
+        if (warp == 0) {
+            // ------------------------------------------------------------------ TMA producer
+            bool ok = true;
+            if (lane == 0 && nblk > 0) {
+                mbar_expect_tx(q_full, (uint32_t)(KH * 128 * p.TPT * p.G));
+#pragma unroll
+                for (int b = 0; b < KH; ++b) tma_load_3d(smem_u32(sQ + b * (kTileRows * 128)), &qmap, b * 64, tok0, h * p.G, q_full);
+            }
+            // K tile j and V tile j are loaded in the order the MMA warp needs them: K(0), K(1), V(0), K(2), V(1), ...
+            for (int step = 0; step < nblk + 1 && ok; ++step) {
+                if (lane == 0) {
+                    const int jk = step, jv = step - 1;
+                    if (jk < nblk) {
+                        const int st = jk & 1;
+                        ok = mbar_wait(&k_empty[st], ((jk >> 1) & 1) ^ 1, status) && ok;
+                        mbar_expect_tx(&k_full[st], (uint32_t)kKt);
+#pragma unroll
+                        for (int b = 0; b < KH; ++b)
+                            tma_load_2d(smem_u32(sK + st * kKt + b * (BK * 128)), &kmap, h * D + b * 64, row_lo + jk * BK, &k_full[st]);
+                    }
+                    if (jv >= 0) {
+                        const int st = jv & 1;
+                        ok = mbar_wait(&v_empty[st], ((jv >> 1) & 1) ^ 1, status) && ok;
+                        mbar_expect_tx(&v_full[st], (uint32_t)kKt);
+#pragma unroll
+                        for (int b = 0; b < KH; ++b)
+                            tma_load_2d(smem_u32(sV + st * kKt + b * (BK * 128)), &vmap, h * D + b * 64, row_lo + jv * BK, &v_full[st]);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------------------------ MMA issuer
+            const bool leader = elect_one();
+            constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
+            constexpr uint32_t idesc_o = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);
+            constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+            const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16);
+            const uint32_t k_lo = umma_desc_lo(smem_u32(sK), 16);
+            const uint32_t v_lo = umma_desc_lo(smem_u32(sV), BK * 128);     // MN-major: LBO = slab stride
+            bool ok = true;
+            auto issue_s = [&](int j) {
+                const int st = j & 1;
+                ok = mbar_wait(&k_full[st], (j >> 1) & 1, status) && ok;
+                tc_fence_after();
+                if (leader) {
+                    constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (BK * 128) >> 4;
+                    const uint32_t b_lo = k_lo + (uint32_t)(st * (kKt >> 4));
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks)
+                        umma_ss(tbase + cS + st * BK, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                                umma_desc_pack(b_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                    umma_commit(&k_empty[st]);
+                    umma_commit(&s_full[st]);
+                }
+                __syncwarp();
+            };
+            if (nblk > 0) {
+                ok = mbar_wait(q_full, 0, status) && ok;
+                issue_s(0);
+            }
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int st = j & 1;
+                // S(j + 1) overwrites the buffer P(j - 1) was read from by the product issued one iteration ago (in order)
+                if (j + 1 < nblk) issue_s(j + 1);
+                ok = mbar_wait(&p_full[st], (j >> 1) & 1, status) && ok;
+                ok = mbar_wait(&v_full[st], (j >> 1) & 1, status) && ok;
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t b_lo = v_lo + (uint32_t)(st * (kKt >> 4));
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks)
+                        umma_ts(tbase + cO, tbase + cS + st * BK + ks * 8, umma_desc_pack(b_lo + ks * (2048 >> 4), hi_1024), idesc_o,
+                                (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(&v_empty[st]);
+                    umma_commit(pv_done);
+                }
+                __syncwarp();
+            }
+        } else {
+            // ------------------------------------------------------------------ softmax and epilogue: one row per thread
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+            const int g = r / p.TPT, e = r - g * p.TPT;
+            const bool row_valid = g < p.G && e < ne;
+            const int tok = tok0 + e;
+            int lo_r = 0, hi_r = -1;
+            if (row_valid) {
+                lo_r = p.kv_lo ? __ldg(p.kv_lo + tok) : __ldg(p.cu_k + seq);
+                hi_r = __ldg(p.kv_hi + tok);
+            }
+            float m_ref = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int st = j & 1;
+                const int R0 = row_lo + j * BK;
+                const int c_lo = max(0, lo_r - R0), c_hi = min(BK, hi_r - R0 + 1);      // visible columns [c_lo, c_hi)
+                ok = mbar_wait(&s_full[st], (j >> 1) & 1, status) && ok;
+                tc_fence_after();
+                uint32_t v[BK];
+                tmem_ld32(tbase + lane_off + cS + st * BK, *reinterpret_cast<uint32_t (*)[32]>(&v[0]));
+                tmem_ld32(tbase + lane_off + cS + st * BK + 32, *reinterpret_cast<uint32_t (*)[32]>(&v[32]));
+                tmem_ld_wait();
+                if (c_lo > 0 || c_hi < BK) {
+#pragma unroll
+                    for (int i = 0; i < BK; ++i)
+                        if (i < c_lo || i >= c_hi) v[i] = 0xff800000u;      // -inf: exp2 gives exactly 0
+                }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < BK; i += 4) {
+                    mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
+                    mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
+                    mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
+                    mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
+                }
+                const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+                // raise the reference only when this tile exceeds it by a lot; the first finite maximum sets it
+                float alpha = 1.f;
+                const bool raise = m_blk > m_ref + kRdLazy;     // false when m_blk is -inf; true when m_ref is -inf and m_blk finite
+                if (raise) {
+                    alpha = m_ref == -INFINITY ? 0.f : rd_ex2(m_ref - m_blk);
+                    m_ref = m_blk;
+                }
+                // accumulator rows already hold products (j > 0): rescale them when any row of the warp changes reference
+                const bool scale_acc = __any_sync(0xffffffffu, raise && j > 0);
+                if (scale_acc) {
+                    ok = mbar_wait(pv_done, (j - 1) & 1, status) && ok;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t a[32];
+                        tmem_ld32(tbase + lane_off + cO + c0, a);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
+                        tmem_st32(tbase + lane_off + cO + c0, a);
+                    }
+                }
+                l_run *= alpha;
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;     // all columns masked so far: every p is exp2(-inf) = 0
+                float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[BK / 2];
+#pragma unroll
+                for (int i = 0; i < BK; i += 4) {
+                    const float p0 = rd_ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+                    const float p1 = rd_ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+                    const float p2 = rd_ex2(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m_use));
+                    const float p3 = rd_ex2(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_use));
+                    ls[0] += p0; ls[1] += p1; ls[2] += p2; ls[3] += p3;
+                    pk[i >> 1] = ElemTraits<ET>::pack2(p0, p1);
+                    pk[(i >> 1) + 1] = ElemTraits<ET>::pack2(p2, p3);
+                }
+                l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                tmem_st32(tbase + lane_off + cS + st * BK, *reinterpret_cast<uint32_t (*)[32]>(&pk[0]));
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&p_full[st]);
+            }
+            // ---- epilogue
+            if (nblk > 0) {
+                ok = mbar_wait(pv_done, (nblk - 1) & 1, status) && ok;
+                tc_fence_after();
+            }
+            const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+            if (row_valid && ok) p.lse[(int64_t)(h * p.G + g) * p.N + tok] = l_run > 0.f ? m_ref + log2f(l_run) : -INFINITY;
+            const bool full_tile = ne == p.TPT && p.G * p.TPT == kTileRows;      // whole box inside the sequence, every row staged
+            uint8_t* my_stage = sQ + quarter * (32 * 128);     // per 64-column slab: rows of this warp at (slab base) + 32 * 128 * quarter
+            ET* orow = reinterpret_cast<ET*>(p.o) + (int64_t)tok * p.o_sn + (int64_t)(h * p.G + g) * p.o_sh;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t a[32];
+                if (nblk > 0) {
+                    tmem_ld32(tbase + lane_off + cO + c0, a);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) a[i] = 0u;
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 x;
+                    x.x = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 0]) * inv_l, __uint_as_float(a[q4 * 8 + 1]) * inv_l);
+                    x.y = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 2]) * inv_l, __uint_as_float(a[q4 * 8 + 3]) * inv_l);
+                    x.z = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 4]) * inv_l, __uint_as_float(a[q4 * 8 + 5]) * inv_l);
+                    x.w = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 6]) * inv_l, __uint_as_float(a[q4 * 8 + 7]) * inv_l);
+                    const int chunk = (c0 >> 3) + q4;
+                    if (full_tile) {
+                        *reinterpret_cast<uint4*>(sQ + (chunk >> 3) * (kTileRows * 128) + sw128_chunk_off(r, chunk & 7)) = x;
+                    } else if (row_valid && ok) {
+                        *reinterpret_cast<uint4*>(orow + chunk * 8) = x;
+                    }
+                }
+            }
+            (void)my_stage;
+            if (full_tile) {
+                // all four warps have staged their rows: one 3-D store per 64-column slab
+                fence_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0 && ok) {
+#pragma unroll
+                    for (int b = 0; b < KH; ++b) tma_store_3d(&omap, b * 64, tok0, h * p.G, smem_u32(sQ + b * (kTileRows * 128)));
+                    bulk_commit();
+                    bulk_wait0();
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, kCols);
+}
+
+template <int D, typename ET>
+static cudaError_t launch_rd(const RangeDenseParams& p, const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                             const CUtensorMap& omap, int max_tiles, cudaStream_t stream) {
+    constexpr int smem = kTileRows * D * 2 + 4 * kRdBK * D * 2 + 256;
+    auto kern = range_fwd_dense<D, ET>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    prof_begin(FSA_KERNEL_RANGE_DENSE, stream);
+    kern<<<dim3((unsigned)max_tiles, (unsigned)p.Hk), kRdThreads, smem, stream>>>(p, qmap, kmap, vmap, omap);
+    prof_end(FSA_KERNEL_RANGE_DENSE, stream);
+    return cudaGetLastError();
+}
+
+}  // namespace fsa
+
+using namespace fsa;
+
+extern "C" int fsa_range_attn_fwd_dense(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                                        const int32_t* cu_seqlens_k, const int32_t* kv_lo, const int32_t* kv_hi, int64_t N, int64_t Nk,
+                                        int B, int Hq, int Hk, int D, int dtype, int64_t q_sn, int64_t q_sh, int64_t k_sn, int64_t v_sn,
+                                        float sm_scale, void* o, int64_t o_sn, int64_t o_sh, float* lse, int32_t* status, void* stream_) {
+    if (N < 0 || Nk < 0 || B < 0 || Hq <= 0 || Hk <= 0 || Hq % Hk != 0) return FSA_ERR_BAD_ARG;
+    if (dtype != FSA_DTYPE_BF16 && dtype != FSA_DTYPE_FP16) return FSA_ERR_BAD_ARG;
+    if (D != 64 && D != 128) return FSA_ERR_UNSUPPORTED;
+    const int G = Hq / Hk;
+    if (G > 32) return FSA_ERR_UNSUPPORTED;
+    if (!(sm_scale > 0.f)) return FSA_ERR_BAD_ARG;
+    if (N == 0 || B == 0) return FSA_OK;
+    if (!q || !k || !v || !cu_seqlens_q || !cu_seqlens_k || !kv_hi || !o || !lse || Nk == 0) return FSA_ERR_BAD_ARG;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)o & 15)) return FSA_ERR_BAD_ARG;
+    if ((q_sn % 8) || (q_sh % 8) || (k_sn % 8) || (v_sn % 8) || (o_sn % 8) || (o_sh % 8)) return FSA_ERR_BAD_ARG;
+    if (k_sn < (int64_t)Hk * D || v_sn < (int64_t)Hk * D) return FSA_ERR_BAD_ARG;
+    (void)cudaGetLastError();
+    int rc = ensure_context();
+    if (rc) return rc;
+    const int TPT = (kTileRows / G) & ~3;
+    CUtensorMap qmap, kmap, vmap, omap;
+    if ((rc = make_tile_map_3d_box(&qmap, q, dtype, D, N, Hq, q_sn, q_sh, TPT, G))) return rc;
+    if ((rc = make_tile_map_3d_box(&omap, o, dtype, D, N, Hq, o_sn, o_sh, TPT, G))) return rc;
+    if ((rc = make_tile_map(&kmap, k, dtype, Nk, (int64_t)Hk * D, k_sn, 64))) return rc;
+    if ((rc = make_tile_map(&vmap, v, dtype, Nk, (int64_t)Hk * D, v_sn, 64))) return rc;
+    RangeDenseParams p;
+    p.cu_q = cu_seqlens_q; p.cu_k = cu_seqlens_k; p.kv_lo = kv_lo; p.kv_hi = kv_hi;
+    p.N = N; p.Nk = Nk; p.B = B; p.Hq = Hq; p.Hk = Hk; p.G = G; p.TPT = TPT;
+    p.scale_log2 = sm_scale * 1.4426950408889634f;
+    p.o = o; p.o_sn = o_sn; p.o_sh = o_sh; p.lse = lse; p.status = status;
+    const int max_tiles = (int)((N + TPT - 1) / TPT) + B;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    cudaError_t e;
+    if (dtype == FSA_DTYPE_BF16)
+        e = D == 128 ? launch_rd<128, __nv_bfloat16>(p, qmap, kmap, vmap, omap, max_tiles, stream)
+                     : launch_rd<64, __nv_bfloat16>(p, qmap, kmap, vmap, omap, max_tiles, stream);
+    else
+        e = D == 128 ? launch_rd<128, __half>(p, qmap, kmap, vmap, omap, max_tiles, stream)
+                     : launch_rd<64, __half>(p, qmap, kmap, vmap, omap, max_tiles, stream);
+    return e == cudaSuccess ? FSA_OK : FSA_ERR_CUDA;
+}

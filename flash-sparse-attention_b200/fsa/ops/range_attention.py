@@ -34,6 +34,10 @@ def _sizes(N, Nk, B, Hq, Hk, D, max_blocks):
 
 
 class RangeAttention(torch.autograd.Function):
+    """Forward: the query-tile-major kernel (``fsa_range_attn_fwd_dense``: accumulator in TMEM across the K/V tiles, no
+    partial rows) for head sizes 64 / 128, else the block-major kernels.  Backward: the block-major kernels on a tile
+    index (built in the backward when the forward did not leave one)."""
+
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, kv_lo, kv_hi, max_blocks, sm_scale):
         assert q.is_cuda, "the sm_100a kernels need CUDA tensors (no CPU fallback)"
@@ -45,20 +49,31 @@ class RangeAttention(torch.autograd.Function):
         B = cu_q.numel() - 1
         q, k, v = _prep(q), _prep(k, True), _prep(v, True)
         dev = q.device
-        ib, fb, _ = _sizes(N, Nk, B, Hq, Hk, D, max_blocks)
-        index_ws, scratch = _alloc_bytes(ib, dev), _alloc_bytes(fb, dev)
         o = torch.empty((N, Hq, D), dtype=q.dtype, device=dev)
         lse = torch.empty((Hq, N), dtype=torch.float32, device=dev)
+        dense = D in (64, 128) and Hq // Hk <= 32
+        index_ws = None
         with torch.cuda.device(dev):
-            rc = L.fsa_range_attn_fwd(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(kv_lo), _lib.ptr(kv_hi),
-                N, Nk, B, Hq, Hk, D, max_blocks, BLOCK, _lib.DTYPE_CODE[q.dtype],
-                q.stride(0), q.stride(1), k.stride(0), v.stride(0), float(sm_scale),
-                _lib.ptr(o), o.stride(0), o.stride(1), _lib.ptr(lse),
-                _lib.ptr(index_ws), index_ws.numel(), _lib.ptr(scratch), scratch.numel(), _lib.current_stream(dev))
-            _lib.check(rc, "fsa_range_attn_fwd")
-        ctx.save_for_backward(q, k, v, o, lse, cu_q, cu_k, kv_lo if kv_lo is not None else torch.empty(0), kv_hi, index_ws)
+            if dense:
+                rc = L.fsa_range_attn_fwd_dense(
+                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(kv_lo), _lib.ptr(kv_hi),
+                    N, Nk, B, Hq, Hk, D, _lib.DTYPE_CODE[q.dtype], q.stride(0), q.stride(1), k.stride(0), v.stride(0),
+                    float(sm_scale), _lib.ptr(o), o.stride(0), o.stride(1), _lib.ptr(lse), None, _lib.current_stream(dev))
+                _lib.check(rc, "fsa_range_attn_fwd_dense")
+            else:
+                ib, fb, _ = _sizes(N, Nk, B, Hq, Hk, D, max_blocks)
+                index_ws, scratch = _alloc_bytes(ib, dev), _alloc_bytes(fb, dev)
+                rc = L.fsa_range_attn_fwd(
+                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(kv_lo), _lib.ptr(kv_hi),
+                    N, Nk, B, Hq, Hk, D, max_blocks, BLOCK, _lib.DTYPE_CODE[q.dtype],
+                    q.stride(0), q.stride(1), k.stride(0), v.stride(0), float(sm_scale),
+                    _lib.ptr(o), o.stride(0), o.stride(1), _lib.ptr(lse),
+                    _lib.ptr(index_ws), index_ws.numel(), _lib.ptr(scratch), scratch.numel(), _lib.current_stream(dev))
+                _lib.check(rc, "fsa_range_attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse, cu_q, cu_k, kv_lo if kv_lo is not None else torch.empty(0), kv_hi,
+                              index_ws if index_ws is not None else torch.empty(0))
         ctx.has_lo = kv_lo is not None
+        ctx.has_index = index_ws is not None
         ctx.max_blocks = max_blocks
         ctx.sm_scale = sm_scale
         ctx.mark_non_differentiable(lse)
@@ -74,8 +89,14 @@ class RangeAttention(torch.autograd.Function):
         B = cu_q.numel() - 1
         do = _prep(do)
         dev = q.device
-        _, _, bb = _sizes(N, Nk, B, Hq, Hk, D, ctx.max_blocks)
+        ib, _, bb = _sizes(N, Nk, B, Hq, Hk, D, ctx.max_blocks)
         scratch = _alloc_bytes(bb, dev)
+        if not ctx.has_index:
+            index_ws = _alloc_bytes(ib, dev)
+            with torch.cuda.device(dev):
+                rc = L.fsa_range_attn_index(_lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(kv_lo), _lib.ptr(kv_hi), N, Nk, B, Hq, Hk,
+                                            ctx.max_blocks, BLOCK, _lib.ptr(index_ws), index_ws.numel(), _lib.current_stream(dev))
+            _lib.check(rc, "fsa_range_attn_index")
         dq = torch.empty((N, Hq, D), dtype=q.dtype, device=dev)
         dk = torch.empty((Nk, Hk, D), dtype=q.dtype, device=dev)
         dv = torch.empty((Nk, Hk, D), dtype=q.dtype, device=dev)

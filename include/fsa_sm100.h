@@ -55,7 +55,8 @@ int fsa_last_cuda_error_line(void);
 #define FSA_KERNEL_SEL_FWD_REDUCE 1
 #define FSA_KERNEL_SEL_BWD_MAIN 2
 #define FSA_KERNEL_SEL_BWD_DQ_REDUCE 3
-#define FSA_KERNEL_SEL_INDEX 4          /* the index build of a forward (several small kernels) */
+#define FSA_KERNEL_SEL_INDEX 4            /* the index build of a forward (several small kernels) */
+#define FSA_KERNEL_RANGE_DENSE 5
 int fsa_profile_enable(int on);
 int fsa_profile_read(int kernel_id, float* ms_sum_out, int* launches_out);
 
@@ -167,6 +168,23 @@ int fsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* 
                        int64_t o_stride_h, int64_t do_stride_n, int64_t do_stride_h, float sm_scale, void* dq, void* dk,
                        void* dv, void* index_ws, int64_t index_ws_bytes, void* scratch, int64_t scratch_bytes,
                        void* stream);
+
+/* Range attention forward without partial rows: one CTA per tile of consecutive query tokens walks the K/V rows its
+ * tokens see and keeps the output accumulator in TMEM (online softmax); o and lse are written once, no index and no
+ * scratch are needed.  Same arguments and results as fsa_range_attn_fwd (it replaces the same reference code: the
+ * forward of CompressedAttention, nsa_ref/ops/compressed_attention.py:33-190, :762-829, and the sliding-window
+ * flash_attn_varlen_func call of fsa/module/fsa.py:149-159).  head_dim 64 or 128, GQA group <= 32.  status: a device int
+ * (zeroed by the caller) that receives a non-zero code if a bounded wait ran out, or NULL.
+ * fsa_range_attn_bwd needs the tile index that fsa_range_attn_fwd leaves in index_ws; after this forward, build it
+ * with fsa_range_attn_index (same max_blocks / block_size as the backward call). */
+int fsa_range_attn_fwd_dense(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                             const int32_t* cu_seqlens_k, const int32_t* kv_lo, const int32_t* kv_hi, int64_t total_tokens,
+                             int64_t total_kv_rows, int batch, int num_q_heads, int num_kv_heads, int head_dim, int dtype,
+                             int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n, int64_t v_stride_n, float sm_scale,
+                             void* o, int64_t o_stride_n, int64_t o_stride_h, float* lse, int32_t* status, void* stream);
+int fsa_range_attn_index(const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* kv_lo, const int32_t* kv_hi,
+                         int64_t total_tokens, int64_t total_kv_rows, int batch, int num_q_heads, int num_kv_heads,
+                         int max_blocks, int block_size, void* index_ws, int64_t index_ws_bytes, void* stream);
 
 /* K/V compression forward: y[c, h, :] = sum_k x[s_b + c * stride + k, h, :] @ W[h, k*d:(k+1)*d, :] (+ bias[h, :]) for the
  * n_b = floor((L_b - kernel_size) / stride) + 1 windows of every sequence (0 when L_b < kernel_size).  Replaces

@@ -65,3 +65,57 @@ def test_compressed_branch(seqlens, Hk, G, d, ks, stride):
     _tol_ok(qc.grad, dq_ref, "dq")
     _tol_ok(kc.grad, dk_ref, "dk")
     _tol_ok(vc.grad, dv_ref, "dv")
+
+
+@pytest.mark.parametrize("seqlens,Hk,G,d,W,dtype,qscale", [
+    ([300, 41], 1, 3, 128, 100, torch.bfloat16, 1.0),       # 40 tokens per tile: 120 of the 128 tile rows are used
+    ([513], 2, 8, 128, 64, torch.bfloat16, 1.0),
+    ([260, 90], 1, 16, 64, 200, torch.float16, 1.0),        # 8 tokens per tile
+    ([1200], 1, 2, 128, 1024, torch.bfloat16, 6.0),         # logits of magnitude ~70: the reference max of a row is raised
+                                                            # while the accumulator already holds products (rescale in TMEM)
+    ([900], 2, 4, 64, 300, torch.bfloat16, 5.0),
+])
+def test_query_major_forward_shapes(seqlens, Hk, G, d, W, dtype, qscale):
+    """Forward of the query-tile-major kernel on group sizes / dtypes / logit ranges beyond the cases above, with q as a
+    strided view of a fused projection (token stride > heads * d)."""
+    N = sum(seqlens)
+    g = torch.Generator().manual_seed(3 * N + W)
+    fused = (torch.randn(N, 2 * Hk * G * d, generator=g) * qscale).to(dtype)
+    q = fused[:, Hk * G * d :].view(N, Hk * G, d)
+    k = torch.randn(N, Hk, d, generator=g).to(dtype)
+    v = torch.randn(N, Hk, d, generator=g).to(dtype)
+    cu = make_cu_seqlens(seqlens)
+    o_ref, lse_ref = orc.sliding_window_attention(q.float(), k.float(), v.float(), cu, W)
+    o, lse = sliding_window_attention(fused.to(DEV)[:, Hk * G * d :].view(N, Hk * G, d), k.to(DEV), v.to(DEV), cu.to(DEV), W)
+    _tol_ok(o, o_ref, "o")
+    fin = torch.isfinite(lse_ref)
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    assert float((lse.cpu()[fin] - lse_ref[fin]).abs().max()) <= 1e-4 * max(1.0, float(lse_ref[fin].abs().max()))
+
+
+def test_query_major_forward_rows_without_keys():
+    """Tokens whose range is empty (kv_hi < kv_lo) get o = 0 and lse = -inf, also when a whole tile sees nothing."""
+    from fsa.ops.range_attention import range_attention
+
+    N, Hk, G, d = 400, 1, 2, 128
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(N, Hk * G, d, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(N, Hk, d, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(N, Hk, d, generator=g).to(torch.bfloat16).to(DEV)
+    cu = make_cu_seqlens([N]).to(DEV)
+    tok = torch.arange(N, dtype=torch.int32, device=DEV)
+    hi = tok.clone()
+    hi[:130] = -1                      # the first two tiles (64 tokens each) see nothing, the third partly
+    hi[300:310] = -1
+    lo = torch.clamp(tok - 50, min=0)
+    o, lse = range_attention(q, k, v, cu, cu, lo, hi, (50 + 1 + 63) // 64 + 1)
+    dead = hi < 0
+    assert float(o[dead].abs().max()) == 0 and bool(torch.isinf(lse[:, dead]).all())
+    # the rest against plain softmax attention over the same ranges
+    qf, kf, vf = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    for t in (130, 200, 299, 310, 399):
+        a, b = int(lo[t]), int(hi[t])
+        for hq in range(Hk * G):
+            s = (kf[a : b + 1, hq // G] @ qf[t, hq]) / d ** 0.5
+            ref = torch.softmax(s, 0) @ vf[a : b + 1, hq // G]
+            assert float((o[t, hq].float().cpu() - ref).abs().max()) <= 2e-2
