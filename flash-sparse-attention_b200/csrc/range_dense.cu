@@ -372,6 +372,333 @@ static cudaError_t launch_rd(const RangeDenseParams& p, const CUtensorMap& qmap,
     return cudaGetLastError();
 }
 
+
+// ------------------------------------------------------------------------------------------------ dQ, query-tile-major
+// dQ of range attention with the same tiling as the forward above: per K/V tile S = Q K^T and dP = dO V^T, then
+// P = exp2(S c - lse), dS = scale P (dP - delta) to swizzled shared memory, dQ (+)= dS K accumulated in TMEM over the
+// tiles and written once.  (In the reference: the dQ part of _backward_kernel, nsa_ref/ops/compressed_attention.py:
+// 193-760, and of flash-attn's backward for the sliding window.)  With it the block-major backward kernel computes
+// only dK and dV and no partial dQ row is written or merged.  Two CTAs per SM (112 KB of shared memory, 256 TMEM columns
+// each), every buffer single: one CTA's dependent chain is covered by the other.
+struct RangeDqParams {
+    const int32_t* cu_q;
+    const int32_t* cu_k;
+    const int32_t* kv_lo;
+    const int32_t* kv_hi;
+    int64_t N, Nk;
+    int B, Hq, Hk, G, TPT;
+    float scale, scale_log2;
+    const float* lse;       // [Hq, N] log2 units
+    const float* delta;     // [Hq, N] sum_d o dO
+    void* dq;               // [N, Hq, D] contiguous
+    int* status;
+};
+
+template <typename ET>
+__global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeDqParams p, const __grid_constant__ CUtensorMap qmap,
+                                                                   const __grid_constant__ CUtensorMap domap,
+                                                                   const __grid_constant__ CUtensorMap kmap,
+                                                                   const __grid_constant__ CUtensorMap vmap,
+                                                                   const __grid_constant__ CUtensorMap dqmap) {
+    constexpr int D = 128, BK = kRdBK, KH = D / 64;
+    constexpr int kQ = kTileRows * D * 2;            // Q tile (later the dQ staging), same for dO
+    constexpr int kKt = BK * D * 2;
+    constexpr int kDS = kTileRows * BK * 2;
+    constexpr uint32_t kCols = 256;
+    constexpr int cS = 0, cDP = BK, cDQ = 2 * BK;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sDO = sQ + kQ;
+    uint8_t* sK = sDO + kQ;
+    uint8_t* sV = sK + kKt;
+    uint8_t* sDS = sV + kKt;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kDS);
+    uint64_t* qd_full = bars;           // Q and dO tiles have landed
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 2;       // the dQ product of the tile is done (K read, dS read)
+    uint64_t* v_full = bars + 3;
+    uint64_t* v_empty = bars + 4;       // S and dP of the tile are done (V read)
+    uint64_t* sdp_full = bars + 5;
+    uint64_t* sdp_free = bars + 6;      // the 128 row threads have read S and dP
+    uint64_t* ds_full = bars + 7;       // ... have written dS
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 8);
+    int* s_meta = reinterpret_cast<int*>(bars + 9);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int* status = p.status;
+    const int h = blockIdx.y;
+    if (tid == 0) {
+        mbar_init(qd_full, 1);
+        mbar_init(k_full, 1); mbar_init(k_empty, 1);
+        mbar_init(v_full, 1); mbar_init(v_empty, 1);
+        mbar_init(sdp_full, 1); mbar_init(sdp_free, 128); mbar_init(ds_full, 128);
+        mbar_init_fence();
+        tma_prefetch_desc(&qmap);
+        tma_prefetch_desc(&domap);
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        tma_prefetch_desc(&dqmap);
+    }
+    if (warp == 0) {
+        int total = 0;
+        for (int b = 0; b < p.B; ++b) total += (__ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b) + p.TPT - 1) / p.TPT;
+        const int want = total - 1 - (int)blockIdx.x;
+        int seq = -1, tok0 = 0, ne = 0;
+        if (want >= 0) {
+            int acc = 0;
+            for (int b = 0; b < p.B; ++b) {
+                const int s0 = __ldg(p.cu_q + b), L = __ldg(p.cu_q + b + 1) - s0;
+                const int nt = (L + p.TPT - 1) / p.TPT;
+                if (want < acc + nt) {
+                    seq = b;
+                    tok0 = s0 + (want - acc) * p.TPT;
+                    ne = min(p.TPT, s0 + L - tok0);
+                    break;
+                }
+                acc += nt;
+            }
+        }
+        int lo = INT_MAX, hi = -1;
+        if (seq >= 0) {
+            const int k0 = __ldg(p.cu_k + seq);
+            for (int e = lane; e < ne; e += 32) {
+                const int l = p.kv_lo ? __ldg(p.kv_lo + tok0 + e) : k0;
+                const int u = __ldg(p.kv_hi + tok0 + e);
+                if (u >= l) { lo = min(lo, l); hi = max(hi, u); }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+        }
+        if (lane == 0) {
+            lo = max(lo, 0);
+            hi = min(hi, (int)p.Nk - 1);
+            s_meta[0] = seq; s_meta[1] = tok0; s_meta[2] = ne; s_meta[3] = lo;
+            s_meta[4] = hi >= lo ? (hi - lo) / BK + 1 : 0;
+        }
+        tmem_alloc(&tmem_slot, kCols);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = tmem_slot;
+    const int seq = s_meta[0], tok0 = s_meta[1], ne = s_meta[2], row_lo = s_meta[3], nblk = s_meta[4];
+
+    if (seq >= 0) {
+        if (warp == 0) {
+            // ------------------------------------------------------------------ TMA producer
+            bool ok = true;
+            if (lane == 0 && nblk > 0) {
+                mbar_expect_tx(qd_full, (uint32_t)(2 * KH * 128 * p.TPT * p.G));
+#pragma unroll
+                for (int b = 0; b < KH; ++b) {
+                    tma_load_3d(smem_u32(sQ + b * (kTileRows * 128)), &qmap, b * 64, tok0, h * p.G, qd_full);
+                    tma_load_3d(smem_u32(sDO + b * (kTileRows * 128)), &domap, b * 64, tok0, h * p.G, qd_full);
+                }
+            }
+            for (int j = 0; j < nblk && ok; ++j) {
+                if (lane == 0) {
+                    ok = mbar_wait(k_empty, (j & 1) ^ 1, status) && ok;
+                    mbar_expect_tx(k_full, (uint32_t)kKt);
+#pragma unroll
+                    for (int b = 0; b < KH; ++b)
+                        tma_load_2d(smem_u32(sK + b * (BK * 128)), &kmap, h * D + b * 64, row_lo + j * BK, k_full);
+                    ok = mbar_wait(v_empty, (j & 1) ^ 1, status) && ok;
+                    mbar_expect_tx(v_full, (uint32_t)kKt);
+#pragma unroll
+                    for (int b = 0; b < KH; ++b)
+                        tma_load_2d(smem_u32(sV + b * (BK * 128)), &vmap, h * D + b * 64, row_lo + j * BK, v_full);
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------------------------ MMA issuer
+            const bool leader = elect_one();
+            constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
+            constexpr uint32_t idesc_dq = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);     // dS (K-major) x K (MN-major)
+            constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+            constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (BK * 128) >> 4;
+            const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16), do_lo = umma_desc_lo(smem_u32(sDO), 16);
+            const uint32_t k_lo = umma_desc_lo(smem_u32(sK), 16), v_lo = umma_desc_lo(smem_u32(sV), 16);
+            const uint32_t ds_lo = umma_desc_lo(smem_u32(sDS), 16);
+            const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sK), BK * 128);
+            bool ok = true;
+            if (nblk > 0) ok = mbar_wait(qd_full, 0, status) && ok;
+            for (int j = 0; j < nblk && ok; ++j) {
+                ok = mbar_wait(k_full, j & 1, status) && ok;
+                ok = mbar_wait(v_full, j & 1, status) && ok;
+                ok = mbar_wait(sdp_free, (j & 1) ^ 1, status) && ok;       // S / dP of the previous tile have been read
+                tc_fence_after();
+                if (leader) {
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks)
+                        umma_ss(tbase + cS, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                                umma_desc_pack(k_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks)
+                        umma_ss(tbase + cDP, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                                umma_desc_pack(v_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                    umma_commit(v_empty);
+                    umma_commit(sdp_full);
+                }
+                __syncwarp();
+                ok = mbar_wait(ds_full, j & 1, status) && ok;
+                fence_async_smem();
+                tc_fence_after();
+                if (leader) {
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks)
+                        umma_ss(tbase + cDQ, umma_desc_pack(ds_lo + ks * 2, hi_1024), umma_desc_pack(k_mn_lo + ks * (2048 >> 4), hi_1024),
+                                idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(k_empty);
+                }
+                __syncwarp();
+            }
+        } else {
+            // ------------------------------------------------------------------ P / dS and the epilogue: one row per thread
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+            const int g = r / p.TPT, e = r - g * p.TPT;
+            const bool row_valid = g < p.G && e < ne;
+            const int tok = tok0 + e;
+            int lo_r = 0, hi_r = -1;
+            float lse_r = 0.f, delta_s = 0.f;
+            if (row_valid) {
+                lo_r = p.kv_lo ? __ldg(p.kv_lo + tok) : __ldg(p.cu_k + seq);
+                hi_r = __ldg(p.kv_hi + tok);
+                const int64_t idx = (int64_t)(h * p.G + g) * p.N + tok;
+                lse_r = __ldg(p.lse + idx);
+                delta_s = __ldg(p.delta + idx) * p.scale;
+                if (!(lse_r > -INFINITY)) hi_r = lo_r - 1;      // a row that saw nothing in the forward sees nothing here
+            }
+            bool ok = true;
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int R0 = row_lo + j * BK;
+                const int c_lo = max(0, lo_r - R0), c_hi = min(BK, hi_r - R0 + 1);
+                ok = mbar_wait(sdp_full, j & 1, status) && ok;
+                tc_fence_after();
+                uint32_t dd[BK / 2];
+                const bool all_visible = __all_sync(0xffffffffu, c_lo == 0 && c_hi == BK);
+#pragma unroll
+                for (int c0 = 0; c0 < BK; c0 += 32) {
+                    uint32_t sv[32], dv[32];
+                    tmem_ld32(tbase + lane_off + cS + c0, sv);
+                    tmem_ld32(tbase + lane_off + cDP + c0, dv);
+                    tmem_ld_wait();
+                    if (all_visible) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = rd_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r));
+                            const float p1 = rd_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r));
+                            dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s),
+                                                                      p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? rd_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                            const float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? rd_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                            const float d0 = p0 > 0.f ? p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s) : 0.f;
+                            const float d1 = p1 > 0.f ? p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s) : 0.f;
+                            dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(sdp_free);
+                // the dQ product of the previous tile has read dS: k_empty completes with it
+                if (j > 0) ok = mbar_wait(k_empty, (j - 1) & 1, status) && ok;
+#pragma unroll
+                for (int ch = 0; ch < BK / 8; ++ch)
+                    *reinterpret_cast<uint4*>(sDS + sw128_chunk_off(r, ch)) = make_uint4(dd[ch * 4], dd[ch * 4 + 1], dd[ch * 4 + 2], dd[ch * 4 + 3]);
+                fence_async_smem();
+                mbar_arrive(ds_full);
+            }
+            // ---- epilogue
+            if (nblk > 0) {
+                ok = mbar_wait(k_empty, (nblk - 1) & 1, status) && ok;
+                tc_fence_after();
+            }
+            const bool full_tile = ne == p.TPT && p.G * p.TPT == kTileRows;
+            ET* drow = reinterpret_cast<ET*>(p.dq) + ((int64_t)tok * p.Hq + (h * p.G + g)) * D;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t a[32];
+                if (nblk > 0) {
+                    tmem_ld32(tbase + lane_off + cDQ + c0, a);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) a[i] = 0u;
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 x;
+                    x.x = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 0]), __uint_as_float(a[q4 * 8 + 1]));
+                    x.y = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 2]), __uint_as_float(a[q4 * 8 + 3]));
+                    x.z = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 4]), __uint_as_float(a[q4 * 8 + 5]));
+                    x.w = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 6]), __uint_as_float(a[q4 * 8 + 7]));
+                    const int chunk = (c0 >> 3) + q4;
+                    if (full_tile) {
+                        *reinterpret_cast<uint4*>(sQ + (chunk >> 3) * (kTileRows * 128) + sw128_chunk_off(r, chunk & 7)) = x;
+                    } else if (row_valid && ok) {
+                        *reinterpret_cast<uint4*>(drow + chunk * 8) = x;
+                    }
+                }
+            }
+            if (full_tile) {
+                fence_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0 && ok) {
+#pragma unroll
+                    for (int b = 0; b < KH; ++b) tma_store_3d(&dqmap, b * 64, tok0, h * p.G, smem_u32(sQ + b * (kTileRows * 128)));
+                    bulk_commit();
+                    bulk_wait0();
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, kCols);
+}
+
+// dQ of a range-attention backward (head_dim 128).  q / dO strided, dq contiguous [N, Hq, 128].
+cudaError_t launch_range_bwd_dq(int dtype, const SelBwdArgs& a, const SelShape& s, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                                int* status, cudaStream_t stream) {
+    CUtensorMap qmap, domap, dqmap;
+    if (make_tile_map_3d_box(&qmap, a.q, dtype, 128, s.N, s.Hq, a.q_sn, a.q_sh, s.TPT, s.G)) return cudaErrorInvalidValue;
+    if (make_tile_map_3d_box(&domap, a.d_o, dtype, 128, s.N, s.Hq, a.do_sn, a.do_sh, s.TPT, s.G)) return cudaErrorInvalidValue;
+    if (make_tile_map_3d_box(&dqmap, a.dq, dtype, 128, s.N, s.Hq, (int64_t)s.Hq * 128, 128, s.TPT, s.G)) return cudaErrorInvalidValue;
+    RangeDqParams p;
+    p.cu_q = a.cu; p.cu_k = a.bd.cu_k ? a.bd.cu_k : a.cu; p.kv_lo = a.bd.kv_lo; p.kv_hi = a.bd.kv_hi;
+    p.N = s.N; p.Nk = s.Nk; p.B = s.B; p.Hq = s.Hq; p.Hk = s.Hk; p.G = s.G; p.TPT = s.TPT;
+    p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+    p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.status = status;
+    constexpr int smem = 2 * kTileRows * 128 * 2 + 2 * kRdBK * 128 * 2 + kTileRows * kRdBK * 2 + 256;
+    const int max_tiles = (int)((s.N + s.TPT - 1) / s.TPT) + s.B;
+    cudaError_t e;
+    if (dtype == kBF16) {
+        auto kern = range_bwd_dq_dense<__nv_bfloat16>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        prof_begin(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
+        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kRdThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
+        prof_end(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
+    } else {
+        auto kern = range_bwd_dq_dense<__half>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        prof_begin(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
+        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kRdThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
+        prof_end(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
+    }
+    return cudaGetLastError();
+}
+
 }  // namespace fsa
 
 using namespace fsa;

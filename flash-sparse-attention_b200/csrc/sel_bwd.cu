@@ -533,8 +533,15 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
     p.s = s; p.ix = ix; p.nsub = nsub; p.bd = a.bd;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.dq_part = (ET*)a.dq_part; p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
+    // range attention (every token sees one contiguous range): dQ by the query-tile-major kernel, no partial dQ rows
+    const bool dq_dense = pipelined && a.bd.kv_hi != nullptr && s.G <= 32;
     if (pipelined) {
-        e = launch_sel_bwd_pipe(ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16, a, s, ix, kmap, vmap, *a.dqmap, num_sms, stream);
+        const int dt = ElemTraits<ET>::kIsBF16 ? (int)kBF16 : (int)kFP16;
+        if (dq_dense && rows > 0) {
+            e = launch_range_bwd_dq(dt, a, s, kmap, vmap, ix.header, stream);
+            if (e != cudaSuccess) return e;
+        }
+        e = launch_sel_bwd_pipe(dt, a, s, ix, kmap, vmap, *a.dqmap, num_sms, dq_dense, stream);
         if (e != cudaSuccess) return e;
     } else {
         auto kern = sel_bwd_main<D, ET>;
@@ -551,7 +558,7 @@ static cudaError_t launch_sel_bwd(const SelBwdArgs& a, const SelShape& s, const 
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    if (rows > 0) {
+    if (rows > 0 && !dq_dense) {
         unsigned grid = (unsigned)((rows + 7) / 8);
         prof_begin(3, stream);
         sel_bwd_dq_reduce<D, ET><<<grid, 256, 0, stream>>>((const ET*)a.dq_part, ix.pos, s, nsub, (ET*)a.dq);

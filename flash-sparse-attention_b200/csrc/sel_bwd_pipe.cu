@@ -38,6 +38,7 @@ struct SelBwdPipeParams {
     SelBounds bd;      // visible K/V rows per token
     ET* dq_part;       // [max_tiles * 128, D] (written through dqmap)
     float* slabs;      // [segments][2 (dK, dV)][64 keys][D] fp32: the partial sums of every segment of tiles
+    int no_dq;         // 1: dQ is computed elsewhere (range attention: the query-tile-major dQ kernel); only dK / dV here
 };
 
 namespace bwdpipe {
@@ -232,6 +233,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             const int j = sched.tile(k);
             // ---- dQ partial of this tile
             BT_TOC(0);
+            if (!p.no_dq) {
             ok = mbar_wait(dq_full, k & 1, status) && ok;
             BT_EV(k, 13, warp == kWFlush && lane == 0);
             BT_TOC(1);
@@ -264,6 +266,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
                 for (int b = 0; b < D / 64; ++b)
                     tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
                 bulk_commit();
+            }
             }
             BT_TOC(2);
             if (!last_of_seg) continue;
@@ -409,16 +412,20 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             }
             __syncwarp();
             BT_EV(k, 10, lane == 0);
-            ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
-            BT_EV(k, 11, lane == 0);
-            tc_fence_after();
+            if (!p.no_dq) {
+                ok = mbar_wait(dq_empty, (k & 1) ^ 1, status) && ok;
+                BT_EV(k, 11, lane == 0);
+                tc_fence_after();
+            }
             if (leader) {
+                if (!p.no_dq) {
 #pragma unroll
-                for (int ks = 0; ks < KT / 16; ++ks)
-                    umma_ss(tbase + cDQ, umma_desc_pack(ds_k_lo + ks * 2, hi_1024), umma_desc_pack(bk + ks * (2048 >> 4), hi_1024),
-                            idesc_dq, ks > 0);
+                    for (int ks = 0; ks < KT / 16; ++ks)
+                        umma_ss(tbase + cDQ, umma_desc_pack(ds_k_lo + ks * 2, hi_1024), umma_desc_pack(bk + ks * (2048 >> 4), hi_1024),
+                                idesc_dq, ks > 0);
+                }
                 umma_commit(pds_empty);
-                umma_commit(dq_full);
+                if (!p.no_dq) umma_commit(dq_full);
                 if (last_of_block) umma_commit(&kv_empty[kvn % kKVStages]);
             }
             __syncwarp();
@@ -611,7 +618,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
 
 template <typename ET>
 static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const SelIndex& ix, const CUtensorMap& kmap,
-                               const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms, cudaStream_t stream) {
+                               const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms, bool no_dq, cudaStream_t stream) {
     SelBwdPipeParams<ET> p;
     p.q = (const ET*)a.q; p.q_sn = a.q_sn; p.q_sh = a.q_sh;
     p.d_o = (const ET*)a.d_o; p.do_sn = a.do_sn; p.do_sh = a.do_sh;
@@ -621,6 +628,7 @@ static cudaError_t launch_pipe(const SelBwdArgs& a, const SelShape& s, const Sel
     p.run = s.RB;                      // (long runs: few segments per block)
     p.bd = a.bd;
     p.dq_part = (ET*)a.dq_part; p.slabs = a.slabs;
+    p.no_dq = no_dq ? 1 : 0;
     auto kern = sel_bwd_pipe<ET>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwdpipe::kBytes);
     if (e != cudaSuccess) return e;
@@ -643,9 +651,9 @@ namespace fsa {
 
 cudaError_t launch_sel_bwd_pipe(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
                                 const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms,
-                                cudaStream_t stream) {
-    return dtype == kBF16 ? launch_pipe<__nv_bfloat16>(a, s, ix, kmap, vmap, dqmap, num_sms, stream)
-                          : launch_pipe<__half>(a, s, ix, kmap, vmap, dqmap, num_sms, stream);
+                                bool no_dq, cudaStream_t stream) {
+    return dtype == kBF16 ? launch_pipe<__nv_bfloat16>(a, s, ix, kmap, vmap, dqmap, num_sms, no_dq, stream)
+                          : launch_pipe<__half>(a, s, ix, kmap, vmap, dqmap, num_sms, no_dq, stream);
 }
 
 }  // namespace fsa

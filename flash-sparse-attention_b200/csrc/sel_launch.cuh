@@ -63,7 +63,12 @@ struct SelBwdArgs {
 // pipelined main kernel for head_dim 128, block size <= 64 (sel_bwd_pipe.cu)
 cudaError_t launch_sel_bwd_pipe(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
                                 const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& dqmap, int num_sms,
-                                cudaStream_t stream);
+                                bool no_dq, cudaStream_t stream);
+
+// dQ of a range-attention backward as one query-tile-major kernel (range_dense.cu; head_dim 128): the accumulator stays
+// in TMEM across the K/V tiles a tile of tokens sees, so the block-major kernel above runs with no_dq
+cudaError_t launch_range_bwd_dq(int dtype, const SelBwdArgs& a, const SelShape& s, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                                int* status, cudaStream_t stream);
 
 cudaError_t dispatch_sel_bwd(int dtype, const SelBwdArgs& a, const SelShape& s, const SelIndex& ix,
                              const CUtensorMap& kmap, const CUtensorMap& vmap, int num_sms, cudaStream_t stream);

@@ -120,7 +120,9 @@ def linear_compress(
     bias = None
     if pe is not None:
         assert pe.dtype == x.dtype and pe.device == x.device
-        bias = torch.einsum("hD,hDd->hd", pe.reshape(H, kernel_size * d), w)
+        # bias[h, :] = sum_D pe[h, D] w[h, D, :] as a broadcast product and a column sum (fp32, rounded once): the batched
+        # GEMM with one row that einsum would launch, and the rank-1 GEMMs of its backward, are far slower than this
+        bias = (pe.reshape(H, kernel_size * d, 1).float() * w.float()).sum(1).to(x.dtype)
     if d in (64, 128):
         y = _LinearCompress.apply(x, w, bias, cu_seqlens, seqlens, ylens, kernel_size, kernel_stride)
     else:
