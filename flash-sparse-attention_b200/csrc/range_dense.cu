@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_fwd_dense(const RangeDens
 #pragma unroll
                     for (int b = 0; b < KH; ++b) tma_store_3d(&omap, b * 64, tok0, h * p.G, smem_u32(sQ + b * (kTileRows * 128)));
                     bulk_commit();
-                    bulk_wait0();
+                    bulk_wait_read0();     // the staging memory has been read; the global writes complete on their own
                 }
             }
         }
@@ -378,8 +378,13 @@ static cudaError_t launch_rd(const RangeDenseParams& p, const CUtensorMap& qmap,
 // P = exp2(S c - lse), dS = scale P (dP - delta) to swizzled shared memory, dQ (+)= dS K accumulated in TMEM over the
 // tiles and written once.  (In the reference: the dQ part of _backward_kernel, nsa_ref/ops/compressed_attention.py:
 // 193-760, and of flash-attn's backward for the sliding window.)  With it the block-major backward kernel computes
-// only dK and dV and no partial dQ row is written or merged.  Two CTAs per SM (112 KB of shared memory, 256 TMEM columns
-// each), every buffer single: one CTA's dependent chain is covered by the other.
+// only dK and dV and no partial dQ row is written or merged.  One CTA per SM, 320 threads:
+//   warp 0      TMA producer: Q and dO tiles once, (K, V) tiles through a three-stage ring;
+//   warp 1      one elected thread issues S(j+1), dP(j+1) (two TMEM buffers) before dQ(j), so that the row threads of
+//               tile j and the products of tile j + 1 overlap;
+//   warps 2..9  two groups of 128 row threads, each on 32 of the 64 key columns: dS to one of two shared-memory buffers;
+//               epilogue: each group rounds 64 of the dQ columns, stages them (the Q tile's memory) and stores its slab by
+//               3-D TMA (plain stores for the last, partial tile of a sequence).
 struct RangeDqParams {
     const int32_t* cu_q;
     const int32_t* cu_k;
@@ -394,8 +399,11 @@ struct RangeDqParams {
     int* status;
 };
 
+constexpr int kDqThreads = 320;
+constexpr int kDqStages = 3;
+
 template <typename ET>
-__global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeDqParams p, const __grid_constant__ CUtensorMap qmap,
+__global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeDqParams p, const __grid_constant__ CUtensorMap qmap,
                                                                    const __grid_constant__ CUtensorMap domap,
                                                                    const __grid_constant__ CUtensorMap kmap,
                                                                    const __grid_constant__ CUtensorMap vmap,
@@ -404,34 +412,34 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeD
     constexpr int kQ = kTileRows * D * 2;            // Q tile (later the dQ staging), same for dO
     constexpr int kKt = BK * D * 2;
     constexpr int kDS = kTileRows * BK * 2;
-    constexpr uint32_t kCols = 256;
-    constexpr int cS = 0, cDP = BK, cDQ = 2 * BK;
+    constexpr uint32_t kCols = 512;
+    constexpr int cDQ = 256;                         // S(b) at 128 b, dP(b) at 128 b + 64
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sDO = sQ + kQ;
-    uint8_t* sK = sDO + kQ;
-    uint8_t* sV = sK + kKt;
-    uint8_t* sDS = sV + kKt;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kDS);
+    uint8_t* sKV = sDO + kQ;                         // stage: K then V
+    uint8_t* sDS = sKV + kDqStages * 2 * kKt;        // two buffers
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * kDS);
     uint64_t* qd_full = bars;           // Q and dO tiles have landed
-    uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = bars + 2;       // the dQ product of the tile is done (K read, dS read)
-    uint64_t* v_full = bars + 3;
-    uint64_t* v_empty = bars + 4;       // S and dP of the tile are done (V read)
-    uint64_t* sdp_full = bars + 5;
-    uint64_t* sdp_free = bars + 6;      // the 128 row threads have read S and dP
-    uint64_t* ds_full = bars + 7;       // ... have written dS
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 8);
-    int* s_meta = reinterpret_cast<int*>(bars + 9);
+    uint64_t* kv_full = bars + 1;       // [3]
+    uint64_t* kv_empty = bars + 4;      // [3] the dQ product of the tile is done
+    uint64_t* sdp_full = bars + 7;      // [2]
+    uint64_t* sdp_free = bars + 9;      // [2] the 256 row threads have read S and dP
+    uint64_t* ds_full = bars + 11;      // [2] ... have written dS
+    uint64_t* ds_empty = bars + 13;     // [2] the dQ product has read dS
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 15);
+    int* s_meta = reinterpret_cast<int*>(bars + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int* status = p.status;
     const int h = blockIdx.y;
     if (tid == 0) {
         mbar_init(qd_full, 1);
-        mbar_init(k_full, 1); mbar_init(k_empty, 1);
-        mbar_init(v_full, 1); mbar_init(v_empty, 1);
-        mbar_init(sdp_full, 1); mbar_init(sdp_free, 128); mbar_init(ds_full, 128);
+        for (int i = 0; i < kDqStages; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 256);
+            mbar_init(&ds_full[i], 256); mbar_init(&ds_empty[i], 1);
+        }
         mbar_init_fence();
         tma_prefetch_desc(&qmap);
         tma_prefetch_desc(&domap);
@@ -500,16 +508,16 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeD
             }
             for (int j = 0; j < nblk && ok; ++j) {
                 if (lane == 0) {
-                    ok = mbar_wait(k_empty, (j & 1) ^ 1, status) && ok;
-                    mbar_expect_tx(k_full, (uint32_t)kKt);
+                    const int st = j % kDqStages;
+                    ok = mbar_wait(&kv_empty[st], ((j / kDqStages) & 1) ^ 1, status) && ok;
+                    mbar_expect_tx(&kv_full[st], (uint32_t)(2 * kKt));
+                    uint8_t* dK = sKV + st * 2 * kKt;
+                    uint8_t* dV = dK + kKt;
 #pragma unroll
-                    for (int b = 0; b < KH; ++b)
-                        tma_load_2d(smem_u32(sK + b * (BK * 128)), &kmap, h * D + b * 64, row_lo + j * BK, k_full);
-                    ok = mbar_wait(v_empty, (j & 1) ^ 1, status) && ok;
-                    mbar_expect_tx(v_full, (uint32_t)kKt);
-#pragma unroll
-                    for (int b = 0; b < KH; ++b)
-                        tma_load_2d(smem_u32(sV + b * (BK * 128)), &vmap, h * D + b * 64, row_lo + j * BK, v_full);
+                    for (int b = 0; b < KH; ++b) {
+                        tma_load_2d(smem_u32(dK + b * (BK * 128)), &kmap, h * D + b * 64, row_lo + j * BK, &kv_full[st]);
+                        tma_load_2d(smem_u32(dV + b * (BK * 128)), &vmap, h * D + b * 64, row_lo + j * BK, &kv_full[st]);
+                    }
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
@@ -521,49 +529,63 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeD
             constexpr uint32_t hi_1024 = umma_desc_hi(1024);
             constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (BK * 128) >> 4;
             const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16), do_lo = umma_desc_lo(smem_u32(sDO), 16);
-            const uint32_t k_lo = umma_desc_lo(smem_u32(sK), 16), v_lo = umma_desc_lo(smem_u32(sV), 16);
+            const uint32_t kv_lo_ = umma_desc_lo(smem_u32(sKV), 16);
             const uint32_t ds_lo = umma_desc_lo(smem_u32(sDS), 16);
-            const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sK), BK * 128);
+            const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sKV), BK * 128);
             bool ok = true;
-            if (nblk > 0) ok = mbar_wait(qd_full, 0, status) && ok;
-            for (int j = 0; j < nblk && ok; ++j) {
-                ok = mbar_wait(k_full, j & 1, status) && ok;
-                ok = mbar_wait(v_full, j & 1, status) && ok;
-                ok = mbar_wait(sdp_free, (j & 1) ^ 1, status) && ok;       // S / dP of the previous tile have been read
+            auto issue_sdp = [&](int j) {
+                const int b = j & 1, st = j % kDqStages;
+                ok = mbar_wait(&kv_full[st], (j / kDqStages) & 1, status) && ok;
+                ok = mbar_wait(&sdp_free[b], ((j >> 1) & 1) ^ 1, status) && ok;     // S / dP of tile j - 2 have been read
                 tc_fence_after();
                 if (leader) {
+                    const uint32_t k_lo = kv_lo_ + (uint32_t)(st * ((2 * kKt) >> 4));
+                    const uint32_t v_lo = k_lo + (uint32_t)(kKt >> 4);
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks)
-                        umma_ss(tbase + cS, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                        umma_ss(tbase + b * 128, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
                                 umma_desc_pack(k_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks)
-                        umma_ss(tbase + cDP, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                        umma_ss(tbase + b * 128 + BK, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
                                 umma_desc_pack(v_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
-                    umma_commit(v_empty);
-                    umma_commit(sdp_full);
+                    umma_commit(&sdp_full[b]);
                 }
                 __syncwarp();
-                ok = mbar_wait(ds_full, j & 1, status) && ok;
+            };
+            if (nblk > 0) {
+                ok = mbar_wait(qd_full, 0, status) && ok;
+                issue_sdp(0);
+            }
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int b = j & 1, st = j % kDqStages;
+                if (j + 1 < nblk) issue_sdp(j + 1);
+                ok = mbar_wait(&ds_full[b], (j >> 1) & 1, status) && ok;
                 fence_async_smem();
                 tc_fence_after();
                 if (leader) {
+                    const uint32_t a_lo = ds_lo + (uint32_t)(b * (kDS >> 4));
+                    const uint32_t b_lo = k_mn_lo + (uint32_t)(st * ((2 * kKt) >> 4));
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks)
-                        umma_ss(tbase + cDQ, umma_desc_pack(ds_lo + ks * 2, hi_1024), umma_desc_pack(k_mn_lo + ks * (2048 >> 4), hi_1024),
+                        umma_ss(tbase + cDQ, umma_desc_pack(a_lo + ks * 2, hi_1024), umma_desc_pack(b_lo + ks * (2048 >> 4), hi_1024),
                                 idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(k_empty);
+                    umma_commit(&kv_empty[st]);
+                    umma_commit(&ds_empty[b]);
                 }
                 __syncwarp();
             }
         } else {
-            // ------------------------------------------------------------------ P / dS and the epilogue: one row per thread
+            // ------------------------------------------------------------------ dS and the epilogue: one row, half the columns
+            const int sb = (warp - 2) >> 2;               // column half of this group
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane;
             const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
             const int g = r / p.TPT, e = r - g * p.TPT;
             const bool row_valid = g < p.G && e < ne;
             const int tok = tok0 + e;
+            constexpr int HC = BK / 2;
+            const int cb = sb * HC;
             int lo_r = 0, hi_r = -1;
             float lse_r = 0.f, delta_s = 0.f;
             if (row_valid) {
@@ -576,59 +598,61 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeD
             }
             bool ok = true;
             for (int j = 0; j < nblk && ok; ++j) {
+                const int b = j & 1;
                 const int R0 = row_lo + j * BK;
                 const int c_lo = max(0, lo_r - R0), c_hi = min(BK, hi_r - R0 + 1);
-                ok = mbar_wait(sdp_full, j & 1, status) && ok;
+                ok = mbar_wait(&sdp_full[b], (j >> 1) & 1, status) && ok;
                 tc_fence_after();
-                uint32_t dd[BK / 2];
+                uint32_t dd[HC / 2];
                 const bool all_visible = __all_sync(0xffffffffu, c_lo == 0 && c_hi == BK);
-#pragma unroll
-                for (int c0 = 0; c0 < BK; c0 += 32) {
+                {
                     uint32_t sv[32], dv[32];
-                    tmem_ld32(tbase + lane_off + cS + c0, sv);
-                    tmem_ld32(tbase + lane_off + cDP + c0, dv);
+                    tmem_ld32(tbase + lane_off + b * 128 + cb, sv);
+                    tmem_ld32(tbase + lane_off + b * 128 + BK + cb, dv);
                     tmem_ld_wait();
                     if (all_visible) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             const float p0 = rd_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r));
                             const float p1 = rd_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r));
-                            dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s),
-                                                                      p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s));
+                            dd[i >> 1] = ElemTraits<ET>::pack2(p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s),
+                                                               p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s));
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
-                            const float p0 = (c0 + i >= c_lo && c0 + i < c_hi) ? rd_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
-                            const float p1 = (c0 + i + 1 >= c_lo && c0 + i + 1 < c_hi) ? rd_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
+                            const float p0 = (cb + i >= c_lo && cb + i < c_hi) ? rd_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_r)) : 0.f;
+                            const float p1 = (cb + i + 1 >= c_lo && cb + i + 1 < c_hi) ? rd_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse_r)) : 0.f;
                             const float d0 = p0 > 0.f ? p0 * fmaf(__uint_as_float(dv[i]), p.scale, -delta_s) : 0.f;
                             const float d1 = p1 > 0.f ? p1 * fmaf(__uint_as_float(dv[i + 1]), p.scale, -delta_s) : 0.f;
-                            dd[(c0 + i) >> 1] = ElemTraits<ET>::pack2(d0, d1);
+                            dd[i >> 1] = ElemTraits<ET>::pack2(d0, d1);
                         }
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(sdp_free);
-                // the dQ product of the previous tile has read dS: k_empty completes with it
-                if (j > 0) ok = mbar_wait(k_empty, (j - 1) & 1, status) && ok;
+                mbar_arrive(&sdp_free[b]);
+                ok = mbar_wait(&ds_empty[b], ((j >> 1) & 1) ^ 1, status) && ok;      // the dQ product of tile j - 2 has read this buffer
+                uint8_t* ds = sDS + b * kDS;
 #pragma unroll
-                for (int ch = 0; ch < BK / 8; ++ch)
-                    *reinterpret_cast<uint4*>(sDS + sw128_chunk_off(r, ch)) = make_uint4(dd[ch * 4], dd[ch * 4 + 1], dd[ch * 4 + 2], dd[ch * 4 + 3]);
+                for (int c4 = 0; c4 < HC / 8; ++c4)
+                    *reinterpret_cast<uint4*>(ds + sw128_chunk_off(r, sb * (HC / 8) + c4)) =
+                        make_uint4(dd[c4 * 4], dd[c4 * 4 + 1], dd[c4 * 4 + 2], dd[c4 * 4 + 3]);
                 fence_async_smem();
-                mbar_arrive(ds_full);
+                mbar_arrive(&ds_full[b]);
             }
-            // ---- epilogue
+            // ---- epilogue: this group's 64 of the 128 dQ columns
             if (nblk > 0) {
-                ok = mbar_wait(k_empty, (nblk - 1) & 1, status) && ok;
+                ok = mbar_wait(&ds_empty[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, status) && ok;
                 tc_fence_after();
             }
             const bool full_tile = ne == p.TPT && p.G * p.TPT == kTileRows;
-            ET* drow = reinterpret_cast<ET*>(p.dq) + ((int64_t)tok * p.Hq + (h * p.G + g)) * D;
+            ET* drow = reinterpret_cast<ET*>(p.dq) + ((int64_t)tok * p.Hq + (h * p.G + g)) * D + sb * 64;
+            uint8_t* stage = sQ + sb * (kTileRows * 128);
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t a[32];
                 if (nblk > 0) {
-                    tmem_ld32(tbase + lane_off + cDQ + c0, a);
+                    tmem_ld32(tbase + lane_off + cDQ + sb * 64 + c0, a);
                     tmem_ld_wait();
                 } else {
 #pragma unroll
@@ -641,9 +665,9 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeD
                     x.y = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 2]), __uint_as_float(a[q4 * 8 + 3]));
                     x.z = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 4]), __uint_as_float(a[q4 * 8 + 5]));
                     x.w = ElemTraits<ET>::pack2(__uint_as_float(a[q4 * 8 + 6]), __uint_as_float(a[q4 * 8 + 7]));
-                    const int chunk = (c0 >> 3) + q4;
+                    const int chunk = (c0 >> 3) + q4;       // 16-byte chunk inside this group's 128-byte half row
                     if (full_tile) {
-                        *reinterpret_cast<uint4*>(sQ + (chunk >> 3) * (kTileRows * 128) + sw128_chunk_off(r, chunk & 7)) = x;
+                        *reinterpret_cast<uint4*>(stage + sw128_chunk_off(r, chunk)) = x;
                     } else if (row_valid && ok) {
                         *reinterpret_cast<uint4*>(drow + chunk * 8) = x;
                     }
@@ -651,12 +675,12 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_bwd_dq_dense(const RangeD
             }
             if (full_tile) {
                 fence_async_smem();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (warp == 2 && lane == 0 && ok) {
-#pragma unroll
-                    for (int b = 0; b < KH; ++b) tma_store_3d(&dqmap, b * 64, tok0, h * p.G, smem_u32(sQ + b * (kTileRows * 128)));
+                if (sb == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                else asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (quarter == 0 && lane == 0 && ok) {
+                    tma_store_3d(&dqmap, sb * 64, tok0, h * p.G, smem_u32(stage));
                     bulk_commit();
-                    bulk_wait0();
+                    bulk_wait_read0();     // the staging memory has been read; the global writes complete on their own
                 }
             }
         }
@@ -678,7 +702,7 @@ cudaError_t launch_range_bwd_dq(int dtype, const SelBwdArgs& a, const SelShape& 
     p.N = s.N; p.Nk = s.Nk; p.B = s.B; p.Hq = s.Hq; p.Hk = s.Hk; p.G = s.G; p.TPT = s.TPT;
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.status = status;
-    constexpr int smem = 2 * kTileRows * 128 * 2 + 2 * kRdBK * 128 * 2 + kTileRows * kRdBK * 2 + 256;
+    constexpr int smem = 2 * kTileRows * 128 * 2 + kDqStages * 2 * kRdBK * 128 * 2 + 2 * kTileRows * kRdBK * 2 + 256;
     const int max_tiles = (int)((s.N + s.TPT - 1) / s.TPT) + s.B;
     cudaError_t e;
     if (dtype == kBF16) {
@@ -686,14 +710,14 @@ cudaError_t launch_range_bwd_dq(int dtype, const SelBwdArgs& a, const SelShape& 
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         prof_begin(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
-        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kRdThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
+        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kDqThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
         prof_end(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
     } else {
         auto kern = range_bwd_dq_dense<__half>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         prof_begin(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
-        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kRdThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
+        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kDqThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
         prof_end(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
     }
     return cudaGetLastError();
