@@ -27,6 +27,7 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, i
 int make_tile_map_3d_box(CUtensorMap* map, const void* base, int dtype, int64_t d0, int64_t d1, int64_t d2, int64_t stride1,
                          int64_t stride2, int box1, int box2);
 int ensure_context();
+int device_sm_count(int* out);
 
 struct RangeDenseParams {
     const int32_t* cu_q;    // [B + 1]
@@ -379,7 +380,8 @@ static cudaError_t launch_rd(const RangeDenseParams& p, const CUtensorMap& qmap,
 // tiles and written once.  (In the reference: the dQ part of _backward_kernel, nsa_ref/ops/compressed_attention.py:
 // 193-760, and of flash-attn's backward for the sliding window.)  With it the block-major backward kernel computes
 // only dK and dV and no partial dQ row is written or merged.  One CTA per SM, 320 threads:
-//   warp 0      TMA producer: Q and dO tiles once, (K, V) tiles through a three-stage ring;
+//   warp 0      TMA producer: Q and dO tiles of every item, (K, V) tiles through a four-stage ring (a stage comes free only
+//               when the tile's dQ product is done, and the next load needs a microsecond to land);
 //   warp 1      one elected thread issues S(j+1), dP(j+1) (two TMEM buffers) before dQ(j), so that the row threads of
 //               tile j and the products of tile j + 1 overlap;
 //   warps 2..9  two groups of 128 row threads, each on 32 of the 64 key columns: dS to one of two shared-memory buffers;
@@ -400,7 +402,50 @@ struct RangeDqParams {
 };
 
 constexpr int kDqThreads = 320;
-constexpr int kDqStages = 3;
+constexpr int kDqStages = 4;
+
+// One work item of the dQ kernel: a tile of tokens x one KV head.
+struct DqItem {
+    int seq, tok0, ne, row_lo, nblk, h;
+};
+
+// Work item w of the list (heaviest tiles first).  Warp-collective: all 32 lanes call it and get the same answer.
+__device__ __forceinline__ DqItem dq_item(const RangeDqParams& p, int ntiles, int w, int lane) {
+    DqItem m;
+    m.h = w % p.Hk;
+    const int want = ntiles - 1 - w / p.Hk;
+    m.seq = -1; m.tok0 = 0; m.ne = 0; m.row_lo = 0; m.nblk = 0;
+    int acc = 0;
+    for (int b = 0; b < p.B; ++b) {
+        const int s0 = __ldg(p.cu_q + b), L = __ldg(p.cu_q + b + 1) - s0;
+        const int nt = (L + p.TPT - 1) / p.TPT;
+        if (want < acc + nt) {
+            m.seq = b;
+            m.tok0 = s0 + (want - acc) * p.TPT;
+            m.ne = min(p.TPT, s0 + L - m.tok0);
+            break;
+        }
+        acc += nt;
+    }
+    if (m.seq < 0) return m;
+    int lo = INT_MAX, hi = -1;
+    const int k0 = __ldg(p.cu_k + m.seq);
+    for (int e = lane; e < m.ne; e += 32) {
+        const int l = p.kv_lo ? __ldg(p.kv_lo + m.tok0 + e) : k0;
+        const int u = __ldg(p.kv_hi + m.tok0 + e);
+        if (u >= l) { lo = min(lo, l); hi = max(hi, u); }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+    }
+    lo = max(lo, 0);
+    hi = min(hi, (int)p.Nk - 1);
+    m.row_lo = lo;
+    m.nblk = hi >= lo ? (hi - lo) / kRdBK + 1 : 0;
+    return m;
+}
 
 template <typename ET>
 __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeDqParams p, const __grid_constant__ CUtensorMap qmap,
@@ -409,9 +454,9 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
                                                                    const __grid_constant__ CUtensorMap vmap,
                                                                    const __grid_constant__ CUtensorMap dqmap) {
     constexpr int D = 128, BK = kRdBK, KH = D / 64;
-    constexpr int kQ = kTileRows * D * 2;            // Q tile (later the dQ staging), same for dO
+    constexpr int kQ = kTileRows * D * 2;            // Q tile, same for dO
     constexpr int kKt = BK * D * 2;
-    constexpr int kDS = kTileRows * BK * 2;
+    constexpr int kDS = kTileRows * BK * 2;          // one dS buffer; the two together stage a dQ tile in the epilogue
     constexpr uint32_t kCols = 512;
     constexpr int cDQ = 256;                         // S(b) at 128 b, dP(b) at 128 b + 64
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -420,26 +465,27 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
     uint8_t* sKV = sDO + kQ;                         // stage: K then V
     uint8_t* sDS = sKV + kDqStages * 2 * kKt;        // two buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * kDS);
-    uint64_t* qd_full = bars;           // Q and dO tiles have landed
-    uint64_t* kv_full = bars + 1;       // [3]
-    uint64_t* kv_empty = bars + 4;      // [3] the dQ product of the tile is done
-    uint64_t* sdp_full = bars + 7;      // [2]
-    uint64_t* sdp_free = bars + 9;      // [2] the 256 row threads have read S and dP
-    uint64_t* ds_full = bars + 11;      // [2] ... have written dS
-    uint64_t* ds_empty = bars + 13;     // [2] the dQ product has read dS
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 15);
-    int* s_meta = reinterpret_cast<int*>(bars + 16);
+    uint64_t* qd_full = bars;           // Q and dO tiles of an item have landed
+    uint64_t* qd_empty = bars + 1;      // ... have been read by the item's last S / dP products
+    uint64_t* kv_full = bars + 2;                        // [stages]
+    uint64_t* kv_empty = kv_full + kDqStages;            // [stages] the dQ product of the tile is done
+    uint64_t* sdp_full = kv_empty + kDqStages;           // [2]
+    uint64_t* sdp_free = sdp_full + 2;                   // [2] the 256 row threads have read S and dP
+    uint64_t* ds_full = sdp_free + 2;                    // [2] ... have written dS
+    uint64_t* ds_empty = ds_full + 2;                    // [2] the dQ product has read dS
+    uint64_t* dq_free = ds_empty + 2;                    // the 256 row threads have read an item's dQ accumulator
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(dq_free + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int* status = p.status;
-    const int h = blockIdx.y;
     if (tid == 0) {
-        mbar_init(qd_full, 1);
+        mbar_init(qd_full, 1); mbar_init(qd_empty, 1);
         for (int i = 0; i < kDqStages; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 256);
             mbar_init(&ds_full[i], 256); mbar_init(&ds_empty[i], 1);
         }
+        mbar_init(dq_free, 256);
         mbar_init_fence();
         tma_prefetch_desc(&qmap);
         tma_prefetch_desc(&domap);
@@ -447,120 +493,110 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
         tma_prefetch_desc(&vmap);
         tma_prefetch_desc(&dqmap);
     }
-    if (warp == 0) {
-        int total = 0;
-        for (int b = 0; b < p.B; ++b) total += (__ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b) + p.TPT - 1) / p.TPT;
-        const int want = total - 1 - (int)blockIdx.x;
-        int seq = -1, tok0 = 0, ne = 0;
-        if (want >= 0) {
-            int acc = 0;
-            for (int b = 0; b < p.B; ++b) {
-                const int s0 = __ldg(p.cu_q + b), L = __ldg(p.cu_q + b + 1) - s0;
-                const int nt = (L + p.TPT - 1) / p.TPT;
-                if (want < acc + nt) {
-                    seq = b;
-                    tok0 = s0 + (want - acc) * p.TPT;
-                    ne = min(p.TPT, s0 + L - tok0);
-                    break;
-                }
-                acc += nt;
-            }
-        }
-        int lo = INT_MAX, hi = -1;
-        if (seq >= 0) {
-            const int k0 = __ldg(p.cu_k + seq);
-            for (int e = lane; e < ne; e += 32) {
-                const int l = p.kv_lo ? __ldg(p.kv_lo + tok0 + e) : k0;
-                const int u = __ldg(p.kv_hi + tok0 + e);
-                if (u >= l) { lo = min(lo, l); hi = max(hi, u); }
-            }
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
-            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
-        }
-        if (lane == 0) {
-            lo = max(lo, 0);
-            hi = min(hi, (int)p.Nk - 1);
-            s_meta[0] = seq; s_meta[1] = tok0; s_meta[2] = ne; s_meta[3] = lo;
-            s_meta[4] = hi >= lo ? (hi - lo) / BK + 1 : 0;
-        }
-        tmem_alloc(&tmem_slot, kCols);
-    }
+    if (warp == 0) tmem_alloc(&tmem_slot, kCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = tmem_slot;
-    const int seq = s_meta[0], tok0 = s_meta[1], ne = s_meta[2], row_lo = s_meta[3], nblk = s_meta[4];
+    int ntiles = 0;
+    for (int b = 0; b < p.B; ++b) ntiles += (__ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b) + p.TPT - 1) / p.TPT;
+    const int nitems = ntiles * p.Hk;
 
-    if (seq >= 0) {
-        if (warp == 0) {
-            // ------------------------------------------------------------------ TMA producer
-            bool ok = true;
-            if (lane == 0 && nblk > 0) {
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        bool ok = true;
+        int kvc = 0, qi = 0;           // K/V tiles and non-empty items so far
+        for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+            const DqItem m = dq_item(p, ntiles, w, lane);
+            if (m.nblk == 0) continue;
+            if (lane == 0) {
+                ok = mbar_wait(qd_empty, (qi & 1) ^ 1, status) && ok;
                 mbar_expect_tx(qd_full, (uint32_t)(2 * KH * 128 * p.TPT * p.G));
 #pragma unroll
                 for (int b = 0; b < KH; ++b) {
-                    tma_load_3d(smem_u32(sQ + b * (kTileRows * 128)), &qmap, b * 64, tok0, h * p.G, qd_full);
-                    tma_load_3d(smem_u32(sDO + b * (kTileRows * 128)), &domap, b * 64, tok0, h * p.G, qd_full);
+                    tma_load_3d(smem_u32(sQ + b * (kTileRows * 128)), &qmap, b * 64, m.tok0, m.h * p.G, qd_full);
+                    tma_load_3d(smem_u32(sDO + b * (kTileRows * 128)), &domap, b * 64, m.tok0, m.h * p.G, qd_full);
                 }
             }
-            for (int j = 0; j < nblk && ok; ++j) {
+            ++qi;
+            for (int j = 0; j < m.nblk && ok; ++j, ++kvc) {
                 if (lane == 0) {
-                    const int st = j % kDqStages;
-                    ok = mbar_wait(&kv_empty[st], ((j / kDqStages) & 1) ^ 1, status) && ok;
+                    const int st = kvc % kDqStages;
+                    ok = mbar_wait(&kv_empty[st], ((kvc / kDqStages) & 1) ^ 1, status) && ok;
                     mbar_expect_tx(&kv_full[st], (uint32_t)(2 * kKt));
                     uint8_t* dK = sKV + st * 2 * kKt;
                     uint8_t* dV = dK + kKt;
 #pragma unroll
                     for (int b = 0; b < KH; ++b) {
-                        tma_load_2d(smem_u32(dK + b * (BK * 128)), &kmap, h * D + b * 64, row_lo + j * BK, &kv_full[st]);
-                        tma_load_2d(smem_u32(dV + b * (BK * 128)), &vmap, h * D + b * 64, row_lo + j * BK, &kv_full[st]);
+                        tma_load_2d(smem_u32(dK + b * (BK * 128)), &kmap, m.h * D + b * 64, m.row_lo + j * BK, &kv_full[st]);
+                        tma_load_2d(smem_u32(dV + b * (BK * 128)), &vmap, m.h * D + b * 64, m.row_lo + j * BK, &kv_full[st]);
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
-        } else if (warp == 1) {
-            // ------------------------------------------------------------------ MMA issuer
-            const bool leader = elect_one();
-            constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
-            constexpr uint32_t idesc_dq = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);     // dS (K-major) x K (MN-major)
-            constexpr uint32_t hi_1024 = umma_desc_hi(1024);
-            constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (BK * 128) >> 4;
-            const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16), do_lo = umma_desc_lo(smem_u32(sDO), 16);
-            const uint32_t kv_lo_ = umma_desc_lo(smem_u32(sKV), 16);
-            const uint32_t ds_lo = umma_desc_lo(smem_u32(sDS), 16);
-            const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sKV), BK * 128);
-            bool ok = true;
-            auto issue_sdp = [&](int j) {
-                const int b = j & 1, st = j % kDqStages;
-                ok = mbar_wait(&kv_full[st], (j / kDqStages) & 1, status) && ok;
-                ok = mbar_wait(&sdp_free[b], ((j >> 1) & 1) ^ 1, status) && ok;     // S / dP of tile j - 2 have been read
-                tc_fence_after();
-                if (leader) {
-                    const uint32_t k_lo = kv_lo_ + (uint32_t)(st * ((2 * kKt) >> 4));
-                    const uint32_t v_lo = k_lo + (uint32_t)(kKt >> 4);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        // The K/V tiles of all items form one sequence c = 0, 1, ...; S / dP of tile c + 1 are issued before dQ of tile c,
+        // also across the boundary between two items (then the next item's Q / dO must have landed, which the producer
+        // starts as soon as this item's last S / dP are done).
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
+        constexpr uint32_t idesc_dq = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);     // dS (K-major) x K (MN-major)
+        constexpr uint32_t hi_1024 = umma_desc_hi(1024);
+        constexpr int kSlabA = (kTileRows * 128) >> 4, kSlabB = (BK * 128) >> 4;
+        const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16), do_lo = umma_desc_lo(smem_u32(sDO), 16);
+        const uint32_t kv_lo_ = umma_desc_lo(smem_u32(sKV), 16);
+        const uint32_t ds_lo = umma_desc_lo(smem_u32(sDS), 16);
+        const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sKV), BK * 128);
+        bool ok = true;
+        auto issue_sdp = [&](int c) {
+            const int b = c & 1, st = c % kDqStages;
+            ok = mbar_wait(&kv_full[st], (c / kDqStages) & 1, status) && ok;
+            ok = mbar_wait(&sdp_free[b], ((c >> 1) & 1) ^ 1, status) && ok;     // S / dP of tile c - 2 have been read
+            tc_fence_after();
+            if (leader) {
+                const uint32_t k_lo = kv_lo_ + (uint32_t)(st * ((2 * kKt) >> 4));
+                const uint32_t v_lo = k_lo + (uint32_t)(kKt >> 4);
 #pragma unroll
-                    for (int ks = 0; ks < D / 16; ++ks)
-                        umma_ss(tbase + b * 128, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
-                                umma_desc_pack(k_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(tbase + b * 128, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                            umma_desc_pack(k_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
 #pragma unroll
-                    for (int ks = 0; ks < D / 16; ++ks)
-                        umma_ss(tbase + b * 128 + BK, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
-                                umma_desc_pack(v_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
-                    umma_commit(&sdp_full[b]);
-                }
-                __syncwarp();
-            };
-            if (nblk > 0) {
-                ok = mbar_wait(qd_full, 0, status) && ok;
-                issue_sdp(0);
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(tbase + b * 128 + BK, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                            umma_desc_pack(v_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                umma_commit(&sdp_full[b]);
             }
-            for (int j = 0; j < nblk && ok; ++j) {
-                const int b = j & 1, st = j % kDqStages;
-                if (j + 1 < nblk) issue_sdp(j + 1);
-                ok = mbar_wait(&ds_full[b], (j >> 1) & 1, status) && ok;
+            __syncwarp();
+        };
+        // next non-empty item at or after w
+        auto next_item = [&](int w, int& nb) {
+            nb = 0;
+            for (; w < nitems; w += gridDim.x) {
+                const DqItem m = dq_item(p, ntiles, w, lane);
+                if (m.nblk > 0) { nb = m.nblk; break; }
+            }
+            return w;
+        };
+        int nb = 0, nb_next = 0;
+        int w = next_item(blockIdx.x, nb);
+        int c = 0, qi = 0;
+        if (w < nitems) {
+            ok = mbar_wait(qd_full, 0, status) && ok;
+            issue_sdp(0);
+        }
+        while (w < nitems && ok) {
+            const int w_next = next_item(w + gridDim.x, nb_next);
+            for (int j = 0; j < nb && ok; ++j, ++c) {
+                const int b = c & 1, st = c % kDqStages;
+                const bool last = j + 1 == nb;
+                if (!last) issue_sdp(c + 1);
+                else if (leader) umma_commit(qd_empty);          // every S / dP of this item has been issued
+                __syncwarp();
+                ok = mbar_wait(&ds_full[b], (c >> 1) & 1, status) && ok;
+                if (j == 0 && qi > 0) ok = mbar_wait(dq_free, (qi - 1) & 1, status) && ok;     // the previous item's dQ has been read
                 fence_async_smem();
                 tc_fence_after();
                 if (leader) {
@@ -574,34 +610,45 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
                     umma_commit(&ds_empty[b]);
                 }
                 __syncwarp();
+                if (last && w_next < nitems) {
+                    // first S / dP of the next item, behind this item's last dQ
+                    ok = mbar_wait(qd_full, (qi + 1) & 1, status) && ok;
+                    issue_sdp(c + 1);
+                }
             }
-        } else {
-            // ------------------------------------------------------------------ dS and the epilogue: one row, half the columns
-            const int sb = (warp - 2) >> 2;               // column half of this group
-            const int quarter = warp & 3;
-            const int r = quarter * 32 + lane;
-            const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-            const int g = r / p.TPT, e = r - g * p.TPT;
-            const bool row_valid = g < p.G && e < ne;
-            const int tok = tok0 + e;
-            constexpr int HC = BK / 2;
-            const int cb = sb * HC;
+            ++qi;
+            w = w_next; nb = nb_next;
+        }
+    } else {
+        // ------------------------------------------------------------------ dS and the epilogue: one row, half the columns
+        const int sb = (warp - 2) >> 2;               // column half of this group
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const int g = r / p.TPT, e = r - g * p.TPT;
+        constexpr int HC = BK / 2;
+        const int cb = sb * HC;
+        bool ok = true;
+        int c = 0, qi = 0;
+        for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+            const DqItem m = dq_item(p, ntiles, w, lane);
+            const bool row_valid = g < p.G && e < m.ne;
+            const int tok = m.tok0 + e;
             int lo_r = 0, hi_r = -1;
             float lse_r = 0.f, delta_s = 0.f;
             if (row_valid) {
-                lo_r = p.kv_lo ? __ldg(p.kv_lo + tok) : __ldg(p.cu_k + seq);
+                lo_r = p.kv_lo ? __ldg(p.kv_lo + tok) : __ldg(p.cu_k + m.seq);
                 hi_r = __ldg(p.kv_hi + tok);
-                const int64_t idx = (int64_t)(h * p.G + g) * p.N + tok;
+                const int64_t idx = (int64_t)(m.h * p.G + g) * p.N + tok;
                 lse_r = __ldg(p.lse + idx);
                 delta_s = __ldg(p.delta + idx) * p.scale;
                 if (!(lse_r > -INFINITY)) hi_r = lo_r - 1;      // a row that saw nothing in the forward sees nothing here
             }
-            bool ok = true;
-            for (int j = 0; j < nblk && ok; ++j) {
-                const int b = j & 1;
-                const int R0 = row_lo + j * BK;
+            for (int j = 0; j < m.nblk && ok; ++j, ++c) {
+                const int b = c & 1;
+                const int R0 = m.row_lo + j * BK;
                 const int c_lo = max(0, lo_r - R0), c_hi = min(BK, hi_r - R0 + 1);
-                ok = mbar_wait(&sdp_full[b], (j >> 1) & 1, status) && ok;
+                ok = mbar_wait(&sdp_full[b], (c >> 1) & 1, status) && ok;
                 tc_fence_after();
                 uint32_t dd[HC / 2];
                 const bool all_visible = __all_sync(0xffffffffu, c_lo == 0 && c_hi == BK);
@@ -610,6 +657,8 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
                     tmem_ld32(tbase + lane_off + b * 128 + cb, sv);
                     tmem_ld32(tbase + lane_off + b * 128 + BK + cb, dv);
                     tmem_ld_wait();
+                    tc_fence_before();
+                    mbar_arrive(&sdp_free[b]);       // both rows are in registers: the buffer may take tile c + 2
                     if (all_visible) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
@@ -629,9 +678,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
                         }
                     }
                 }
-                tc_fence_before();
-                mbar_arrive(&sdp_free[b]);
-                ok = mbar_wait(&ds_empty[b], ((j >> 1) & 1) ^ 1, status) && ok;      // the dQ product of tile j - 2 has read this buffer
+                ok = mbar_wait(&ds_empty[b], ((c >> 1) & 1) ^ 1, status) && ok;      // the dQ product of tile c - 2 has read this buffer
                 uint8_t* ds = sDS + b * kDS;
 #pragma unroll
                 for (int c4 = 0; c4 < HC / 8; ++c4)
@@ -640,18 +687,18 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
                 fence_async_smem();
                 mbar_arrive(&ds_full[b]);
             }
-            // ---- epilogue: this group's 64 of the 128 dQ columns
-            if (nblk > 0) {
-                ok = mbar_wait(&ds_empty[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, status) && ok;
+            // ---- epilogue of the item: this group's 64 of the 128 dQ columns
+            const bool full_tile = m.ne == p.TPT && p.G * p.TPT == kTileRows && m.nblk > 0;
+            if (m.nblk > 0) {
+                ok = mbar_wait(&ds_empty[(c - 1) & 1], ((c - 1) >> 1) & 1, status) && ok;      // the item's last dQ product is done
                 tc_fence_after();
             }
-            const bool full_tile = ne == p.TPT && p.G * p.TPT == kTileRows;
-            ET* drow = reinterpret_cast<ET*>(p.dq) + ((int64_t)tok * p.Hq + (h * p.G + g)) * D + sb * 64;
-            uint8_t* stage = sQ + sb * (kTileRows * 128);
+            ET* drow = reinterpret_cast<ET*>(p.dq) + ((int64_t)tok * p.Hq + (m.h * p.G + g)) * D + sb * 64;
+            uint8_t* stage = sDS + sb * kDS;            // (both dS buffers are free: every dQ product of the item is done)
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t a[32];
-                if (nblk > 0) {
+                if (m.nblk > 0) {
                     tmem_ld32(tbase + lane_off + cDQ + sb * 64 + c0, a);
                     tmem_ld_wait();
                 } else {
@@ -673,17 +720,24 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
                     }
                 }
             }
+            if (m.nblk > 0) {
+                tc_fence_before();
+                mbar_arrive(dq_free);            // the accumulator may take the next item
+                ++qi;
+            }
             if (full_tile) {
                 fence_async_smem();
                 if (sb == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
                 else asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (quarter == 0 && lane == 0 && ok) {
-                    tma_store_3d(&dqmap, sb * 64, tok0, h * p.G, smem_u32(stage));
+                if (quarter == 0 && lane == 0) {
+                    if (ok) tma_store_3d(&dqmap, sb * 64, m.tok0, m.h * p.G, smem_u32(stage));
                     bulk_commit();
-                    bulk_wait_read0();     // the staging memory has been read; the global writes complete on their own
+                    bulk_wait_read0();           // the staging memory is a dS buffer again in the next item
                 }
+                asm volatile("bar.sync 3, 256;" ::: "memory");
             }
         }
+        (void)qi;
     }
     tc_fence_before();
     __syncthreads();
@@ -703,21 +757,24 @@ cudaError_t launch_range_bwd_dq(int dtype, const SelBwdArgs& a, const SelShape& 
     p.scale = a.sm_scale; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
     p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.status = status;
     constexpr int smem = 2 * kTileRows * 128 * 2 + kDqStages * 2 * kRdBK * 128 * 2 + 2 * kTileRows * kRdBK * 2 + 256;
-    const int max_tiles = (int)((s.N + s.TPT - 1) / s.TPT) + s.B;
+    const int64_t max_items = ((s.N + s.TPT - 1) / s.TPT + s.B) * (int64_t)s.Hk;
+    int sms = 0;
+    if (device_sm_count(&sms) != 0 || sms <= 0) return cudaErrorInvalidValue;
+    const unsigned grid = (unsigned)(max_items < sms ? max_items : sms);
     cudaError_t e;
     if (dtype == kBF16) {
         auto kern = range_bwd_dq_dense<__nv_bfloat16>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         prof_begin(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
-        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kDqThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
+        kern<<<grid, kDqThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
         prof_end(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
     } else {
         auto kern = range_bwd_dq_dense<__half>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         prof_begin(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
-        kern<<<dim3((unsigned)max_tiles, (unsigned)s.Hk), kDqThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
+        kern<<<grid, kDqThreads, smem, stream>>>(p, qmap, domap, kmap, vmap, dqmap);
         prof_end(FSA_KERNEL_SEL_BWD_DQ_REDUCE, stream);
     }
     return cudaGetLastError();
