@@ -43,30 +43,50 @@ __global__ void __launch_bounds__(256) rope_kernel(const ET* __restrict__ x, int
     *reinterpret_cast<uint4*>(orow + half + v * 8) = o2;
 }
 
-// out[n, :] = g[n,0] a[n, :] + g[n,1] b[n, :] + g[n,2] c[n, :]   (rows of HD = heads * head_dim elements)
+// 16-byte streaming load / store (the rows are used once: keep them out of the way of L2-resident data)
+__device__ __forceinline__ uint4 ld_stream16(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+
+// out[n, :] = g[n,0] a[n, :] + g[n,1] b[n, :] + g[n,2] c[n, :]   (rows of HD = heads * head_dim elements).
+// Two 16-byte vectors per thread, all six loads issued before the arithmetic.
 template <typename ET>
 __global__ void __launch_bounds__(256) gate_mix_fwd_kernel(const ET* __restrict__ g, const ET* __restrict__ a,
                                                            const ET* __restrict__ b, const ET* __restrict__ c, int64_t N, int HD,
                                                            ET* __restrict__ out) {
     const int vec = HD / 8;
-    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= N * vec) return;
-    const int64_t n = gid / vec;
-    const float g0 = (float)g[n * 3], g1 = (float)g[n * 3 + 1], g2 = (float)g[n * 3 + 2];
-    uint4 va = reinterpret_cast<const uint4*>(a)[gid], vb = reinterpret_cast<const uint4*>(b)[gid],
-          vc = reinterpret_cast<const uint4*>(c)[gid];
-    const uint32_t *pa = &va.x, *pb = &vb.x, *pc = &vc.x;
-    uint4 o;
-    uint32_t* po = &o.x;
+    const int64_t total = N * vec;
+    const int64_t base = (int64_t)blockIdx.x * (blockDim.x * 2) + threadIdx.x;
+    uint4 va[2], vb[2], vc[2];
+    float gg[2][3];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float2 x = ElemTraits<ET>::unpack2(pa[i]), y = ElemTraits<ET>::unpack2(pb[i]), z = ElemTraits<ET>::unpack2(pc[i]);
-        po[i] = ElemTraits<ET>::pack2(g0 * x.x + g1 * y.x + g2 * z.x, g0 * x.y + g1 * y.y + g2 * z.y);
+    for (int u = 0; u < 2; ++u) {
+        const int64_t gid = base + u * blockDim.x;
+        if (gid < total) {
+            va[u] = ld_stream16(reinterpret_cast<const uint4*>(a) + gid);
+            vb[u] = ld_stream16(reinterpret_cast<const uint4*>(b) + gid);
+            vc[u] = ld_stream16(reinterpret_cast<const uint4*>(c) + gid);
+            const int64_t n = gid / vec;
+            gg[u][0] = (float)g[n * 3]; gg[u][1] = (float)g[n * 3 + 1]; gg[u][2] = (float)g[n * 3 + 2];
+        }
     }
-    reinterpret_cast<uint4*>(out)[gid] = o;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int64_t gid = base + u * blockDim.x;
+        if (gid >= total) continue;
+        const uint32_t *pa = &va[u].x, *pb = &vb[u].x, *pc = &vc[u].x;
+        uint4 o;
+        uint32_t* po = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 x = ElemTraits<ET>::unpack2(pa[i]), y = ElemTraits<ET>::unpack2(pb[i]), z = ElemTraits<ET>::unpack2(pc[i]);
+            po[i] = ElemTraits<ET>::pack2(gg[u][0] * x.x + gg[u][1] * y.x + gg[u][2] * z.x, gg[u][0] * x.y + gg[u][1] * y.y + gg[u][2] * z.y);
+        }
+        st_stream16(reinterpret_cast<uint4*>(out) + gid, o);
+    }
 }
 
-// da = g0 do, db = g1 do, dc = g2 do, dg[n, i] = sum over the row of do * branch_i.  One warp per token.
+// da = g0 do, db = g1 do, dc = g2 do, dg[n, i] = sum over the row of do * branch_i.  One warp per token; two 16-byte
+// vectors of every input per lane and iteration (eight loads in flight).
 template <typename ET>
 __global__ void __launch_bounds__(256) gate_mix_bwd_kernel(const ET* __restrict__ g, const ET* __restrict__ a,
                                                            const ET* __restrict__ b, const ET* __restrict__ c,
@@ -78,28 +98,42 @@ __global__ void __launch_bounds__(256) gate_mix_bwd_kernel(const ET* __restrict_
     const float g0 = (float)g[n * 3], g1 = (float)g[n * 3 + 1], g2 = (float)g[n * 3 + 2];
     float s0 = 0.f, s1 = 0.f, s2 = 0.f;
     const int vec = HD / 8;
-    for (int v = lane; v < vec; v += 32) {
-        const int64_t idx = n * vec + v;
-        uint4 vd = reinterpret_cast<const uint4*>(d_o)[idx];
-        uint4 va = reinterpret_cast<const uint4*>(a)[idx], vb = reinterpret_cast<const uint4*>(b)[idx],
-              vc = reinterpret_cast<const uint4*>(c)[idx];
-        const uint32_t *pd = &vd.x, *pa = &va.x, *pb = &vb.x, *pc = &vc.x;
-        uint4 oa, ob, oc;
-        uint32_t *qa = &oa.x, *qb = &ob.x, *qc = &oc.x;
+    for (int v0 = lane; v0 < vec; v0 += 64) {
+        uint4 vd[2], va[2], vb[2], vc[2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float2 d = ElemTraits<ET>::unpack2(pd[i]);
-            float2 x = ElemTraits<ET>::unpack2(pa[i]), y = ElemTraits<ET>::unpack2(pb[i]), z = ElemTraits<ET>::unpack2(pc[i]);
-            s0 += d.x * x.x + d.y * x.y;
-            s1 += d.x * y.x + d.y * y.y;
-            s2 += d.x * z.x + d.y * z.y;
-            qa[i] = ElemTraits<ET>::pack2(g0 * d.x, g0 * d.y);
-            qb[i] = ElemTraits<ET>::pack2(g1 * d.x, g1 * d.y);
-            qc[i] = ElemTraits<ET>::pack2(g2 * d.x, g2 * d.y);
+        for (int u = 0; u < 2; ++u) {
+            const int v = v0 + 32 * u;
+            if (v < vec) {
+                const int64_t idx = n * vec + v;
+                vd[u] = ld_stream16(reinterpret_cast<const uint4*>(d_o) + idx);
+                va[u] = ld_stream16(reinterpret_cast<const uint4*>(a) + idx);
+                vb[u] = ld_stream16(reinterpret_cast<const uint4*>(b) + idx);
+                vc[u] = ld_stream16(reinterpret_cast<const uint4*>(c) + idx);
+            }
         }
-        reinterpret_cast<uint4*>(da)[idx] = oa;
-        reinterpret_cast<uint4*>(db)[idx] = ob;
-        reinterpret_cast<uint4*>(dc)[idx] = oc;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int v = v0 + 32 * u;
+            if (v >= vec) continue;
+            const int64_t idx = n * vec + v;
+            const uint32_t *pd = &vd[u].x, *pa = &va[u].x, *pb = &vb[u].x, *pc = &vc[u].x;
+            uint4 oa, ob, oc;
+            uint32_t *qa = &oa.x, *qb = &ob.x, *qc = &oc.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float2 d = ElemTraits<ET>::unpack2(pd[i]);
+                float2 x = ElemTraits<ET>::unpack2(pa[i]), y = ElemTraits<ET>::unpack2(pb[i]), z = ElemTraits<ET>::unpack2(pc[i]);
+                s0 += d.x * x.x + d.y * x.y;
+                s1 += d.x * y.x + d.y * y.y;
+                s2 += d.x * z.x + d.y * z.y;
+                qa[i] = ElemTraits<ET>::pack2(g0 * d.x, g0 * d.y);
+                qb[i] = ElemTraits<ET>::pack2(g1 * d.x, g1 * d.y);
+                qc[i] = ElemTraits<ET>::pack2(g2 * d.x, g2 * d.y);
+            }
+            st_stream16(reinterpret_cast<uint4*>(da) + idx, oa);
+            st_stream16(reinterpret_cast<uint4*>(db) + idx, ob);
+            st_stream16(reinterpret_cast<uint4*>(dc) + idx, oc);
+        }
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
@@ -141,7 +175,7 @@ extern "C" int fsa_gate_mix_fwd(const void* gate, const void* a, const void* b, 
     if (!gate || !a || !b || !c || !out || row_elems % 8) return FSA_ERR_BAD_ARG;
     (void)cudaGetLastError();
     int64_t threads = total * (row_elems / 8);
-    unsigned grid = (unsigned)((threads + 255) / 256);
+    unsigned grid = (unsigned)((threads + 511) / 512);   // two vectors per thread
     if (dtype == FSA_DTYPE_BF16)
         gate_mix_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)a,
                                                                                    (const __nv_bfloat16*)b, (const __nv_bfloat16*)c, total,
