@@ -355,8 +355,10 @@ __global__ void __launch_bounds__(256) sel_bwd_delta(const ET* __restrict__ o, i
         a[j] = b[j] = make_uint4(0u, 0u, 0u, 0u);
         nn[j] = 0; hh[j] = 0;
         if (r < rows) {
-            nn[j] = r / Hq;
-            hh[j] = (int)(r - nn[j] * Hq);
+            // (N * Hq fits in 32 bits for every problem the index build accepts: a 32-bit division, not a 64-bit one)
+            const uint32_t n32 = (uint32_t)r / (uint32_t)Hq;
+            nn[j] = n32;
+            hh[j] = (int)((uint32_t)r - n32 * (uint32_t)Hq);
             a[j] = *reinterpret_cast<const uint4*>(o + nn[j] * o_sn + (int64_t)hh[j] * o_sh + part * 8);
             b[j] = *reinterpret_cast<const uint4*>(d_o + nn[j] * do_sn + (int64_t)hh[j] * do_sh + part * 8);
         }
