@@ -91,6 +91,11 @@ SIGNATURES = {
     ),
     "fsa_rope": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p]),
+    "fsa_gate_proj_mix_scratch_bytes": (c_int64, [c_int64, c_int]),
+    "fsa_gate_proj_mix_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
+                                      c_void_p, c_void_p]),
+    "fsa_gate_proj_mix_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "fsa_gate_mix_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "fsa_gate_mix_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_void_p]),

@@ -13,7 +13,7 @@ import torch
 from fsa.module.rope import RopeConfig, RotaryEmbedding
 from fsa.ops.compressed_attention import compressed_attention
 from fsa.ops.FSA_topk_sparse_attention import FSA_topk_sparse_attention
-from fsa.ops.gate import gate_mix
+from fsa.ops.gate import gate_mix, gate_proj_mix
 from fsa.ops.linear_compress import compressed_seqlens, linear_compress
 from fsa.ops.range_attention import sliding_window_attention
 
@@ -105,7 +105,10 @@ class FlashSparseAttention(torch.nn.Module):
         sparse_attn_output = FSA_topk_sparse_attention(q, k, v, topk_idx, self.block_size, cu_seqlens, None)
         sliding_attn_output, _ = sliding_window_attention(q, k, v, cu_seqlens, self.window_size)
 
-        gate = self.gate(x)
-        attn_output = gate_mix(gate, compressed_attn_output, sparse_attn_output, sliding_attn_output)
+        # gate = sigmoid(Linear(hidden, 3)(x)) and the mix of the three branches, fused (same rounding points as the modules)
+        if x.is_cuda and self.hidden_size % 8 == 0 and self.hidden_size <= 16384:
+            attn_output = gate_proj_mix(x, self.gate[0].weight, compressed_attn_output, sparse_attn_output, sliding_attn_output)
+        else:
+            attn_output = gate_mix(self.gate(x), compressed_attn_output, sparse_attn_output, sliding_attn_output)
         attn_output = attn_output.reshape(attn_output.shape[0], -1)
         return self.proj_o(attn_output)

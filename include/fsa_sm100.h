@@ -259,6 +259,19 @@ int fsa_gate_mix_fwd(const void* gate, const void* a, const void* b, const void*
 int fsa_gate_mix_bwd(const void* gate, const void* a, const void* b, const void* c, const void* d_out, int64_t total,
                      int row_elems, int dtype, void* da, void* db, void* dc, float* dgate, void* stream);
 
+/* The layer's gate path fused (fsa/module/fsa.py:162-171): gate = sigmoid(x @ w_gate^T) with w_gate [3, hidden] (the
+ * Linear's product and the sigmoid each rounded to the activation dtype, as the separate modules round), then
+ * out = g0 a + g1 b + g2 c.  x [N, hidden] (row stride x_stride_n), a / b / c / out [N, row_elems] contiguous,
+ * gate [N, 3] (written: the backward needs it).  hidden <= 16384.
+ * Backward: da, db, dc = g_i d_out; dx [N, hidden] contiguous = the gate path's part of dL/dx; dw_gate [3, hidden];
+ * scratch: fsa_gate_proj_mix_scratch_bytes(N, hidden) bytes.  No atomics: dw_gate is summed over token chunks in order. */
+int64_t fsa_gate_proj_mix_scratch_bytes(int64_t total, int hidden);
+int fsa_gate_proj_mix_fwd(const void* x, int64_t x_stride_n, const void* w_gate, const void* a, const void* b, const void* c,
+                          int64_t total, int hidden, int row_elems, int dtype, void* out, void* gate, void* stream);
+int fsa_gate_proj_mix_bwd(const void* x, int64_t x_stride_n, const void* w_gate, const void* gate, const void* a, const void* b,
+                          const void* c, const void* d_out, int64_t total, int hidden, int row_elems, int dtype, void* da, void* db,
+                          void* dc, void* dx, void* dw_gate, float* scratch, int64_t scratch_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * One-step decode (fsa_preview)
  * ------------------------------------------------------------------------------------------- */
