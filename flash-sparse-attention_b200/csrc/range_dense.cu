@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_fwd_dense(const RangeDens
             int lo_r = 0, hi_r = -1;
             if (row_valid) {
                 lo_r = p.kv_lo ? __ldg(p.kv_lo + tok) : __ldg(p.cu_k + seq);
-                hi_r = __ldg(p.kv_hi + tok);
+                hi_r = min(__ldg(p.kv_hi + tok), (int)p.Nk - 1);     // rows past the end of K/V do not exist
             }
             float m_ref = -INFINITY, l_run = 0.f;
             bool ok = true;
@@ -638,7 +638,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
             float lse_r = 0.f, delta_s = 0.f;
             if (row_valid) {
                 lo_r = p.kv_lo ? __ldg(p.kv_lo + tok) : __ldg(p.cu_k + m.seq);
-                hi_r = __ldg(p.kv_hi + tok);
+                hi_r = min(__ldg(p.kv_hi + tok), (int)p.Nk - 1);     // rows past the end of K/V do not exist
                 const int64_t idx = (int64_t)(m.h * p.G + g) * p.N + tok;
                 lse_r = __ldg(p.lse + idx);
                 delta_s = __ldg(p.delta + idx) * p.scale;

@@ -387,6 +387,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
         const int e = r - g * s.TPT;
         // this warp's 32 staged rows: D/64 slabs of 32 rows x 128 bytes, 128-byte swizzle
         uint8_t* my_os = sOS + sb * C::kOS + quarter * (32 * D * 2);
+        // the (m, l) pairs of a (head, token) complete a 128-byte line over T tiles far apart in time: keep those lines in
+        // L2; the partial rows are written once and read once by the merge: let them leave first
+        const uint64_t pol_ml = l2_policy_evict_last(), pol_part = l2_policy_evict_first();
         const uint32_t tS0 = tbase + lane_off + C::cS;
         const uint32_t tO = tbase + lane_off + C::cO + sb * D;
         bool ok = true;
@@ -455,7 +458,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             }
             tc_fence_before();
             mbar_arrive(&o_empty[sb]);
-            if (prev_valid) p.ml[prev_mli] = make_float2(prev_m, prev_l);
+            if (prev_valid) st_float2_hint(p.ml + prev_mli, prev_m, prev_l, pol_ml);
             fence_async_smem();
             __syncwarp();
 #ifdef FSA_TIMING
@@ -464,7 +467,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) sel_fwd_main(const SelFwdParam
             if (lane == 0) {
 #pragma unroll
                 for (int b = 0; b < D / 64; ++b)
-                    tma_store_2d(&omap, b * 64, prev_j * kTileRows + quarter * 32, smem_u32(my_os + b * (32 * 128)));
+                    tma_store_2d_hint(&omap, b * 64, prev_j * kTileRows + quarter * 32, smem_u32(my_os + b * (32 * 128)), pol_part);
                 bulk_commit();
             }
             T_TOC(5);

@@ -74,6 +74,7 @@ def test_compressed_branch(seqlens, Hk, G, d, ks, stride):
     ([1200], 1, 2, 128, 1024, torch.bfloat16, 6.0),         # logits of magnitude ~70: the reference max of a row is raised
                                                             # while the accumulator already holds products (rescale in TMEM)
     ([900], 2, 4, 64, 300, torch.bfloat16, 5.0),
+    ([5, 130, 64, 1, 257, 33] * 4, 2, 4, 128, 96, torch.bfloat16, 1.0),    # many short sequences: most tiles are partial
 ])
 def test_query_major_forward_shapes(seqlens, Hk, G, d, W, dtype, qscale):
     """Forward of the query-tile-major kernel on group sizes / dtypes / logit ranges beyond the cases above, with q as a
