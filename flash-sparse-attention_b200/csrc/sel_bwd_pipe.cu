@@ -216,7 +216,6 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
         const int d_idx = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
         uint8_t* my_stage = sDQ + quarter * (32 * 256);
-        const uint64_t pol_part = l2_policy_evict_first();      // partial rows: written once, read once by the merge
         bool ok = true;
         int nflush = 0;
         BT_DECL;
@@ -265,7 +264,7 @@ __global__ void __launch_bounds__(bwdpipe::kThreads, 1) sel_bwd_pipe(const SelBw
             if (lane == 0) {
 #pragma unroll
                 for (int b = 0; b < D / 64; ++b)
-                    tma_store_2d_hint(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)), pol_part);
+                    tma_store_2d(&dqmap, b * 64, j * kTileRows + quarter * 32, smem_u32(my_stage + b * (32 * 128)));
                 bulk_commit();
             }
             }
