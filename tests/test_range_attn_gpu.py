@@ -25,7 +25,8 @@ def _lse_ok(lse, ref):
     assert float((lse.cpu()[fin] - ref[fin]).abs().max()) <= 1e-4
 
 
-@pytest.mark.parametrize("seqlens,Hk,G,d,W", [([700, 45, 300], 2, 2, 128, 128), ([1500], 1, 4, 128, 512), ([333], 2, 1, 64, 64)])
+@pytest.mark.parametrize("seqlens,Hk,G,d,W", [([700, 45, 300], 2, 2, 128, 128), ([1500], 1, 4, 128, 512), ([333], 2, 1, 64, 64),
+                                              ([33, 70, 5, 128] * 10, 1, 4, 128, 64)])
 def test_sliding_window(seqlens, Hk, G, d, W):
     N = sum(seqlens)
     g = torch.Generator().manual_seed(N + W)
@@ -75,6 +76,7 @@ def test_compressed_branch(seqlens, Hk, G, d, ks, stride):
                                                             # while the accumulator already holds products (rescale in TMEM)
     ([900], 2, 4, 64, 300, torch.bfloat16, 5.0),
     ([5, 130, 64, 1, 257, 33] * 4, 2, 4, 128, 96, torch.bfloat16, 1.0),    # many short sequences: most tiles are partial
+    ([17, 40, 3, 64, 129] * 14, 1, 2, 128, 50, torch.bfloat16, 1.0),       # 70 sequences: the tile lookup walks them 32 at a time
 ])
 def test_query_major_forward_shapes(seqlens, Hk, G, d, W, dtype, qscale):
     """Forward of the query-tile-major kernel on group sizes / dtypes / logit ranges beyond the cases above, with q as a
