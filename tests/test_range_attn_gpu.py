@@ -122,3 +122,59 @@ def test_query_major_forward_rows_without_keys():
             s = (kf[a : b + 1, hq // G] @ qf[t, hq]) / d ** 0.5
             ref = torch.softmax(s, 0) @ vf[a : b + 1, hq // G]
             assert float((o[t, hq].float().cpu() - ref).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("branch", ["window", "compressed"])
+def test_query_major_kernels_at_full_length(branch):
+    """One 32768-token sequence with the layer's group size (the length of the layer benchmark's sequences): o, lse and dq
+    of sampled tokens against closed-form fp32 attention over the token's range; dv through the identity
+    sum_rows(dv) = sum over tokens and heads of dO (every softmax row sums to one)."""
+    from fsa.ops.range_attention import compressed_attention_core, sliding_window_attention
+
+    L, Hk, G, d = 32768, 2, 4, 128
+    g = torch.Generator().manual_seed(77)
+    q = torch.randn(L, Hk * G, d, generator=g).to(torch.bfloat16)
+    do = torch.randn(L, Hk * G, d, generator=g).to(torch.bfloat16)
+    cu = make_cu_seqlens([L])
+    if branch == "window":
+        W = 512
+        k = torch.randn(L, Hk, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(L, Hk, d, generator=g).to(torch.bfloat16)
+        rng = lambda t: (max(0, t - W), t)
+        qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+        o, lse = sliding_window_attention(qc, kc, vc, cu.to(DEV), W)
+    else:
+        ks, st = 32, 16
+        nc = (L - ks) // st + 1
+        k = torch.randn(nc, Hk, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(nc, Hk, d, generator=g).to(torch.bfloat16)
+        rng = lambda t: (0, min((t - ks + 1) // st, nc - 1) if t >= ks - 1 else -1)
+        qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+        o, lse = compressed_attention_core(qc, kc, vc, ks, st, cu.to(DEV), make_cu_seqlens([nc]).to(DEV), nc)
+    o.backward(do.to(DEV))
+    oc, lc, dqc = o.detach().float().cpu(), lse.float().cpu(), qc.grad.float().cpu()
+    kf, vf, qf, dof = k.float(), v.float(), q.float(), do.float()
+    scale = d ** -0.5
+    toks = [0, 1, 30, 31, 32, 63, 64, 511, 512, 513, 4095, 4096, 20000, L - 2, L - 1] + torch.randint(0, L, (60,), generator=g).tolist()
+    for t in toks:
+        a, b = rng(t)
+        for hq in (0, 3, 5):
+            h = hq // G
+            if b < a:
+                assert float(oc[t, hq].abs().max()) == 0 and lc[hq, t] == float("-inf") and float(dqc[t, hq].abs().max()) == 0
+                continue
+            s = (kf[a : b + 1, h] @ qf[t, hq]) * scale
+            p = torch.softmax(s, 0)
+            o_ref = p @ vf[a : b + 1, h]
+            lse_ref = torch.logsumexp(s, 0) * 1.4426950408889634
+            dp = vf[a : b + 1, h] @ dof[t, hq]
+            ds = p * (dp - (o_ref * dof[t, hq]).sum()) * scale
+            dq_ref = ds @ kf[a : b + 1, h]
+            assert float((oc[t, hq] - o_ref).abs().max()) <= 2e-2 * max(1.0, float(o_ref.abs().max()))
+            assert abs(float(lc[hq, t] - lse_ref)) <= 1e-3
+            assert float((dqc[t, hq] - dq_ref).abs().max()) <= 2e-2 * max(1.0, float(dq_ref.abs().max()))
+    # dv: every probability row sums to one, so the column sums of dv equal those of dO over the tokens that see a key
+    seen = torch.tensor([rng(t)[1] >= rng(t)[0] for t in range(L)])
+    want = dof[seen].reshape(-1, Hk, G, d).sum((0, 2))
+    got = vc.grad.float().cpu().sum(0)
+    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max()) + 2.0
