@@ -178,3 +178,22 @@ def test_query_major_kernels_at_full_length(branch):
     want = dof[seen].reshape(-1, Hk, G, d).sum((0, 2))
     got = vc.grad.float().cpu().sum(0)
     assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max()) + 2.0
+
+
+def test_fp16_forward_and_backward():
+    """fp16 inputs through the query-tile-major forward / dQ kernels and the block-major dK/dV kernel."""
+    seqlens, Hk, G, d, W = [300, 130], 2, 4, 128, 100
+    N = sum(seqlens)
+    g = torch.Generator().manual_seed(21)
+    q, do = (torch.randn(N, Hk * G, d, generator=g).to(torch.float16) for _ in range(2))
+    k, v = (torch.randn(N, Hk, d, generator=g).to(torch.float16) for _ in range(2))
+    cu = make_cu_seqlens(seqlens)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.with_grads(orc.sliding_window_attention, q, k, v, do, cu, W)
+    qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    o, lse = sliding_window_attention(qc, kc, vc, cu.to(DEV), W)
+    o.backward(do.to(DEV))
+    _tol_ok(o, o_ref, "o")
+    _lse_ok(lse, lse_ref)
+    _tol_ok(qc.grad, dq_ref, "dq")
+    _tol_ok(kc.grad, dk_ref, "dk")
+    _tol_ok(vc.grad, dv_ref, "dv")
