@@ -83,3 +83,39 @@ def test_backward_is_bit_reproducible():
         y.backward(torch.randn(y.shape, generator=gy).to(torch.bfloat16).to(DEV))
         grads.append((xr.grad.clone(), wr.grad.clone()))
     assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1])
+
+
+def test_kernels_match_reference_generated_vectors():
+    """Forward (with the PE bias), dx and dW against the vectors the reference's own Triton kernels produced
+    (tests/golden/linear_compress_case*.npz; head_dim 64 cases run on the kernels of this library)."""
+    import glob
+    import os
+
+    import numpy as np
+
+    paths = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "linear_compress_case*.npz")))
+    assert len(paths) == 3
+    ran = 0
+    for path in paths:
+        z = np.load(path)
+        x, w, dy = (torch.from_numpy(z[k]) for k in ("x", "w", "dy"))
+        if x.shape[-1] not in (64, 128):
+            continue
+        ran += 1
+        pe = torch.from_numpy(z["pe"]) if z["pe"].size else None
+        cu = torch.from_numpy(z["cu"])
+        seqlens = (cu[1:] - cu[:-1]).tolist()
+        ks, st = int(z["kernel_size"]), int(z["kernel_stride"])
+        xc, wc = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+        with torch.no_grad():
+            yb, y_cu = linear_compress(xc, wc, cu.to(DEV), ks, st, pe.to(DEV) if pe is not None else None, seqlens)
+        assert y_cu.tolist() == z["y_cu"].tolist()
+        assert float((yb.float().cpu() - torch.from_numpy(z["y"]).float()).abs().max()) <= 1.6e-2
+        # the vectors' dx / dW are those of the two kernels (no bias path)
+        y, _ = linear_compress(xc, wc, cu.to(DEV), ks, st, None, seqlens)
+        assert float((y.float().cpu() - torch.from_numpy(z["y_nobias"]).float()).abs().max()) <= 8e-3
+        y.backward(dy.to(DEV))
+        dx_ref, dw_ref = torch.from_numpy(z["dx"]).float(), torch.from_numpy(z["dw"]).float()
+        assert float((xc.grad.float().cpu() - dx_ref).abs().max()) <= 8e-3 * max(1.0, float(dx_ref.abs().max()))
+        assert float((wc.grad.float().cpu() - dw_ref).norm()) <= 2e-3 * float(dw_ref.norm())
+    assert ran == 2
