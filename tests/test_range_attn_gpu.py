@@ -197,3 +197,36 @@ def test_fp16_forward_and_backward():
     _tol_ok(qc.grad, dq_ref, "dq")
     _tol_ok(kc.grad, dk_ref, "dk")
     _tol_ok(vc.grad, dv_ref, "dv")
+
+
+def test_sliding_window_against_flash_attn():
+    """The sliding-window branch against the very call the reference makes (fsa/module/fsa.py:149-159):
+    ``flash_attn_varlen_func(q, k, v, cu, cu, max, max, causal=True, window_size=(W, -1))`` of the third-party
+    flash-attn package (2.8.3 in this image), forward and backward, bf16 on both sides.  Skipped where that package has no
+    kernel for the GPU."""
+    try:
+        from flash_attn import flash_attn_varlen_func
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"flash_attn not importable: {e}")
+    seqlens, Hk, G, d, W = [700, 45, 300, 1111], 2, 4, 128, 512
+    N = sum(seqlens)
+    g = torch.Generator().manual_seed(31)
+    q, do = (torch.randn(N, Hk * G, d, generator=g).to(torch.bfloat16).to(DEV) for _ in range(2))
+    k, v = (torch.randn(N, Hk, d, generator=g).to(torch.bfloat16).to(DEV) for _ in range(2))
+    cu = make_cu_seqlens(seqlens).to(DEV)
+    qr, kr, vr = (x.clone().requires_grad_(True) for x in (q, k, v))
+    try:
+        o_ref = flash_attn_varlen_func(qr, kr, vr, cu, cu, max(seqlens), max(seqlens), causal=True, window_size=(W, -1))
+        o_ref.backward(do)
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"flash_attn does not run on this GPU: {type(e).__name__}")
+    qc, kc, vc = (x.clone().requires_grad_(True) for x in (q, k, v))
+    o, _ = sliding_window_attention(qc, kc, vc, cu, W)
+    o.backward(do)
+    # two bf16 implementations of the same function: each rounds its output once
+    for name, got, ref in (("o", o, o_ref), ("dq", qc.grad, qr.grad), ("dk", kc.grad, kr.grad), ("dv", vc.grad, vr.grad)):
+        err = (got.float() - ref.float()).abs()
+        scale = max(1.0, float(ref.float().abs().max()) / 2.0)
+        assert float(err.max()) <= 3e-2 * scale, f"{name}: max-abs {float(err.max()):.3e}"
+        assert float(err.mean()) <= 1.5e-3 * scale, f"{name}: mean-abs {float(err.mean()):.3e}"
