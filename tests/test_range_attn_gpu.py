@@ -26,7 +26,8 @@ def _lse_ok(lse, ref):
 
 
 @pytest.mark.parametrize("seqlens,Hk,G,d,W", [([700, 45, 300], 2, 2, 128, 128), ([1500], 1, 4, 128, 512), ([333], 2, 1, 64, 64),
-                                              ([33, 70, 5, 128] * 10, 1, 4, 128, 64)])
+                                              ([33, 70, 5, 128] * 10, 1, 4, 128, 64),
+                                              ([400, 90], 1, 2, 256, 100)])       # head_dim 256: the block-major forward and backward
 def test_sliding_window(seqlens, Hk, G, d, W):
     N = sum(seqlens)
     g = torch.Generator().manual_seed(N + W)
