@@ -231,3 +231,48 @@ def test_sliding_window_against_flash_attn():
         scale = max(1.0, float(ref.float().abs().max()) / 2.0)
         assert float(err.max()) <= 3e-2 * scale, f"{name}: max-abs {float(err.max()):.3e}"
         assert float(err.mean()) <= 1.5e-3 * scale, f"{name}: mean-abs {float(err.mean()):.3e}"
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_shapes_forward_backward(seed):
+    """Seeded random problems (sequence counts and lengths, group sizes incl. those that leave tile rows unused, head
+    sizes, windows shorter and longer than a K/V tile, both dtypes) through both branches against the oracle."""
+    rnd = torch.Generator().manual_seed(1000 + seed)
+    ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=rnd))
+    G = [1, 2, 3, 4, 6, 8, 16][ri(0, 6)]
+    Hk = ri(1, 2)
+    d = [64, 128][ri(0, 1)]
+    dtype = [torch.bfloat16, torch.float16][ri(0, 1)]
+    seqlens = [ri(1, 400) for _ in range(ri(1, 5))]
+    N = sum(seqlens)
+    q, do = (torch.randn(N, Hk * G, d, generator=rnd).to(dtype) for _ in range(2))
+    cu = make_cu_seqlens(seqlens)
+    if seed % 2 == 0:
+        W = ri(1, 300)
+        k, v = (torch.randn(N, Hk, d, generator=rnd).to(dtype) for _ in range(2))
+        ref = orc.with_grads(orc.sliding_window_attention, q, k, v, do, cu, W)
+        qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+        o, lse = sliding_window_attention(qc, kc, vc, cu.to(DEV), W)
+    else:
+        ks, st = [(32, 16), (16, 8), (32, 32)][ri(0, 2)]
+        cmp_lens = [(L - ks) // st + 1 if L >= ks else 0 for L in seqlens]
+        if sum(cmp_lens) == 0:
+            seqlens[0] += ks
+            N = sum(seqlens)
+            q, do = (torch.randn(N, Hk * G, d, generator=rnd).to(dtype) for _ in range(2))
+            cu = make_cu_seqlens(seqlens)
+            cmp_lens = [(L - ks) // st + 1 if L >= ks else 0 for L in seqlens]
+        Nc = sum(cmp_lens)
+        k, v = (torch.randn(Nc, Hk, d, generator=rnd).to(dtype) for _ in range(2))
+        cu_k = make_cu_seqlens(cmp_lens)
+        ref = orc.with_grads(orc.compressed_attention, q, k, v, do, ks, st, cu, cu_k)
+        qc, kc, vc = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+        o, lse = compressed_attention_core(qc, kc, vc, ks, st, cu.to(DEV), cu_k.to(DEV), max(cmp_lens))
+    o.backward(do.to(DEV))
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = ref
+    tag = f"seed {seed}: G={G} Hk={Hk} d={d} {dtype} seqlens={seqlens}"
+    _tol_ok(o, o_ref, "o " + tag)
+    _lse_ok(lse, lse_ref)
+    _tol_ok(qc.grad, dq_ref, "dq " + tag)
+    _tol_ok(kc.grad, dk_ref, "dk " + tag)
+    _tol_ok(vc.grad, dv_ref, "dv " + tag)
