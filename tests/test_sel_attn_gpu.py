@@ -72,6 +72,38 @@ def test_forward_backward_matches_oracle(seqlens, Hk, G, d, bs, T, dtype):
     _tol_ok(dv, dv_ref, "dv")
 
 
+@pytest.mark.parametrize("seed", list(range(10)))
+def test_random_shapes_match_oracle(seed):
+    """Seeded random problems: sequence counts and lengths, group sizes (also those that leave tile rows unused),
+    head sizes, block sizes, top-k, both dtypes."""
+    rnd = torch.Generator().manual_seed(5000 + seed)
+    ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=rnd))
+    G = [1, 2, 3, 4, 6, 8, 16][ri(0, 6)]
+    Hk = ri(1, 2)
+    d = [64, 128, 128, 256][ri(0, 3)]
+    bs = [32, 64, 64, 128][ri(0, 3)]
+    T = [2, 4, 8, 16][ri(0, 3)]
+    dtype = [torch.bfloat16, torch.float16][ri(0, 1)]
+    seqlens = [ri(0, 500) for _ in range(ri(1, 4))]
+    if sum(seqlens) == 0:
+        seqlens[0] = 77
+    N = sum(seqlens)
+    cu = make_cu_seqlens(seqlens)
+    q, k, v, do = make_qkv(N, Hk * G, Hk, d, 300 + seed, dtype)
+    idx = make_topk_idx(seqlens, Hk, T, bs, 400 + seed)
+    scale = d ** -0.5
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = sel_attn_forward_backward(q, k, v, do, idx, bs, cu, scale)
+    qc, kc, vc, dc, ic, cc = (x.to(DEV) for x in (q, k, v, do, idx, cu))
+    o, lse, ws = sel_attn_fwd(qc, kc, vc, ic, bs, cc, scale, check_status=True)
+    dq, dk, dv = sel_attn_bwd(qc, kc, vc, o, lse, dc, ic, bs, cc, scale, ws, check_status=True)
+    tag = f" (seed {seed}: G={G} Hk={Hk} d={d} B_K={bs} T={T} {dtype} seqlens={seqlens})"
+    _tol_ok(o, o_ref, "o" + tag)
+    assert float((lse.cpu() - lse_ref).abs().max()) <= 1e-4
+    _tol_ok(dq, dq_ref, "dq" + tag)
+    _tol_ok(dk, dk_ref, "dk" + tag)
+    _tol_ok(dv, dv_ref, "dv" + tag)
+
+
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "sel_attn_case*.npz")))
 
 
