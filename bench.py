@@ -34,7 +34,7 @@ import torch  # noqa: E402
 
 # DRAM bytes (read + write) per launch of the main kernels from one ncu capture of the small case (one 16384-token
 # sequence of config 1); traffic grows with the token count, so config 1 is 4 x that.
-NCU_TRAFFIC_SMALL = {"sel_bwd_main": 210.3e6 + 582.7e6, "sel_fwd_main": 79.5e6 + 496.1e6}
+NCU_TRAFFIC_SMALL = {"sel_bwd_main": 210.3e6 + 582.7e6, "sel_fwd_main": 73.3e6 + 479.6e6}
 # the compressed pass of the decode step at batch 8, from one ncu capture; grows with the batch
 NCU_TRAFFIC_DECODE_B8 = 268.5e6 + 6.7e6
 
