@@ -52,49 +52,6 @@ __device__ __forceinline__ float rd_ex2(float x) {
     return y;
 }
 
-// Sequences are cut into tiles of TPT tokens.  Both helpers are warp-collective (every lane calls them and gets the same
-// answer) and walk the sequences 32 at a time, so that a packed batch of thousands of short sequences costs B / 32 steps.
-__device__ __forceinline__ int rd_count_tiles(const int32_t* __restrict__ cu_q, int B, int TPT, int lane) {
-    int total = 0;
-    for (int b0 = 0; b0 < B; b0 += 32) {
-        const int b = b0 + lane;
-        int nt = b < B ? (__ldg(cu_q + b + 1) - __ldg(cu_q + b) + TPT - 1) / TPT : 0;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) nt += __shfl_xor_sync(0xffffffffu, nt, d);
-        total += nt;
-    }
-    return total;
-}
-// tile `want` of the list: its sequence (-1 if there is no such tile), first token and number of tokens
-__device__ __forceinline__ void rd_find_tile(const int32_t* __restrict__ cu_q, int B, int TPT, int want, int lane, int& seq, int& tok0,
-                                             int& ne) {
-    seq = -1; tok0 = 0; ne = 0;
-    if (want < 0) return;
-    int acc = 0;
-    for (int b0 = 0; b0 < B; b0 += 32) {
-        const int b = b0 + lane;
-        const int s0 = b < B ? __ldg(cu_q + b) : 0, L = b < B ? __ldg(cu_q + b + 1) - s0 : 0;
-        const int nt = (L + TPT - 1) / TPT;
-        int incl = nt;                                   // inclusive prefix over the 32 sequences
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int up = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += up;
-        }
-        const unsigned hit = __ballot_sync(0xffffffffu, want < acc + incl);
-        if (hit) {
-            const int src = __ffs(hit) - 1;              // first sequence whose tiles reach past `want`
-            const int first = acc + __shfl_sync(0xffffffffu, incl - nt, src);
-            const int s_src = __shfl_sync(0xffffffffu, s0, src), L_src = __shfl_sync(0xffffffffu, L, src);
-            seq = b0 + src;
-            tok0 = s_src + (want - first) * TPT;
-            ne = min(TPT, s_src + L_src - tok0);
-            return;
-        }
-        acc += __shfl_sync(0xffffffffu, incl, 31);
-    }
-}
-
 template <int D, typename ET>
 __global__ void __launch_bounds__(kRdThreads, 2) range_fwd_dense(const RangeDenseParams p, const __grid_constant__ CUtensorMap qmap,
                                                                 const __grid_constant__ CUtensorMap kmap,
@@ -141,9 +98,9 @@ __global__ void __launch_bounds__(kRdThreads, 2) range_fwd_dense(const RangeDens
     }
     if (warp == 0) {
         // which tile is this: the heaviest (last) tiles of the list start first
-        const int total = rd_count_tiles(p.cu_q, p.B, p.TPT, lane);
+        const int total = count_seq_tiles(p.cu_q, p.B, p.TPT, lane);
         int seq, tok0, ne;
-        rd_find_tile(p.cu_q, p.B, p.TPT, total - 1 - (int)blockIdx.x, lane, seq, tok0, ne);
+        find_seq_tile(p.cu_q, p.B, p.TPT, total - 1 - (int)blockIdx.x, lane, seq, tok0, ne);
         // lowest and highest K/V row any token of the tile sees
         int lo = INT_MAX, hi = -1;
         if (seq >= 0) {
@@ -443,7 +400,7 @@ __device__ __forceinline__ DqItem dq_item(const RangeDqParams& p, int ntiles, in
     m.h = w % p.Hk;
     const int want = ntiles - 1 - w / p.Hk;
     m.row_lo = 0; m.nblk = 0;
-    rd_find_tile(p.cu_q, p.B, p.TPT, want, lane, m.seq, m.tok0, m.ne);
+    find_seq_tile(p.cu_q, p.B, p.TPT, want, lane, m.seq, m.tok0, m.ne);
     if (m.seq < 0) return m;
     int lo = INT_MAX, hi = -1;
     const int k0 = __ldg(p.cu_k + m.seq);
@@ -515,7 +472,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = tmem_slot;
-    const int ntiles = rd_count_tiles(p.cu_q, p.B, p.TPT, lane);
+    const int ntiles = count_seq_tiles(p.cu_q, p.B, p.TPT, lane);
     const int nitems = ntiles * p.Hk;
 
     if (warp == 0) {

@@ -227,6 +227,49 @@ struct TileSchedule {
     __device__ __forceinline__ int tile(int k) const { return ((k / run) * grid + cta) * run + (k % run); }
 };
 
+// Query-tile-major kernels cut every sequence into tiles of TPT consecutive tokens.  Both helpers are warp-collective (every lane calls them and gets the same
+// answer) and walk the sequences 32 at a time, so that a packed batch of thousands of short sequences costs B / 32 steps.
+__device__ __forceinline__ int count_seq_tiles(const int32_t* __restrict__ cu_q, int B, int TPT, int lane) {
+    int total = 0;
+    for (int b0 = 0; b0 < B; b0 += 32) {
+        const int b = b0 + lane;
+        int nt = b < B ? (__ldg(cu_q + b + 1) - __ldg(cu_q + b) + TPT - 1) / TPT : 0;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) nt += __shfl_xor_sync(0xffffffffu, nt, d);
+        total += nt;
+    }
+    return total;
+}
+// tile `want` of the list: its sequence (-1 if there is no such tile), first token and number of tokens
+__device__ __forceinline__ void find_seq_tile(const int32_t* __restrict__ cu_q, int B, int TPT, int want, int lane, int& seq, int& tok0,
+                                             int& ne) {
+    seq = -1; tok0 = 0; ne = 0;
+    if (want < 0) return;
+    int acc = 0;
+    for (int b0 = 0; b0 < B; b0 += 32) {
+        const int b = b0 + lane;
+        const int s0 = b < B ? __ldg(cu_q + b) : 0, L = b < B ? __ldg(cu_q + b + 1) - s0 : 0;
+        const int nt = (L + TPT - 1) / TPT;
+        int incl = nt;                                   // inclusive prefix over the 32 sequences
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, want < acc + incl);
+        if (hit) {
+            const int src = __ffs(hit) - 1;              // first sequence whose tiles reach past `want`
+            const int first = acc + __shfl_sync(0xffffffffu, incl - nt, src);
+            const int s_src = __shfl_sync(0xffffffffu, s0, src), L_src = __shfl_sync(0xffffffffu, L, src);
+            seq = b0 + src;
+            tok0 = s_src + (want - first) * TPT;
+            ne = min(TPT, s_src + L_src - tok0);
+            return;
+        }
+        acc += __shfl_sync(0xffffffffu, incl, 31);
+    }
+}
+
 // One tile of the list, read from its record: no searching, and the address depends only on the
 // tile index, so records and entries can be prefetched any number of tiles ahead.
 struct TileInfo {

@@ -72,18 +72,13 @@ __global__ void __launch_bounds__(128) select_topk_fused_kernel(const SelFusedPa
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 5);
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    // which (sequence, query tile) is this CTA's
-    int item = blockIdx.x, b = 0, L = 0;
-    for (; b < p.B; ++b) {
-        L = __ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b);
-        const int nt = (L + kSfRows - 1) / kSfRows;
-        if (item < nt) break;
-        item -= nt;
-    }
-    if (b >= p.B) return;
+    // which (sequence, query tile) is this CTA's (every warp finds it, 32 sequences per step)
+    int b, n0, ne;
+    find_seq_tile(p.cu_q, p.B, kSfRows, (int)blockIdx.x, tid & 31, b, n0, ne);
+    if (b < 0) return;
     const int h = blockIdx.y;
-    const int tok0 = item * kSfRows;
-    const int n0 = __ldg(p.cu_q + b) + tok0;
+    const int L = __ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b);
+    const int tok0 = n0 - __ldg(p.cu_q + b);
     const int kbase = __ldg(p.cu_k + b), ncmp = __ldg(p.cu_k + b + 1) - kbase;
     const int t_last = min(L, tok0 + kSfRows) - 1;
     const int nkt = ((t_last / p.BK + 1) * BS + kSfKeys - 1) / kSfKeys;     // key tiles that hold a causal block of the tile

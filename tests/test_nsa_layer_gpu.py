@@ -213,6 +213,7 @@ def test_topk_selection_on_real_valued_scores():
     ([300, 20, 700, 129], 1, 4, 128, 32, 16, 64, 16),      # a sequence with no compressed token, ragged tails
     ([513, 400], 2, 1, 64, 32, 16, 32, 6),                  # 32-key blocks: taps [1, 2, 1]
     ([2100], 1, 2, 128, 32, 16, 64, 16),                    # more than one tile of 128 compressed keys
+    ([70, 200, 33, 140, 129] * 8, 1, 2, 128, 32, 16, 64, 4),   # 40 sequences: the tile lookup walks them 32 at a time
 ])
 def test_fused_topk_selection_against_oracle(seqlens, Hk, G, d, ks, st, bs, T):
     """fsa_select_topk_fused (q.k^T inside the kernel) against the oracle fed fp32 products of the same bf16 inputs.
