@@ -364,11 +364,11 @@ static cudaError_t launch_rd(const RangeDenseParams& p, const CUtensorMap& qmap,
 // P = exp2(S c - lse), dS = scale P (dP - delta) to swizzled shared memory, dQ (+)= dS K accumulated in TMEM over the
 // tiles and written once.  (In the reference: the dQ part of _backward_kernel, nsa_ref/ops/compressed_attention.py:
 // 193-760, and of flash-attn's backward for the sliding window.)  With it the block-major backward kernel computes
-// only dK and dV and no partial dQ row is written or merged.  One CTA per SM, 320 threads:
+// only dK and dV and no partial dQ row is written or merged.  One CTA per SM, 352 threads:
 //   warp 0      TMA producer: Q and dO tiles of every item, (K, V) tiles through a four-stage ring (a stage comes free only
 //               when the tile's dQ product is done, and the next load needs a microsecond to land);
-//   warp 1      one elected thread issues S(j+1), dP(j+1) (two TMEM buffers) before dQ(j), so that the row threads of
-//               tile j and the products of tile j + 1 overlap;
+//   warp 1      one elected thread issues S and dP (two TMEM buffers: they run a tile ahead of the row threads);
+//   warp 10     one elected thread issues dQ (a second issuer: see the MMA section);
 //   warps 2..9  two groups of 128 row threads, each on 32 of the 64 key columns: dS to one of two shared-memory buffers;
 //               epilogue: each group rounds 64 of the dQ columns, stages them (the Q tile's memory) and stores its slab by
 //               3-D TMA (plain stores for the last, partial tile of a sequence).
@@ -386,7 +386,7 @@ struct RangeDqParams {
     int* status;
 };
 
-constexpr int kDqThreads = 320;
+constexpr int kDqThreads = 352;     // producer, S/dP issuer, 8 row warps, dQ issuer
 constexpr int kDqStages = 4;
 
 // One work item of the dQ kernel: a tile of tokens x one KV head.
@@ -509,11 +509,12 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        // The K/V tiles of all items form one sequence c = 0, 1, ...; S / dP of tile c + 1 are issued before dQ of tile c,
-        // also across the boundary between two items (then the next item's Q / dO must have landed, which the producer
-        // starts as soon as this item's last S / dP are done).
+    } else if (warp == 1 || warp == kDqThreads / 32 - 1) {
+        // ------------------------------------------------------------------ MMA issuers
+        // Two warps, because one thread issues a tcgen05.mma only every ~100 cycles while the tensor pipe needs ~60 for an
+        // N = 64 product: warp 1 issues S and dP, the last warp issues dQ.  The K/V tiles of all items form one sequence
+        // c = 0, 1, ...; S / dP run ahead of dQ as far as their two TMEM buffers and the K/V ring allow, also across the
+        // boundary between two items (the next item's Q / dO are loaded as soon as this item's last S / dP are done).
         const bool leader = elect_one();
         constexpr uint32_t idesc_s = umma_idesc(ElemTraits<ET>::kIsBF16, 128, BK, false, false);
         constexpr uint32_t idesc_dq = umma_idesc(ElemTraits<ET>::kIsBF16, 128, D, false, true);     // dS (K-major) x K (MN-major)
@@ -524,73 +525,54 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
         const uint32_t ds_lo = umma_desc_lo(smem_u32(sDS), 16);
         const uint32_t k_mn_lo = umma_desc_lo(smem_u32(sKV), BK * 128);
         bool ok = true;
-        auto issue_sdp = [&](int c) {
-            const int b = c & 1, st = c % kDqStages;
-            ok = mbar_wait(&kv_full[st], (c / kDqStages) & 1, status) && ok;
-            ok = mbar_wait(&sdp_free[b], ((c >> 1) & 1) ^ 1, status) && ok;     // S / dP of tile c - 2 have been read
-            tc_fence_after();
-            if (leader) {
-                const uint32_t k_lo = kv_lo_ + (uint32_t)(st * ((2 * kKt) >> 4));
-                const uint32_t v_lo = k_lo + (uint32_t)(kKt >> 4);
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tbase + b * 128, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
-                            umma_desc_pack(k_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tbase + b * 128 + BK, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
-                            umma_desc_pack(v_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
-                umma_commit(&sdp_full[b]);
-            }
-            __syncwarp();
-        };
-        // next non-empty item at or after w
-        auto next_item = [&](int w, int& nb) {
-            nb = 0;
-            for (; w < nitems; w += gridDim.x) {
-                const DqItem m = dq_item(p, ntiles, w, lane);
-                if (m.nblk > 0) { nb = m.nblk; break; }
-            }
-            return w;
-        };
-        int nb = 0, nb_next = 0;
-        int w = next_item(blockIdx.x, nb);
         int c = 0, qi = 0;
-        if (w < nitems) {
-            ok = mbar_wait(qd_full, 0, status) && ok;
-            issue_sdp(0);
-        }
-        while (w < nitems && ok) {
-            const int w_next = next_item(w + gridDim.x, nb_next);
-            for (int j = 0; j < nb && ok; ++j, ++c) {
-                const int b = c & 1, st = c % kDqStages;
-                const bool last = j + 1 == nb;
-                if (!last) issue_sdp(c + 1);
-                else if (leader) umma_commit(qd_empty);          // every S / dP of this item has been issued
-                __syncwarp();
-                ok = mbar_wait(&ds_full[b], (c >> 1) & 1, status) && ok;
-                if (j == 0 && qi > 0) ok = mbar_wait(dq_free, (qi - 1) & 1, status) && ok;     // the previous item's dQ has been read
-                fence_async_smem();
-                tc_fence_after();
-                if (leader) {
-                    const uint32_t a_lo = ds_lo + (uint32_t)(b * (kDS >> 4));
-                    const uint32_t b_lo = k_mn_lo + (uint32_t)(st * ((2 * kKt) >> 4));
+        for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+            const DqItem m = dq_item(p, ntiles, w, lane);
+            if (m.nblk == 0) continue;
+            if (warp == 1) {
+                ok = mbar_wait(qd_full, qi & 1, status) && ok;
+                for (int j = 0; j < m.nblk && ok; ++j, ++c) {
+                    const int b = c & 1, st = c % kDqStages;
+                    ok = mbar_wait(&kv_full[st], (c / kDqStages) & 1, status) && ok;
+                    ok = mbar_wait(&sdp_free[b], ((c >> 1) & 1) ^ 1, status) && ok;     // S / dP of tile c - 2 have been read
+                    tc_fence_after();
+                    if (leader) {
+                        const uint32_t k_lo = kv_lo_ + (uint32_t)(st * ((2 * kKt) >> 4));
+                        const uint32_t v_lo = k_lo + (uint32_t)(kKt >> 4);
 #pragma unroll
-                    for (int ks = 0; ks < BK / 16; ++ks)
-                        umma_ss(tbase + cDQ, umma_desc_pack(a_lo + ks * 2, hi_1024), umma_desc_pack(b_lo + ks * (2048 >> 4), hi_1024),
-                                idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(&kv_empty[st]);
-                    umma_commit(&ds_empty[b]);
+                        for (int ks = 0; ks < D / 16; ++ks)
+                            umma_ss(tbase + b * 128, umma_desc_pack(q_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                                    umma_desc_pack(k_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+#pragma unroll
+                        for (int ks = 0; ks < D / 16; ++ks)
+                            umma_ss(tbase + b * 128 + BK, umma_desc_pack(do_lo + (ks >> 2) * kSlabA + (ks & 3) * 2, hi_1024),
+                                    umma_desc_pack(v_lo + (ks >> 2) * kSlabB + (ks & 3) * 2, hi_1024), idesc_s, ks > 0);
+                        umma_commit(&sdp_full[b]);
+                        if (j + 1 == m.nblk) umma_commit(qd_empty);          // every S / dP of this item has been issued
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
-                if (last && w_next < nitems) {
-                    // first S / dP of the next item, behind this item's last dQ
-                    ok = mbar_wait(qd_full, (qi + 1) & 1, status) && ok;
-                    issue_sdp(c + 1);
+            } else {
+                for (int j = 0; j < m.nblk && ok; ++j, ++c) {
+                    const int b = c & 1, st = c % kDqStages;
+                    ok = mbar_wait(&ds_full[b], (c >> 1) & 1, status) && ok;      // (implies S / dP of the tile are done with K and V)
+                    if (j == 0 && qi > 0) ok = mbar_wait(dq_free, (qi - 1) & 1, status) && ok;     // the previous item's dQ has been read
+                    fence_async_smem();
+                    tc_fence_after();
+                    if (leader) {
+                        const uint32_t a_lo = ds_lo + (uint32_t)(b * (kDS >> 4));
+                        const uint32_t b_lo = k_mn_lo + (uint32_t)(st * ((2 * kKt) >> 4));
+#pragma unroll
+                        for (int ks = 0; ks < BK / 16; ++ks)
+                            umma_ss(tbase + cDQ, umma_desc_pack(a_lo + ks * 2, hi_1024), umma_desc_pack(b_lo + ks * (2048 >> 4), hi_1024),
+                                    idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(&kv_empty[st]);
+                        umma_commit(&ds_empty[b]);
+                    }
+                    __syncwarp();
                 }
             }
             ++qi;
-            w = w_next; nb = nb_next;
         }
     } else {
         // ------------------------------------------------------------------ dS and the epilogue: one row, half the columns
