@@ -150,7 +150,10 @@ int fsa_sel_bwd(const void* q, const void* k, const void* v, const void* o, cons
  *   sliding window     - replaces flash_attn_varlen_func(causal=True, window_size=(W, -1)) as called in
  *       fsa/module/fsa.py:149-159: kv_lo[n] = max(cu[b], n - W), kv_hi[n] = n.
  * Tensors, strides, dtype, lse (log2 units), workspaces and return codes are as for fsa_sel_fwd / fsa_sel_bwd;
- * fsa_range_attn_bytes returns the three workspace sizes (any out pointer may be null). */
+ * fsa_range_attn_bytes returns the three workspace sizes (any out pointer may be null).
+ * fsa_range_attn_bwd at head_dim 128 computes dq with a query-tile-major kernel (accumulator in TMEM over the K/V tiles a
+ * tile of tokens sees, written once) and dk / dv with the block-major kernel; other head sizes use the block-major kernel
+ * for all three. */
 int fsa_range_attn_bytes(int64_t total_tokens, int64_t total_kv_rows, int batch, int num_q_heads, int num_kv_heads,
                          int head_dim, int max_blocks, int block_size, int64_t* index_bytes_out,
                          int64_t* fwd_scratch_bytes_out, int64_t* bwd_scratch_bytes_out);
