@@ -511,8 +511,9 @@ __global__ void __launch_bounds__(kDqThreads, 1) range_bwd_dq_dense(const RangeD
         }
     } else if (warp == 1 || warp == kDqThreads / 32 - 1) {
         // ------------------------------------------------------------------ MMA issuers
-        // Two warps, because one thread issues a tcgen05.mma only every ~100 cycles while the tensor pipe needs ~60 for an
-        // N = 64 product: warp 1 issues S and dP, the last warp issues dQ.  The K/V tiles of all items form one sequence
+        // Two warps: the k-steps of one accumulator follow one another at ~100 cycles each, and a single issuing thread also
+        // waits on barriers between products; with dQ on a warp of its own its chain overlaps the S / dP chains of the next
+        // tile (measured: 20 % faster).  Warp 1 issues S and dP, the last warp issues dQ.  The K/V tiles of all items form one sequence
         // c = 0, 1, ...; S / dP run ahead of dQ as far as their two TMEM buffers and the K/V ring allow, also across the
         // boundary between two items (the next item's Q / dO are loaded as soon as this item's last S / dP are done).
         const bool leader = elect_one();
