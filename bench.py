@@ -169,7 +169,7 @@ def tensor_peak(burst):
     v = float(peaks.get(key, 0) or 0)
     if v:
         return v, f"MEASURED_PEAKS.json {key}"
-    return (1590.0, "fallback (burst cuBLAS bf16 measured earlier on this pool)") if burst else (1400.0, "fallback (sustained cuBLAS bf16 on this pool)")
+    return (1590.0, "fallback (burst cuBLAS bf16 of an earlier B200 measurement)") if burst else (1400.0, "fallback (sustained cuBLAS bf16 of an earlier B200 measurement)")
 
 
 class Dist:
@@ -309,7 +309,7 @@ def run_decode(args, dd, steps, sub=False):
                                                cache.cmp_row0, max_len=max_len, shard=shard, **nsa)
         return gate_mix(mod.gate(qd.view(B, -1)), oc, os_.contiguous(), ow.contiguous())
 
-    # N > 1: the step holds two NCCL all-gathers; capturing them in a graph stalled here, so the sharded step is three
+    # N > 1: the step holds two NCCL all-gathers, which are kept out of the graphs (a captured collective did not complete), so the sharded step is three
     # graphs (its collective-free parts) with the two all-gathers launched in between
     use_graph = not args.no_graph
     step = eager_step

@@ -51,7 +51,7 @@ class GraphedStep:
 class GraphedShardedAttention:
     """The KV-sequence-sharded decode attention as three CUDA graphs around its two all-gathers.
 
-    A collective captured inside a graph stalled on this system, and launched kernel by kernel the sharded step is
+    A collective captured inside a graph did not complete, and launched kernel by kernel the sharded step is
     bound by host launch cost; so the step's three collective-free parts (``DecodeStepPlan.part1/2/3``) are captured
     separately and the two NCCL all-gathers of one packed buffer each stay ordinary launches between the replays:
     five launches per step instead of about forty."""
